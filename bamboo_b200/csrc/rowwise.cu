@@ -1,0 +1,341 @@
+// HBM-bound row-wise kernels of a transformer stage: LayerNorm forward/backward (with the
+// residual gradient folded in), bias-gradient column sums, token+position embedding
+// gather and its gradient scatter.  All loads/stores are 16-byte vectors; one warp owns a
+// row so no block-level synchronisation is needed on the hot loops; grids are sized as a
+// multiple of the SM count and stride over rows.
+#include "common.cuh"
+
+namespace {
+
+constexpr int WARPS = 8;              // warps per CTA for warp-per-row kernels
+constexpr int CTAS_PER_SM = 4;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& q, float* f) {
+  f[0] = bb::bf16_lo(q.x); f[1] = bb::bf16_hi(q.x); f[2] = bb::bf16_lo(q.y); f[3] = bb::bf16_hi(q.y);
+  f[4] = bb::bf16_lo(q.z); f[5] = bb::bf16_hi(q.z); f[6] = bb::bf16_lo(q.w); f[7] = bb::bf16_hi(q.w);
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 q;
+  q.x = bb::pack_bf16x2(f[0], f[1]); q.y = bb::pack_bf16x2(f[2], f[3]);
+  q.z = bb::pack_bf16x2(f[4], f[5]); q.w = bb::pack_bf16x2(f[6], f[7]);
+  return q;
+}
+
+// ------------------------------------------------------------------ LayerNorm forward
+// y = (x - mean) * rstd * gamma + beta ; statistics in fp32 (biased variance, eps inside sqrt)
+__global__ void __launch_bounds__(WARPS * 32)
+layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
+                     const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ y,
+                     float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int h, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int warp_global = blockIdx.x * WARPS + (threadIdx.x >> 5);
+  const int warp_stride = gridDim.x * WARPS;
+  const int nch = h >> 3;
+  for (int row = warp_global; row < rows; row += warp_stride) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * h);
+    float s = 0.f;
+    for (int c = lane; c < nch; c += 32) {
+      float f[8]; unpack8(xr[c], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += f[i];
+    }
+    const float mean = warp_sum(s) / (float)h;
+    float v = 0.f;
+    for (int c = lane; c < nch; c += 32) {   // second pass hits L1
+      float f[8]; unpack8(xr[c], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { float d = f[i] - mean; v += d * d; }
+    }
+    const float rstd = rsqrtf(warp_sum(v) / (float)h + eps);
+    uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * h);
+    for (int c = lane; c < nch; c += 32) {
+      float f[8], g[8], b[8];
+      unpack8(xr[c], f);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(gamma) + c), g);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(beta) + c), b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = (f[i] - mean) * rstd * g[i] + b[i];
+      yr[c] = pack8(f);
+    }
+    if (lane == 0) { mean_out[row] = mean; rstd_out[row] = rstd; }
+  }
+}
+
+// ------------------------------------------------------------------ LayerNorm backward
+// dx = rstd * (dy*gamma - mean(dy*gamma) - xhat * mean(dy*gamma*xhat)) [+ dres]
+// Per-CTA partial sums of dgamma = sum dy*xhat and dbeta = sum dy go to `partials`
+// ([gridDim.x][2][h] fp32); reduce_partials_kernel folds them into the fp32 gradients.
+__global__ void __launch_bounds__(WARPS * 32)
+layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                     const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
+                     const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
+                     __nv_bfloat16* __restrict__ dx, float* __restrict__ partials, int rows, int h) {
+  extern __shared__ float acc[];  // [warps][2][h], each lane owns its own columns
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = blockDim.x >> 5;
+  const int nch = h >> 3;
+  float* my_g = acc + (size_t)warp * 2 * h;
+  float* my_b = my_g + h;
+  for (int c = lane; c < nch; c += 32)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { my_g[c * 8 + i] = 0.f; my_b[c * 8 + i] = 0.f; }
+  const int warp_global = blockIdx.x * nwarps + warp;
+  const int warp_stride = gridDim.x * nwarps;
+  for (int row = warp_global; row < rows; row += warp_stride) {
+    const uint4* dyr = reinterpret_cast<const uint4*>(dy + (size_t)row * h);
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * h);
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float s1 = 0.f, s2 = 0.f;
+    for (int c = lane; c < nch; c += 32) {
+      float d[8], f[8], g[8];
+      unpack8(dyr[c], d); unpack8(xr[c], f);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(gamma) + c), g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { float t = d[i] * g[i]; s1 += t; s2 += t * (f[i] - mean) * rstd; }
+    }
+    const float c1 = warp_sum(s1) / (float)h, c2 = warp_sum(s2) / (float)h;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + (size_t)row * h);
+    const uint4* rr = dres ? reinterpret_cast<const uint4*>(dres + (size_t)row * h) : nullptr;
+    for (int c = lane; c < nch; c += 32) {
+      float d[8], f[8], g[8], o[8];
+      unpack8(dyr[c], d); unpack8(xr[c], f);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(gamma) + c), g);
+      float r[8];
+      if (rr) unpack8(rr[c], r);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float xh = (f[i] - mean) * rstd;
+        o[i] = rstd * (d[i] * g[i] - c1 - xh * c2) + (rr ? r[i] : 0.f);
+        my_g[c * 8 + i] += d[i] * xh;
+        my_b[c * 8 + i] += d[i];
+      }
+      dxr[c] = pack8(o);
+    }
+  }
+  __syncthreads();
+  float* out = partials + (size_t)blockIdx.x * 2 * h;
+  for (int j = threadIdx.x; j < 2 * h; j += blockDim.x) {
+    float s = 0.f;
+    for (int w = 0; w < nwarps; ++w) s += acc[(size_t)w * 2 * h + j];
+    out[j] = s;
+  }
+}
+
+// out[j] += sum_p partials[p * stride + j]   (fixed order: deterministic)
+__global__ void reduce_partials_kernel(const float* __restrict__ partials, float* __restrict__ out, int nparts, int n,
+                                       long long stride) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= n) return;
+  float s = 0.f;
+  for (int p = 0; p < nparts; ++p) s += partials[(size_t)p * stride + j];
+  out[j] += s;
+}
+
+// ------------------------------------------------------------------ bias gradient
+// partials[split][n] = sum over this split's rows of dy[row][n]
+__global__ void __launch_bounds__(256)
+colsum_kernel(const __nv_bfloat16* __restrict__ dy, float* __restrict__ partials, int rows, int n, long long ld, int rows_per_split) {
+  __shared__ float red[8][256];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col0 = blockIdx.x * 256 + lane * 8;
+  const int r0 = blockIdx.y * rows_per_split;
+  const int r1 = min(rows, r0 + rows_per_split);
+  float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (col0 < n) {
+    for (int r = r0 + warp; r < r1; r += 8) {
+      float f[8];
+      unpack8(*reinterpret_cast<const uint4*>(dy + (size_t)r * ld + col0), f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s[i] += f[i];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[warp][lane * 8 + i] = s[i];
+  __syncthreads();
+  const int j = threadIdx.x, col = blockIdx.x * 256 + j;
+  if (col < n) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w][j];
+    partials[(size_t)blockIdx.y * n + col] = t;
+  }
+}
+
+// ------------------------------------------------------------------ embedding
+// out[t,:] = wte[tok[t],:] + wpe[t % seq,:]
+__global__ void __launch_bounds__(WARPS * 32)
+embedding_fwd_kernel(const long long* __restrict__ tok, const __nv_bfloat16* __restrict__ wte,
+                     const __nv_bfloat16* __restrict__ wpe, __nv_bfloat16* __restrict__ out, int tokens, int seq, int h,
+                     int vocab, int* status) {
+  const int lane = threadIdx.x & 31;
+  const int nch = h >> 3;
+  for (int t = blockIdx.x * WARPS + (threadIdx.x >> 5); t < tokens; t += gridDim.x * WARPS) {
+    long long id = tok[t];
+    if (id < 0 || id >= vocab) { if (lane == 0) atomicCAS(status, 0, BB_ERR_INVALID_ARG); id = 0; }
+    const uint4* e = reinterpret_cast<const uint4*>(wte + (size_t)id * h);
+    const uint4* p = wpe ? reinterpret_cast<const uint4*>(wpe + (size_t)(t % seq) * h) : nullptr;
+    uint4* o = reinterpret_cast<uint4*>(out + (size_t)t * h);
+    for (int c = lane; c < nch; c += 32) {
+      float a[8], b[8];
+      unpack8(__ldg(e + c), a);
+      if (p) { unpack8(__ldg(p + c), b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[i] += b[i]; }
+      o[c] = pack8(a);
+    }
+  }
+}
+
+// dwte[tok[t],:] += dout[t,:] ; dwpe[t % seq,:] += dout[t,:]   (fp32 gradients, vector atomics)
+__global__ void __launch_bounds__(WARPS * 32)
+embedding_bwd_kernel(const long long* __restrict__ tok, const __nv_bfloat16* __restrict__ dout, float* __restrict__ dwte,
+                     float* __restrict__ dwpe, int tokens, int seq, int h, int vocab) {
+  const int lane = threadIdx.x & 31;
+  const int nch = h >> 3;
+  for (int t = blockIdx.x * WARPS + (threadIdx.x >> 5); t < tokens; t += gridDim.x * WARPS) {
+    long long id = tok[t];
+    if (id < 0 || id >= vocab) continue;
+    const uint4* d = reinterpret_cast<const uint4*>(dout + (size_t)t * h);
+    float4* ge = reinterpret_cast<float4*>(dwte + (size_t)id * h);
+    float4* gp = dwpe ? reinterpret_cast<float4*>(dwpe + (size_t)(t % seq) * h) : nullptr;
+    for (int c = lane; c < nch; c += 32) {
+      float f[8]; unpack8(d[c], f);
+      const float4 lo = make_float4(f[0], f[1], f[2], f[3]), hi = make_float4(f[4], f[5], f[6], f[7]);
+      atomicAdd(ge + 2 * c, lo); atomicAdd(ge + 2 * c + 1, hi);
+      if (gp) { atomicAdd(gp + 2 * c, lo); atomicAdd(gp + 2 * c + 1, hi); }
+    }
+  }
+}
+
+int row_grid(int rows) {
+  long long want = ((long long)rows + WARPS - 1) / WARPS;
+  long long cap = (long long)bb_num_sms() * CTAS_PER_SM;
+  return (int)(want < cap ? (want > 0 ? want : 1) : cap);
+}
+
+}  // namespace
+
+extern "C" int bb_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                                int rows, int h, float eps, void* stream) {
+  if (!x || !gamma || !beta || !y || !mean || !rstd || rows <= 0 || h <= 0 || (h & 7)) {
+    bb_set_last_error_msg("bb_layernorm_fwd: null pointer or hidden size not a multiple of 8");
+    return BB_ERR_INVALID_ARG;
+  }
+  layernorm_fwd_kernel<<<row_grid(rows), WARPS * 32, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, (const __nv_bfloat16*)beta, (__nv_bfloat16*)y, mean, rstd, rows, h, eps);
+  BB_CUDA_CHECK(cudaGetLastError());
+  return BB_OK;
+}
+
+namespace {
+int ln_bwd_warps(int h) {
+  int w = (int)((200 * 1024) / ((size_t)2 * h * sizeof(float)));
+  return w > WARPS ? WARPS : w;
+}
+int ln_bwd_grid(int rows, int h) {
+  const int w = ln_bwd_warps(h);
+  long long want = ((long long)rows + w - 1) / w;
+  long long cap = (long long)bb_num_sms() * (w * 2 * h * 4 > 100 * 1024 ? 1 : 2);
+  return (int)(want < cap ? (want > 0 ? want : 1) : cap);
+}
+}  // namespace
+
+extern "C" long long bb_layernorm_bwd_workspace_bytes(int rows, int h) {
+  if (rows <= 0 || h <= 0 || ln_bwd_warps(h) < 1) return 0;
+  return (long long)ln_bwd_grid(rows, h) * 2 * h * (long long)sizeof(float);
+}
+
+extern "C" int bb_layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
+                                const void* dres, void* dx, float* dgamma, float* dbeta, void* workspace,
+                                long long workspace_bytes, int rows, int h, void* stream) {
+  if (!dy || !x || !gamma || !mean || !rstd || !dx || !dgamma || !dbeta || !workspace || rows <= 0 || h <= 0 || (h & 7)) {
+    bb_set_last_error_msg("bb_layernorm_bwd: null pointer or hidden size not a multiple of 8");
+    return BB_ERR_INVALID_ARG;
+  }
+  const int warps = ln_bwd_warps(h);
+  if (warps < 1) { bb_set_last_error_msg("bb_layernorm_bwd: hidden size too large (max 25600)"); return BB_ERR_TOO_LARGE; }
+  if (workspace_bytes < bb_layernorm_bwd_workspace_bytes(rows, h)) {
+    bb_set_last_error_msg("bb_layernorm_bwd: workspace smaller than bb_layernorm_bwd_workspace_bytes()");
+    return BB_ERR_INVALID_ARG;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  static bool attr = false;
+  if (!attr) {
+    BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr = true;
+  }
+  const int grid = ln_bwd_grid(rows, h);
+  const size_t smem = (size_t)warps * 2 * h * sizeof(float);
+  float* ws = (float*)workspace;
+  layernorm_bwd_kernel<<<grid, warps * 32, smem, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                                      (const __nv_bfloat16*)gamma, mean, rstd, (const __nv_bfloat16*)dres,
+                                                      (__nv_bfloat16*)dx, ws, rows, h);
+  BB_CUDA_CHECK(cudaGetLastError());
+  reduce_partials_kernel<<<(h + 255) / 256, 256, 0, s>>>(ws, dgamma, grid, h, 2LL * h);
+  reduce_partials_kernel<<<(h + 255) / 256, 256, 0, s>>>(ws + h, dbeta, grid, h, 2LL * h);
+  BB_CUDA_CHECK(cudaGetLastError());
+  return BB_OK;
+}
+
+namespace {
+int colsum_splits(int rows) {
+  int s = (rows + 255) / 256;
+  return s < 1 ? 1 : (s > 64 ? 64 : s);
+}
+}  // namespace
+
+extern "C" long long bb_colsum_workspace_bytes(int rows, int n) {
+  if (rows <= 0 || n <= 0) return 0;
+  return (long long)colsum_splits(rows) * n * (long long)sizeof(float);
+}
+
+extern "C" int bb_colsum_accum(const void* dy, long long ld, float* out, void* workspace, long long workspace_bytes,
+                               int rows, int n, void* stream) {
+  if (!dy || !out || !workspace || rows <= 0 || n <= 0 || (n & 7) || (ld & 7)) {
+    bb_set_last_error_msg("bb_colsum_accum: null pointer, or n / ld not a multiple of 8");
+    return BB_ERR_INVALID_ARG;
+  }
+  if (workspace_bytes < bb_colsum_workspace_bytes(rows, n)) {
+    bb_set_last_error_msg("bb_colsum_accum: workspace smaller than bb_colsum_workspace_bytes()");
+    return BB_ERR_INVALID_ARG;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  const int splits = colsum_splits(rows);
+  const int rps = (rows + splits - 1) / splits;
+  dim3 grid((n + 255) / 256, splits);
+  colsum_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)dy, (float*)workspace, rows, n, ld, rps);
+  reduce_partials_kernel<<<(n + 255) / 256, 256, 0, s>>>((const float*)workspace, out, splits, n, (long long)n);
+  BB_CUDA_CHECK(cudaGetLastError());
+  return BB_OK;
+}
+
+extern "C" int bb_embedding_fwd(const long long* tokens, const void* wte, const void* wpe, void* out, int n_tokens,
+                                int seq, int h, int vocab, void* stream) {
+  if (!tokens || !wte || !out || n_tokens <= 0 || seq <= 0 || h <= 0 || (h & 7) || vocab <= 0) {
+    bb_set_last_error_msg("bb_embedding_fwd: null pointer or hidden size not a multiple of 8");
+    return BB_ERR_INVALID_ARG;
+  }
+  embedding_fwd_kernel<<<row_grid(n_tokens), WARPS * 32, 0, (cudaStream_t)stream>>>(
+      tokens, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, (__nv_bfloat16*)out, n_tokens, seq, h, vocab,
+      bb_device_status_word());
+  BB_CUDA_CHECK(cudaGetLastError());
+  return BB_OK;
+}
+
+extern "C" int bb_embedding_bwd(const long long* tokens, const void* dout, float* dwte, float* dwpe, int n_tokens, int seq,
+                                int h, int vocab, void* stream) {
+  if (!tokens || !dout || !dwte || n_tokens <= 0 || seq <= 0 || h <= 0 || (h & 7) || vocab <= 0) {
+    bb_set_last_error_msg("bb_embedding_bwd: null pointer or hidden size not a multiple of 8");
+    return BB_ERR_INVALID_ARG;
+  }
+  embedding_bwd_kernel<<<row_grid(n_tokens), WARPS * 32, 0, (cudaStream_t)stream>>>(
+      tokens, (const __nv_bfloat16*)dout, dwte, dwpe, n_tokens, seq, h, vocab);
+  BB_CUDA_CHECK(cudaGetLastError());
+  return BB_OK;
+}

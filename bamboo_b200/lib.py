@@ -100,3 +100,127 @@ def gemm(a, b, out, *, a_mn=False, b_mn=False, epilogue=EPI_STORE, bias=None, ou
                  ld_aux=aux.stride(0) if aux is not None else 0, tile_n=tile_n, max_ctas=max_ctas)
     check(load().bb_gemm_bf16(ctypes.byref(d), _stream()), "bb_gemm_bf16")
     return out
+
+
+# ---------------------------------------------------------------------------- helpers
+_LL = ctypes.c_longlong
+_F = ctypes.c_float
+_I = ctypes.c_int
+_workspaces = {}
+
+
+def workspace(nbytes, tag="default"):
+    """A per-device scratch buffer that only ever grows (allocated through torch so it is
+    accounted in the caching allocator; the native side never allocates)."""
+    import torch
+    dev = torch.cuda.current_device()
+    key = (dev, tag)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=f"cuda:{dev}")
+        _workspaces[key] = buf
+    return buf
+
+
+def layernorm_fwd(x, gamma, beta, y, mean, rstd, eps=1e-5):
+    rows, h = x.numel() // x.shape[-1], x.shape[-1]
+    check(load().bb_layernorm_fwd(_ptr(x), _ptr(gamma), _ptr(beta), _ptr(y), _ptr(mean), _ptr(rstd),
+                                  _I(rows), _I(h), _F(eps), _stream()), "bb_layernorm_fwd")
+    return y
+
+
+def layernorm_bwd(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta):
+    rows, h = x.numel() // x.shape[-1], x.shape[-1]
+    lib = load()
+    lib.bb_layernorm_bwd_workspace_bytes.restype = _LL
+    need = lib.bb_layernorm_bwd_workspace_bytes(_I(rows), _I(h))
+    ws = workspace(need, "rowwise")
+    check(lib.bb_layernorm_bwd(_ptr(dy), _ptr(x), _ptr(gamma), _ptr(mean), _ptr(rstd), _ptr(dres), _ptr(dx),
+                               _ptr(dgamma), _ptr(dbeta), _ptr(ws), _LL(ws.numel()), _I(rows), _I(h), _stream()),
+          "bb_layernorm_bwd")
+    return dx
+
+
+def colsum_accum(dy, out):
+    """out(fp32)[n] += dy(bf16)[rows, n].sum(0)"""
+    rows, n = dy.shape
+    lib = load()
+    lib.bb_colsum_workspace_bytes.restype = _LL
+    need = lib.bb_colsum_workspace_bytes(_I(rows), _I(n))
+    ws = workspace(need, "rowwise")
+    check(lib.bb_colsum_accum(_ptr(dy), _LL(dy.stride(0)), _ptr(out), _ptr(ws), _LL(ws.numel()), _I(rows), _I(n),
+                              _stream()), "bb_colsum_accum")
+    return out
+
+
+def embedding_fwd(tokens, wte, wpe, out, seq):
+    check(load().bb_embedding_fwd(_ptr(tokens), _ptr(wte), _ptr(wpe), _ptr(out), _I(tokens.numel()), _I(seq),
+                                  _I(wte.shape[1]), _I(wte.shape[0]), _stream()), "bb_embedding_fwd")
+    return out
+
+
+def embedding_bwd(tokens, dout, dwte, dwpe, seq):
+    check(load().bb_embedding_bwd(_ptr(tokens), _ptr(dout), _ptr(dwte), _ptr(dwpe), _I(tokens.numel()), _I(seq),
+                                  _I(dwte.shape[1]), _I(dwte.shape[0]), _stream()), "bb_embedding_bwd")
+
+
+def attention_fwd(qkv, out, lse, B, H, S, D, causal, scale=None):
+    """qkv: [B*S, 3*H*D] packed projection output; out: [B*S, H*D]; lse: [B,H,S] fp32."""
+    hd = H * D
+    esz = qkv.element_size()
+    base = qkv.data_ptr()
+    scale = (1.0 / D ** 0.5) if scale is None else scale
+    check(load().bb_attention_fwd(ctypes.c_void_p(base), ctypes.c_void_p(base + hd * esz),
+                                  ctypes.c_void_p(base + 2 * hd * esz), _ptr(out), _ptr(lse), _I(B), _I(H), _I(S),
+                                  _I(D), _LL(qkv.stride(0)), _LL(out.stride(0)), _I(int(causal)), _F(scale),
+                                  _stream()), "bb_attention_fwd")
+    return out
+
+
+def attention_bwd(qkv, out, dout, lse, dqkv, B, H, S, D, causal, scale=None):
+    hd = H * D
+    esz = qkv.element_size()
+    base, dbase = qkv.data_ptr(), dqkv.data_ptr()
+    scale = (1.0 / D ** 0.5) if scale is None else scale
+    lib = load()
+    lib.bb_attention_bwd_workspace_bytes.restype = _LL
+    need = lib.bb_attention_bwd_workspace_bytes(_I(B), _I(H), _I(S))
+    ws = workspace(need, "attention")
+    check(lib.bb_attention_bwd(ctypes.c_void_p(base), ctypes.c_void_p(base + hd * esz),
+                               ctypes.c_void_p(base + 2 * hd * esz), _ptr(out), _ptr(dout), _ptr(lse),
+                               ctypes.c_void_p(dbase), ctypes.c_void_p(dbase + hd * esz),
+                               ctypes.c_void_p(dbase + 2 * hd * esz), _ptr(ws), _LL(ws.numel()), _I(B), _I(H), _I(S),
+                               _I(D), _LL(qkv.stride(0)), _LL(out.stride(0)), _LL(dqkv.stride(0)), _I(int(causal)),
+                               _F(scale), _stream()), "bb_attention_bwd")
+    return dqkv
+
+
+def cross_entropy_fwd(logits, targets, lse, row_loss, loss_out, vocab, ignore_index=-100):
+    rows = logits.shape[0]
+    check(load().bb_cross_entropy_fwd(_ptr(logits), _LL(logits.stride(0)), _ptr(targets), _ptr(lse), _ptr(row_loss),
+                                      _ptr(loss_out), _I(rows), _I(vocab), _LL(ignore_index), _stream()),
+          "bb_cross_entropy_fwd")
+    return loss_out
+
+
+def cross_entropy_bwd(logits, targets, lse, loss_out, dlogits, vocab, grad_scale=1.0, grad_scale_dev=None,
+                      ignore_index=-100):
+    rows, cols = logits.shape
+    check(load().bb_cross_entropy_bwd(_ptr(logits), _LL(logits.stride(0)), _ptr(targets), _ptr(lse), _ptr(loss_out),
+                                      _ptr(grad_scale_dev), _F(grad_scale), _ptr(dlogits), _LL(dlogits.stride(0)),
+                                      _I(rows), _I(vocab), _I(cols), _LL(ignore_index), _stream()),
+          "bb_cross_entropy_bwd")
+    return dlogits
+
+
+def adam_step(master, grad, exp_avg, exp_avg_sq, param_lp, *, lr, beta1=0.9, beta2=0.999, eps=1e-8, step,
+              adam_w_mode=True, bias_correction=True, weight_decay=0.0, grad_scale=1.0, zero_grad=True):
+    check(load().bb_adam_step(_ptr(master), _ptr(grad), _ptr(exp_avg), _ptr(exp_avg_sq), _ptr(param_lp),
+                              _LL(master.numel()), _F(lr), _F(beta1), _F(beta2), _F(eps), _I(step),
+                              _I(int(adam_w_mode)), _I(int(bias_correction)), _F(weight_decay), _F(grad_scale),
+                              _I(int(zero_grad)), _stream()), "bb_adam_step")
+
+
+def cast_f32_to_bf16(src, dst):
+    check(load().bb_cast_f32_to_bf16(_ptr(src), _ptr(dst), _LL(src.numel()), _stream()), "bb_cast_f32_to_bf16")
+    return dst

@@ -70,6 +70,81 @@ typedef struct bb_gemm_desc {
  * bias / activation / residual elementwise kernels. */
 int bb_gemm_bf16(const bb_gemm_desc* desc, void* stream);
 
+/* ---- LayerNorm -------------------------------------------------------------------- */
+/* y = (x - mean) * rstd * gamma + beta over rows of h bf16 values; mean/rstd (fp32, per
+ * row) are saved for the backward pass.  h % 8 == 0.
+ * Replaces: the LayerNorm module of the reference transformer blocks, a chain of eager
+ * mean/std/sub/div/mul/add kernels (EX/pipeline_parallelism/gpt2.py:20-32). */
+int bb_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                     int rows, int h, float eps, void* stream);
+/* dx = LN'(dy) (+ dres, the gradient arriving over the residual branch); dgamma/dbeta
+ * (fp32) are accumulated (+=).  `workspace` holds per-CTA partial sums
+ * (bb_layernorm_bwd_workspace_bytes) that a second kernel reduces in a fixed order.
+ * Replaces: autograd's backward of the same module (DS/runtime/pipe/engine.py:1680-1727). */
+long long bb_layernorm_bwd_workspace_bytes(int rows, int h);
+int bb_layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
+                     const void* dres, void* dx, float* dgamma, float* dbeta, void* workspace,
+                     long long workspace_bytes, int rows, int h, void* stream);
+
+/* out[n] += sum_rows dy[row, n] : bias gradient of a linear layer (fp32 accumulate).
+ * Replaces: the bias-gradient reduction autograd runs for nn.Linear
+ * (EX/pipeline_parallelism/gpt2.py:52-64 via DS/runtime/pipe/engine.py:1680-1727). */
+long long bb_colsum_workspace_bytes(int rows, int n);
+int bb_colsum_accum(const void* dy, long long ld, float* out, void* workspace, long long workspace_bytes,
+                    int rows, int n, void* stream);
+
+/* ---- embedding -------------------------------------------------------------------- */
+/* out[t,:] = wte[tokens[t],:] + wpe[t % seq,:] (wpe may be NULL); gradient scatter into
+ * fp32 dwte/dwpe.  The reference examples have no embedding (they train on random float
+ * activations, EX/pipeline_parallelism/gpt2.py:283-295); the benchmark configurations add
+ * token and learned position embeddings in front of stage 0, loaded by
+ * _exec_load_micro_batch (DS/runtime/pipe/engine.py:1729-1779). */
+int bb_embedding_fwd(const long long* tokens, const void* wte, const void* wpe, void* out, int n_tokens,
+                     int seq, int h, int vocab, void* stream);
+int bb_embedding_bwd(const long long* tokens, const void* dout, float* dwte, float* dwpe, int n_tokens, int seq,
+                     int h, int vocab, void* stream);
+
+/* ---- attention -------------------------------------------------------------------- */
+/* softmax(scale * Q K^T [+ causal mask]) V without materialising the scores; q/k/v are
+ * addressed as base + token*stride + head*D so a packed [tokens, 3*H*D] projection is
+ * consumed in place.  lse: [B,H,S] fp32.  D in {64, 128}.
+ * Replaces: the matmul / softmax / matmul chain of the reference attention
+ * (EX/pipeline_parallelism/gpt2.py:66-75) and its autograd backward. */
+int bb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H, int S, int D,
+                     long long stride_qkv, long long stride_o, int causal, float scale, void* stream);
+long long bb_attention_bwd_workspace_bytes(int B, int H, int S);
+int bb_attention_bwd(const void* q, const void* k, const void* v, const void* out, const void* d_out, const float* lse,
+                     void* dq, void* dk, void* dv, void* workspace, long long workspace_bytes, int B, int H, int S,
+                     int D, long long stride_qkv, long long stride_o, long long stride_dqkv, int causal, float scale,
+                     void* stream);
+
+/* ---- loss ------------------------------------------------------------------------- */
+/* Token-level cross entropy over bf16 logits [rows, ld] with `vocab` valid columns:
+ * lse/row_loss per row, loss_out[0] = mean over non-ignored rows, loss_out[1] = their count.
+ * Replaces: loss_fn(outputs, labels) on the last stage (DS/runtime/pipe/engine.py:1650-1663). */
+int bb_cross_entropy_fwd(const void* logits, long long ld, const long long* targets, float* lse, float* row_loss,
+                         float* loss_out, int rows, int vocab, long long ignore_index, void* stream);
+/* dlogits = (softmax - onehot) * grad_scale * (*grad_scale_dev, if given) / count, zero in
+ * the padded columns vocab..cols; may run in place.
+ * Replaces: the loss part of DeepSpeedEngine.backward (DS/runtime/engine.py:1416-1478). */
+int bb_cross_entropy_bwd(const void* logits, long long ld, const long long* targets, const float* lse,
+                         const float* loss_out, const float* grad_scale_dev, float grad_scale, void* dlogits,
+                         long long ldd, int rows, int vocab, int cols, long long ignore_index, void* stream);
+
+/* ---- optimizer -------------------------------------------------------------------- */
+/* One Adam / AdamW step over a flat parameter arena: fp32 master weights, gradient and
+ * moments; refreshes the bf16 working copy (may be NULL) and optionally clears the
+ * gradient in the same pass.  grad_scale multiplies the gradient first (1/dp averaging).
+ * Replaces: FusedAdam.step (DS/ops/adam/fused_adam.py:85-182) ->
+ * multi_tensor_adam (CS/adam/multi_tensor_adam.cu:28-163) and zero_grad
+ * (DS/runtime/engine.py:1526-1573). */
+int bb_adam_step(float* master, float* grad, float* exp_avg, float* exp_avg_sq, void* param_bf16, long long n,
+                 float lr, float beta1, float beta2, float eps, int step, int adam_w_mode, int bias_correction,
+                 float weight_decay, float grad_scale, int zero_grad, void* stream);
+/* dst(bf16) = src(fp32); used when a shadow stage is promoted or refreshed
+ * (PipelineModule.build_layers(stage, buffer), DS/runtime/pipe/module.py:262-332). */
+int bb_cast_f32_to_bf16(const float* src, void* dst, long long n, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
