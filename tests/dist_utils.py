@@ -1,0 +1,48 @@
+"""Run a function on N CPU ranks (gloo) as child processes and collect their results."""
+import os
+import tempfile
+import traceback
+
+import torch
+import torch.multiprocessing as mp
+
+
+def _entry(rank, world, store_path, fn, args, queue):
+    try:
+        os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), BAMBOO_QUIET="1",
+                          MASTER_ADDR="127.0.0.1")
+        torch.set_num_threads(1)
+        import torch.distributed as dist
+        store = dist.FileStore(store_path, world)
+        dist.init_process_group("gloo", store=dist.PrefixStore("pg", store), rank=rank, world_size=world)
+        out = fn(rank, world, dist.PrefixStore("engine", store), *args)
+        queue.put((rank, "ok", out))
+    except SystemExit as e:
+        queue.put((rank, "exit", e.code))
+    except BaseException:
+        queue.put((rank, "error", traceback.format_exc()))
+
+
+def run_ranks(fn, world, *args, timeout=240):
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "store")
+        procs = [ctx.Process(target=_entry, args=(r, world, path, fn, args, queue)) for r in range(world)]
+        for p in procs:
+            p.start()
+        results = {}
+        try:
+            for _ in range(world):
+                rank, status, payload = queue.get(timeout=timeout)
+                results[rank] = (status, payload)
+        finally:
+            for p in procs:
+                p.join(timeout=20)
+                if p.is_alive():
+                    p.kill()
+    errors = [f"rank {rank} failed:\n{payload}" for rank, (status, payload) in sorted(results.items())
+              if status == "error"]
+    if errors:
+        raise AssertionError("\n".join(errors))
+    return results
