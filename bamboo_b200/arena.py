@@ -71,6 +71,11 @@ class ParamArena:
         for p, off in zip(self.params, self.offsets):
             p.main_grad = self.grad[off:off + p.numel()].view(p.shape)
 
+    def named_slices(self):
+        """(index, offset, numel) of every parameter in the flat buffers."""
+        for i, (p, off) in enumerate(zip(self.params, self.offsets)):
+            yield i, off, p.numel()
+
     def fold_autograd_grads(self):
         """Generic torch layers leave their gradient in ``param.grad``; accumulate it into
         the fp32 arena (the sm_100a layers write there directly and leave ``grad`` None)."""

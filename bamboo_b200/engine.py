@@ -783,6 +783,8 @@ class PipelineEngine:
             torch.cuda.current_stream().wait_event(self._rc_event)
             self._rc_event = None
         scales = getattr(self, "_reduce_scale", {})
+        if getattr(self, "capture_grads", False):
+            self.last_grads = {sid: self.arenas[sid].grad.clone() * scales.get(sid, 1.0) for sid in self.stage_ids}
         for sid in self.stage_ids:
             a = self._adam
             self.arenas[sid].adam_step(lr=a["lr"], beta1=a["beta1"], beta2=a["beta2"], eps=a["eps"],

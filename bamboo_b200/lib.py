@@ -34,6 +34,10 @@ class GemmDesc(ctypes.Structure):
 
 _lib = None
 _lock = threading.Lock()
+# number of kernels launched through this binding (benchmarks report it)
+LAUNCHES = 0
+# optional hook called as hook(name, flops, launch_fn) around GEMM launches (profiling only)
+gemm_hook = None
 
 
 def load():
@@ -98,6 +102,12 @@ def gemm(a, b, out, *, a_mn=False, b_mn=False, epilogue=EPI_STORE, bias=None, ou
                  B=_ptr(b), ldb=b.stride(0), b_mn_major=int(b_mn), D=_ptr(out), ldd=out.stride(0),
                  epilogue=epilogue, bias=_ptr(bias), D2=_ptr(out2), aux=_ptr(aux),
                  ld_aux=aux.stride(0) if aux is not None else 0, tile_n=tile_n, max_ctas=max_ctas)
+    global LAUNCHES
+    LAUNCHES += 1
+    if gemm_hook is not None:
+        gemm_hook((M, N, K, int(a_mn), int(b_mn), epilogue), 2.0 * M * N * K,
+                  lambda: check(load().bb_gemm_bf16(ctypes.byref(d), _stream()), "bb_gemm_bf16"))
+        return out
     check(load().bb_gemm_bf16(ctypes.byref(d), _stream()), "bb_gemm_bf16")
     return out
 
@@ -123,6 +133,8 @@ def workspace(nbytes, tag="default"):
 
 
 def layernorm_fwd(x, gamma, beta, y, mean, rstd, eps=1e-5):
+    global LAUNCHES
+    LAUNCHES += 1
     rows, h = x.numel() // x.shape[-1], x.shape[-1]
     check(load().bb_layernorm_fwd(_ptr(x), _ptr(gamma), _ptr(beta), _ptr(y), _ptr(mean), _ptr(rstd),
                                   _I(rows), _I(h), _F(eps), _stream()), "bb_layernorm_fwd")
@@ -130,6 +142,8 @@ def layernorm_fwd(x, gamma, beta, y, mean, rstd, eps=1e-5):
 
 
 def layernorm_bwd(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta):
+    global LAUNCHES
+    LAUNCHES += 3
     rows, h = x.numel() // x.shape[-1], x.shape[-1]
     lib = load()
     lib.bb_layernorm_bwd_workspace_bytes.restype = _LL
@@ -143,6 +157,8 @@ def layernorm_bwd(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta):
 
 def colsum_accum(dy, out):
     """out(fp32)[n] += dy(bf16)[rows, n].sum(0)"""
+    global LAUNCHES
+    LAUNCHES += 2
     rows, n = dy.shape
     lib = load()
     lib.bb_colsum_workspace_bytes.restype = _LL
@@ -154,18 +170,24 @@ def colsum_accum(dy, out):
 
 
 def embedding_fwd(tokens, wte, wpe, out, seq):
+    global LAUNCHES
+    LAUNCHES += 1
     check(load().bb_embedding_fwd(_ptr(tokens), _ptr(wte), _ptr(wpe), _ptr(out), _I(tokens.numel()), _I(seq),
                                   _I(wte.shape[1]), _I(wte.shape[0]), _stream()), "bb_embedding_fwd")
     return out
 
 
 def embedding_bwd(tokens, dout, dwte, dwpe, seq):
+    global LAUNCHES
+    LAUNCHES += 1
     check(load().bb_embedding_bwd(_ptr(tokens), _ptr(dout), _ptr(dwte), _ptr(dwpe), _I(tokens.numel()), _I(seq),
                                   _I(dwte.shape[1]), _I(dwte.shape[0]), _stream()), "bb_embedding_bwd")
 
 
 def attention_fwd(qkv, out, lse, B, H, S, D, causal, scale=None):
     """qkv: [B*S, 3*H*D] packed projection output; out: [B*S, H*D]; lse: [B,H,S] fp32."""
+    global LAUNCHES
+    LAUNCHES += 1
     hd = H * D
     esz = qkv.element_size()
     base = qkv.data_ptr()
@@ -178,6 +200,8 @@ def attention_fwd(qkv, out, lse, B, H, S, D, causal, scale=None):
 
 
 def attention_bwd(qkv, out, dout, lse, dqkv, B, H, S, D, causal, scale=None):
+    global LAUNCHES
+    LAUNCHES += 3
     hd = H * D
     esz = qkv.element_size()
     base, dbase = qkv.data_ptr(), dqkv.data_ptr()
@@ -196,6 +220,8 @@ def attention_bwd(qkv, out, dout, lse, dqkv, B, H, S, D, causal, scale=None):
 
 
 def cross_entropy_fwd(logits, targets, lse, row_loss, loss_out, vocab, ignore_index=-100):
+    global LAUNCHES
+    LAUNCHES += 2
     rows = logits.shape[0]
     check(load().bb_cross_entropy_fwd(_ptr(logits), _LL(logits.stride(0)), _ptr(targets), _ptr(lse), _ptr(row_loss),
                                       _ptr(loss_out), _I(rows), _I(vocab), _LL(ignore_index), _stream()),
@@ -205,6 +231,8 @@ def cross_entropy_fwd(logits, targets, lse, row_loss, loss_out, vocab, ignore_in
 
 def cross_entropy_bwd(logits, targets, lse, loss_out, dlogits, vocab, grad_scale=1.0, grad_scale_dev=None,
                       ignore_index=-100):
+    global LAUNCHES
+    LAUNCHES += 1
     rows, cols = logits.shape
     check(load().bb_cross_entropy_bwd(_ptr(logits), _LL(logits.stride(0)), _ptr(targets), _ptr(lse), _ptr(loss_out),
                                       _ptr(grad_scale_dev), _F(grad_scale), _ptr(dlogits), _LL(dlogits.stride(0)),
@@ -215,6 +243,8 @@ def cross_entropy_bwd(logits, targets, lse, loss_out, dlogits, vocab, grad_scale
 
 def adam_step(master, grad, exp_avg, exp_avg_sq, param_lp, *, lr, beta1=0.9, beta2=0.999, eps=1e-8, step,
               adam_w_mode=True, bias_correction=True, weight_decay=0.0, grad_scale=1.0, zero_grad=True):
+    global LAUNCHES
+    LAUNCHES += 1
     check(load().bb_adam_step(_ptr(master), _ptr(grad), _ptr(exp_avg), _ptr(exp_avg_sq), _ptr(param_lp),
                               _LL(master.numel()), _F(lr), _F(beta1), _F(beta2), _F(eps), _I(step),
                               _I(int(adam_w_mode)), _I(int(bias_correction)), _F(weight_decay), _F(grad_scale),
@@ -222,5 +252,7 @@ def adam_step(master, grad, exp_avg, exp_avg_sq, param_lp, *, lr, beta1=0.9, bet
 
 
 def cast_f32_to_bf16(src, dst):
+    global LAUNCHES
+    LAUNCHES += 1
     check(load().bb_cast_f32_to_bf16(_ptr(src), _ptr(dst), _LL(src.numel()), _stream()), "bb_cast_f32_to_bf16")
     return dst

@@ -1,0 +1,235 @@
+"""Parity of every sm_100a kernel, called through the C ABI, with an fp32 PyTorch statement
+of the same operation on the same seeded inputs.  Tolerance: bf16 outputs within 2e-2 of
+the reference magnitude; fp32 accumulations within 1e-3."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def L():
+    from bamboo_b200 import lib
+    lib.load()
+    return lib
+
+
+def close(got, want, tol=2e-2):
+    err = (got.float() - want.float()).abs().max().item()
+    scale = want.float().abs().max().item()
+    assert err <= tol * scale + 1e-3, (err, scale)
+
+
+def gelu(x):
+    return F.gelu(x, approximate="tanh")
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_gemm_operand_layouts(L, a_mn, b_mn, tile_n):
+    torch.manual_seed(0)
+    M, N, K = 384, 512, 320
+    A = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    B = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    a = A.t().contiguous() if a_mn else A
+    b = B.t().contiguous() if b_mn else B
+    out = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    L.gemm(a, b, out, a_mn=a_mn, b_mn=b_mn, M=M, N=N, K=K, tile_n=tile_n)
+    close(out, A.float() @ B.float().t())
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 64), (200, 136, 72), (130, 264, 200), (8, 8, 8), (1024, 1024, 1000)])
+def test_gemm_ragged_shapes(L, shape):
+    torch.manual_seed(1)
+    M, N, K = shape
+    A = torch.randn(M, K, device="cuda").bfloat16()
+    B = torch.randn(N, K, device="cuda").bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    out = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    L.gemm(A, B, out, epilogue=L.EPI_BIAS, bias=bias)
+    close(out, A.float() @ B.float().t() + bias.float())
+
+
+def test_gemm_epilogues(L):
+    torch.manual_seed(2)
+    M, N, K = 384, 768, 320
+    A = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    B = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    aux = torch.randn(M, N, device="cuda").bfloat16()
+    ref = A.float() @ B.float().t()
+    out = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    out2 = torch.zeros_like(out)
+    L.gemm(A, B, out, epilogue=L.EPI_BIAS_GELU, bias=bias, out2=out2)
+    close(out2, ref + bias.float())
+    close(out, gelu((ref + bias.float()).bfloat16().float()))
+    L.gemm(A, B, out, epilogue=L.EPI_BIAS_RESIDUAL, bias=bias, aux=aux)
+    close(out, ref + bias.float() + aux.float())
+    x = aux.float().requires_grad_(True)
+    gelu(x).sum().backward()
+    L.gemm(A, B, out, epilogue=L.EPI_MUL_DGELU, aux=aux)
+    close(out, ref * x.grad)
+    acc = torch.randn(M, N, device="cuda")
+    want = acc + ref
+    L.gemm(A, B, acc, epilogue=L.EPI_ACCUM_F32)
+    close(acc, want, 1e-3)
+    L.gemm(A, B, acc, epilogue=L.EPI_STORE_F32)
+    close(acc, ref, 1e-3)
+
+
+def test_gemm_is_linear_and_deterministic_at_full_size(L):
+    """GPT-2-medium MLP shape: two runs are bit-identical and (A1+A2)B = A1 B + A2 B in fp32 output."""
+    torch.manual_seed(3)
+    M, N, K = 8192, 4096, 1024
+    A1 = torch.randint(-4, 5, (M, K), device="cuda").bfloat16()
+    A2 = torch.randint(-4, 5, (M, K), device="cuda").bfloat16()
+    B = torch.randint(-4, 5, (N, K), device="cuda").bfloat16()
+    o1, o2, o12, again = (torch.empty(M, N, device="cuda") for _ in range(4))
+    L.gemm(A1, B, o1, epilogue=L.EPI_STORE_F32)
+    L.gemm(A2, B, o2, epilogue=L.EPI_STORE_F32)
+    L.gemm((A1 + A2), B, o12, epilogue=L.EPI_STORE_F32)
+    L.gemm(A1, B, again, epilogue=L.EPI_STORE_F32)
+    assert torch.equal(o1, again)
+    assert torch.equal(o12, o1 + o2)          # small integers: exact in bf16 x bf16 -> fp32
+    assert torch.equal(o1[:256], (A1[:256].float() @ B.float().t()))
+
+
+def test_gemm_rejects_bad_arguments(L):
+    A = torch.zeros(16, 12, device="cuda", dtype=torch.bfloat16)   # leading dimension not a multiple of 8
+    B = torch.zeros(16, 12, device="cuda", dtype=torch.bfloat16)
+    out = torch.zeros(16, 16, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(L.BambooNativeError):
+        L.gemm(A, B, out)
+    with pytest.raises(L.BambooNativeError):
+        L.gemm(out, out, out, epilogue=L.EPI_BIAS)                 # bias missing
+
+
+@pytest.mark.parametrize("rows,h", [(512, 256), (8192, 1024), (300, 768), (1000, 4096)])
+def test_layernorm(L, rows, h):
+    torch.manual_seed(4)
+    x = torch.randn(rows, h, device="cuda").bfloat16()
+    g = (1 + 0.1 * torch.randn(h, device="cuda")).bfloat16()
+    b = (0.1 * torch.randn(h, device="cuda")).bfloat16()
+    y = torch.empty_like(x)
+    mean, rstd = torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda")
+    L.layernorm_fwd(x, g, b, y, mean, rstd, 1e-5)
+    xf, gf, bf = x.float().requires_grad_(True), g.float().requires_grad_(True), b.float().requires_grad_(True)
+    yr = F.layer_norm(xf, (h,), gf, bf, 1e-5)
+    close(y, yr)
+    dy, dres = torch.randn(rows, h, device="cuda").bfloat16(), torch.randn(rows, h, device="cuda").bfloat16()
+    yr.backward(dy.float())
+    dx = torch.empty_like(x)
+    dg, db = torch.ones(h, device="cuda"), torch.ones(h, device="cuda")      # accumulate on top of 1
+    L.layernorm_bwd(dy, x, g, mean, rstd, dres, dx, dg, db)
+    close(dx, xf.grad + dres.float())
+    close(dg - 1, gf.grad)
+    close(db - 1, bf.grad)
+
+
+@pytest.mark.parametrize("rows,n", [(8192, 4096), (100, 264), (513, 1024), (1, 8)])
+def test_colsum(L, rows, n):
+    torch.manual_seed(5)
+    dy = torch.randn(rows, n, device="cuda").bfloat16()
+    out = torch.ones(n, device="cuda")
+    L.colsum_accum(dy, out)
+    close(out - 1, dy.float().sum(0), 1e-3)
+
+
+def test_embedding(L):
+    torch.manual_seed(6)
+    V, h, B, S = 1024, 256, 4, 128
+    tok = torch.randint(0, V, (B, S), device="cuda")
+    tok[0, :8] = 7                                                   # collisions in the scatter
+    wte, wpe = torch.randn(V, h, device="cuda").bfloat16(), torch.randn(S, h, device="cuda").bfloat16()
+    out = torch.empty(B * S, h, device="cuda", dtype=torch.bfloat16)
+    L.embedding_fwd(tok, wte, wpe, out, S)
+    close(out, wte[tok.view(-1)].float() + wpe.float().repeat(B, 1))
+    dout = torch.randn(B * S, h, device="cuda").bfloat16()
+    dwte, dwpe = torch.zeros(V, h, device="cuda"), torch.zeros(S, h, device="cuda")
+    L.embedding_bwd(tok, dout, dwte, dwpe, S)
+    close(dwte, torch.zeros(V, h, device="cuda").index_add_(0, tok.view(-1), dout.float()), 1e-3)
+    close(dwpe, dout.float().view(B, S, h).sum(0), 1e-3)
+
+
+@pytest.mark.parametrize("rows,V,Vp", [(512, 1024, 1024), (1024, 50257, 50304), (100, 30522, 30528), (4, 8, 8)])
+def test_cross_entropy(L, rows, V, Vp):
+    torch.manual_seed(7)
+    logits = torch.zeros(rows, Vp, device="cuda", dtype=torch.bfloat16)
+    logits[:, :V] = (3 * torch.randn(rows, V, device="cuda")).bfloat16()
+    tgt = torch.randint(0, V, (rows,), device="cuda")
+    tgt[::7] = -100                                                  # ignored positions
+    lse, rl, lo = torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda"), torch.empty(2, device="cuda")
+    L.cross_entropy_fwd(logits, tgt, lse, rl, lo, V)
+    lf = logits[:, :V].float().requires_grad_(True)
+    ref = F.cross_entropy(lf, tgt, ignore_index=-100)
+    assert lo[0].item() == pytest.approx(ref.item(), rel=1e-4)
+    assert lo[1].item() == (tgt != -100).sum().item()
+    (ref * 0.25).backward()
+    L.cross_entropy_bwd(logits, tgt, lse, lo, logits, V, grad_scale=0.25)       # in place
+    close(logits[:, :V], lf.grad)
+    assert logits[:, V:].abs().max().item() == 0 if Vp > V else True
+
+
+def test_adam_matches_torch(L):
+    torch.manual_seed(8)
+    n = 1 << 20
+    p, m, v = torch.randn(n, device="cuda"), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    g, lp = torch.empty(n, device="cuda"), torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    pr = p.clone().requires_grad_(True)
+    opt = torch.optim.Adam([pr], lr=1e-3)
+    for step in (1, 2, 3):
+        gg = torch.randn(n, device="cuda")
+        g.copy_(gg)
+        pr.grad = gg.clone()
+        opt.step()
+        L.adam_step(p, g, m, v, lp, lr=1e-3, step=step)
+    close(p, pr.detach(), 1e-5)
+    close(lp, pr.detach(), 1e-2)
+    assert g.abs().max().item() == 0
+    close(m, opt.state[pr]["exp_avg"], 1e-5)
+    close(v, opt.state[pr]["exp_avg_sq"], 1e-5)
+
+
+def _attn_ref(qkv, B, H, S, D, causal):
+    q, k, v = qkv.float().view(B, S, 3, H, D).permute(2, 0, 3, 1, 4)
+    return F.scaled_dot_product_attention(q, k, v, is_causal=causal).permute(0, 2, 1, 3).reshape(B * S, H * D)
+
+
+@pytest.mark.parametrize("B,H,S,D,causal", [(2, 4, 128, 64, True), (2, 3, 256, 64, False), (1, 2, 1024, 64, True),
+                                            (1, 2, 200, 64, True), (1, 2, 72, 64, False), (1, 2, 256, 128, True),
+                                            (2, 2, 320, 128, False)])
+def test_attention(L, B, H, S, D, causal):
+    torch.manual_seed(9)
+    qkv = torch.randn(B * S, 3 * H * D, device="cuda").bfloat16()
+    out = torch.empty(B * S, H * D, device="cuda", dtype=torch.bfloat16)
+    lse = torch.empty(B, H, S, device="cuda")
+    L.attention_fwd(qkv, out, lse, B, H, S, D, causal)
+    qf = qkv.float().requires_grad_(True)
+    ref = _attn_ref(qf, B, H, S, D, causal)
+    close(out, ref)
+    do = torch.randn_like(out)
+    ref.backward(do.float())
+    dqkv = torch.empty_like(qkv)
+    L.attention_bwd(qkv, out, do, lse, dqkv, B, H, S, D, causal)
+    close(dqkv, qf.grad)
+
+
+def test_attention_rows_sum_to_one_at_full_size(L):
+    """GPT-2-medium attention shape: with V = 1 every output element must be 1."""
+    B, H, S, D = 8, 16, 1024, 64
+    torch.manual_seed(10)
+    qkv = torch.randn(B * S, 3 * H * D, device="cuda").bfloat16()
+    qkv[:, 2 * H * D:] = 1
+    out = torch.empty(B * S, H * D, device="cuda", dtype=torch.bfloat16)
+    lse = torch.empty(B, H, S, device="cuda")
+    L.attention_fwd(qkv, out, lse, B, H, S, D, True)
+    assert (out.float() - 1).abs().max().item() < 1e-2
+    assert torch.isfinite(lse).all()
+
+
+def test_status_word_is_clean(L):
+    torch.cuda.synchronize()
+    assert L.read_status() == 0

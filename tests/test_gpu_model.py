@@ -1,0 +1,98 @@
+"""Per-step loss and gradient parity of the CUDA training step with the fp32 oracle on the
+same seeded weights and tokens (bf16 tolerance 2e-2 relative), through the public API
+(PipelineModule / deepspeed.initialize / train_batch)."""
+import os
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from oracle import gpt_ref  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+
+
+def build_engine(cfg, mb, gas, lr, seed=0):
+    from bamboo_b200 import api, models
+    from bamboo_b200.module import PipelineModule
+    os.environ["BAMBOO_QUIET"] = "1"
+    tc = models.TransformerConfig(layers=cfg.layers, hidden=cfg.hidden, heads=cfg.heads, ffn=cfg.ffn, seq=cfg.seq,
+                                  vocab=cfg.vocab, causal=cfg.causal)
+    model = PipelineModule(models.transformer_layer_specs(tc, seed), num_stages=1, loss_fn=models.transformer_loss(tc),
+                           partition_method="uniform")
+    config = {"train_micro_batch_size_per_gpu": mb, "gradient_accumulation_steps": gas, "bf16": {"enabled": True},
+              "optimizer": {"type": "Adam", "params": {"lr": lr}}}
+    engine, *_ = api.initialize(model=model, config=config)
+    engine.capture_grads = True
+    return engine
+
+
+def oracle_names(cfg):
+    names = ["wte", "wpe"]
+    for i in range(cfg.layers):
+        names += [f"b{i}.{n}" for n in ("ln1_w", "ln1_b", "qkv_w", "qkv_b", "proj_w", "proj_b", "ln2_w", "ln2_b",
+                                        "fc1_w", "fc1_b", "fc2_w", "fc2_b")]
+    return names + ["lnf_w", "lnf_b", "head_w"]
+
+
+def compare_grads(engine, ref, cfg):
+    arena = engine.arenas[0]
+    flat = engine.last_grads[0].cpu()
+    worst = 0.0
+    for (i, off, n), name in zip(arena.named_slices(), oracle_names(cfg)):
+        want = ref.last_grads[name]
+        got = flat[off:off + n].view(arena.params[i].shape)[: want.shape[0]]
+        rel = ((got - want).norm() / (want.norm() + 1e-12)).item()
+        worst = max(worst, rel)
+        assert rel <= 5 * TOL, (name, rel)        # per-tensor (small bias vectors are noisier)
+    got_all = torch.cat([flat[off:off + n].view(arena.params[i].shape)[: ref.last_grads[nm].shape[0]].reshape(-1)
+                         for (i, off, n), nm in zip(arena.named_slices(), oracle_names(cfg))])
+    want_all = torch.cat([ref.last_grads[nm].reshape(-1) for nm in oracle_names(cfg)])
+    assert ((got_all - want_all).norm() / want_all.norm()).item() <= TOL
+    return worst
+
+
+def test_toy_gpt_five_steps_match_oracle():
+    """The 2-stage toy of the plumbing configuration, run here as one stage on one GPU:
+    4 layers, hidden 256, 4 heads, FFN 1024, seq 128, vocab 1024, micro-batch 4 x 4."""
+    cfg = gpt_ref.RefConfig(layers=4, hidden=256, heads=4, ffn=1024, seq=128, vocab=1024)
+    mb, gas, steps, lr = 4, 4, 5, 1e-4
+    ref = gpt_ref.RefTrainer(cfg, seed=0, lr=lr, micro_batches=gas)
+    engine = build_engine(cfg, mb, gas, lr)
+    data = gpt_ref.synthetic_batches(cfg, mb, gas, steps, seed=1)
+    for batches in data:
+        want = ref.train_batch(batches)
+        got = float(engine.train_batch(data_iter=iter(batches)))
+        assert got == pytest.approx(want, rel=TOL)
+        compare_grads(engine, ref, cfg)
+    # weights after 5 Adam steps
+    arena = engine.arenas[0]
+    for (i, off, n), name in zip(arena.named_slices(), oracle_names(cfg)):
+        want = ref.P[name].detach()
+        got = arena.master[off:off + n].view(arena.params[i].shape)[: want.shape[0]].cpu()
+        assert (got - want).abs().max().item() <= 5 * lr * steps * 0.5 + 1e-6, name
+    from bamboo_b200 import lib
+    torch.cuda.synchronize()
+    assert lib.read_status() == 0
+
+
+def test_bidirectional_ragged_vocab_matches_oracle():
+    """Encoder-style attention and a vocabulary that is not a multiple of the tile width."""
+    cfg = gpt_ref.RefConfig(layers=2, hidden=128, heads=2, ffn=512, seq=64, vocab=1000, causal=False)
+    mb, gas, lr = 2, 2, 1e-3
+    ref = gpt_ref.RefTrainer(cfg, seed=3, lr=lr, micro_batches=gas)
+    engine = build_engine(cfg, mb, gas, lr, seed=3)
+    for batches in gpt_ref.synthetic_batches(cfg, mb, gas, 2, seed=5):
+        want = ref.train_batch(batches)
+        got = float(engine.train_batch(data_iter=iter(batches)))
+        assert got == pytest.approx(want, rel=TOL)
+        compare_grads(engine, ref, cfg)
+
+
+def test_layers_refuse_cpu_tensors():
+    from bamboo_b200 import layers, lib
+    blk = layers.TransformerBlock(64, 1, 256)
+    with pytest.raises(lib.BambooNativeError):
+        blk(torch.zeros(1, 8, 64))
