@@ -1,0 +1,290 @@
+"""Benchmark of the pipeline training step: tokens/s of GPT-2-medium (24 layers, hidden 1024,
+16 heads, FFN 4096, seq 1024, vocab 50257, bf16 with fp32 master weights; micro-batch 8 x 16
+micro-batches per step) split over N pipeline stages on N GPUs.
+
+    python bench.py --gpus N --steps K --warmup W [--rc off|lazy|eager] [--impl reference]
+
+One rank per GPU (torchrun for N > 1).  Prints one JSON line on rank 0.  ``value`` is the
+device-resident throughput (tokens already in HBM), ``e2e`` is measured through the public
+API (``train_batch``) with pinned host token buffers copied in and the loss read back every
+step.  ``--impl reference`` times the CPU restatement of the reference's step (the oracle)
+on the host cores for the same workload, on a bounded sample per step.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "tokens/sec"
+MICRO_BATCH, MICRO_BATCHES = 8, 16
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="bamboo_b200", choices=["bamboo_b200", "reference"])
+    ap.add_argument("--rc", default="auto", choices=["auto", "off", "lazy", "eager"])
+    ap.add_argument("--model", default="gpt2-medium", choices=["gpt2-medium", "toy"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--micro-batches", type=int, default=0,
+                    help="profiling only: fewer micro-batches per step than the benchmark configuration")
+    return ap.parse_args()
+
+
+def model_config(name):
+    from bamboo_b200 import models
+    return models.GPT2_MEDIUM if name == "gpt2-medium" else models.GPT_TOY
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def synthetic_tokens(cfg, steps, seed, pin):
+    """Uniform token ids; labels = tokens shifted by one (last position ignored)."""
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for _ in range(steps):
+        step = []
+        for _ in range(MICRO_BATCHES):
+            tok = torch.randint(0, cfg.vocab, (MICRO_BATCH, cfg.seq), generator=g)
+            lab = torch.full_like(tok, -100)
+            lab[:, :-1] = tok[:, 1:]
+            if pin:
+                tok, lab = tok.pin_memory(), lab.pin_memory()
+            step.append((tok, lab))
+        out.append(step)
+    return out
+
+
+def cpu_baseline(cfg, seconds_budget=25.0):
+    """The oracle (CPU port of the reference step) on the host cores, bounded sample."""
+    import torch
+    from oracle import gpt_ref
+    cores = len(os.sched_getaffinity(0))
+    torch.set_num_threads(cores)
+    rc = gpt_ref.RefConfig(cfg.layers, cfg.hidden, cfg.heads, cfg.ffn, cfg.seq, cfg.vocab, cfg.causal)
+    ref = gpt_ref.RefTrainer(rc, seed=0, lr=1e-4, micro_batches=1)
+    g = torch.Generator().manual_seed(1)
+    seqs, t_fb = 0, 0.0
+    while t_fb < seconds_budget * 0.6 and seqs < 4:
+        tok = torch.randint(0, cfg.vocab, (1, cfg.seq), generator=g)
+        lab = torch.full_like(tok, -100); lab[:, :-1] = tok[:, 1:]
+        t0 = time.perf_counter()
+        loss = gpt_ref.forward_loss(rc, ref.P, tok, lab)
+        loss.backward()
+        t_fb += time.perf_counter() - t0
+        seqs += 1
+    t0 = time.perf_counter()
+    with torch.no_grad():
+        for k, p in ref.P.items():
+            gpt_ref.adam_update(p, p.grad, ref.m[k], ref.v[k], 1, 1e-4)
+    t_adam = time.perf_counter() - t0
+    step_seqs = MICRO_BATCH * MICRO_BATCHES
+    per_seq = t_fb / seqs + t_adam / step_seqs
+    return {"value": cfg.seq / per_seq, "unit": METRIC, "cores": cores, "kind": "port",
+            "sample": f"{seqs} sequence(s) of {cfg.seq} tokens forward+backward in fp32 plus one Adam update "
+                      f"amortised over the {step_seqs}-sequence step"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", 0))
+    if rank != 0:
+        return
+    cfg = model_config(args.model)
+    vals = []
+    t_all = time.perf_counter()
+    for i in range(args.warmup + args.steps):
+        b = cpu_baseline(cfg, seconds_budget=8.0)
+        if i >= args.warmup:
+            vals.append(b["value"])
+        if time.perf_counter() - t_all > 240:
+            break
+    v = sum(vals) / max(len(vals), 1) if vals else b["value"]
+    b["value"] = v
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": METRIC, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": cfg.seq * MICRO_BATCH * MICRO_BATCHES / v * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.model} pipeline step, micro-batch {MICRO_BATCH} x {MICRO_BATCHES}, seq {cfg.seq}"},
+            "cpu_baseline": b, "e2e": {"value": v, "unit": METRIC, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    global MICRO_BATCHES
+    args = parse()
+    if args.micro_batches:
+        MICRO_BATCHES = args.micro_batches
+    if args.impl == "reference":
+        return run_reference(args)
+    import torch
+    import torch.distributed as dist
+    from bamboo_b200 import api, lib, models
+    from bamboo_b200.module import PipelineModule
+
+    rank = int(os.environ.get("RANK", 0))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    assert world == args.gpus, f"launch with torchrun --nproc-per-node {args.gpus} (WORLD_SIZE={world})"
+    os.environ.setdefault("BAMBOO_QUIET", "1")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        api.init_distributed("nccl", rank=rank, world_size=world)
+    lib.load()
+
+    cfg = model_config(args.model)
+    rc = args.rc if args.rc != "auto" else ("eager" if world > 1 else "off")
+    if world == 1:
+        rc = "off"
+    model = PipelineModule(models.transformer_layer_specs(cfg, 0), num_stages=world, loss_fn=models.transformer_loss(cfg),
+                           partition_method="type:TransformerBlock" if world > 1 else "uniform")
+    engine, *_ = api.initialize(model=model, config={
+        "train_micro_batch_size_per_gpu": MICRO_BATCH, "gradient_accumulation_steps": MICRO_BATCHES,
+        "bf16": {"enabled": True}, "optimizer": {"type": "Adam", "params": {"lr": 1e-4}},
+        "bamboo_b200": {"rc_retain_graph": False}},
+        redundancy_level=0 if rc == "off" else 1, eager_recovery=(rc == "eager"))
+    dev = torch.device("cuda", local_rank)
+    tokens_per_step = MICRO_BATCH * MICRO_BATCHES * cfg.seq
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(steps_data, read_loss):
+        barrier()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        last = None
+        for batches in steps_data:
+            loss = engine.train_batch(data_iter=iter(batches))
+            if read_loss and torch.is_tensor(loss):
+                last = loss.item()          # device -> host read of the step result
+            elif torch.is_tensor(loss):
+                last = loss
+        end.record()
+        barrier()
+        ms = torch.tensor([start.elapsed_time(end)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item(), last
+
+    host = synthetic_tokens(cfg, max(args.warmup, 1) + args.steps, seed=1, pin=True)
+    resident = [[(t.to(dev), l.to(dev)) for t, l in step] for step in host[-args.steps:]]
+    timed(host[:max(args.warmup, 1)], read_loss=True)                      # warm-up (untimed)
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    n0 = lib.LAUNCHES
+    ms_dev, loss_dev = timed(resident, read_loss=False)
+    launches = lib.LAUNCHES - n0
+    ms_e2e, loss_e2e = timed(host[-args.steps:], read_loss=True)
+    clocks = sampler.stop()
+    status = lib.read_status()
+
+    # ---- roofline of the dominant kernel (the tcgen05 GEMM): one extra, instrumented step
+    records = []
+
+    def hook(key, flops, launch):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(); launch(); e.record()
+        records.append((key, flops, s, e))
+
+    lib.gemm_hook = hook
+    engine.train_batch(data_iter=iter(resident[0]))
+    lib.gemm_hook = None
+    torch.cuda.synchronize()
+    g_flops = sum(r[1] for r in records)
+    g_ms = sum(r[2].elapsed_time(r[3]) for r in records)
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = json.load(open(peaks_path))["bf16_tflops_sustained"], "measured (sustained, MEASURED_PEAKS.json)"
+    else:
+        peak, peak_src = 1400.0, "fallback (sustained)"
+    achieved = g_flops / (g_ms * 1e-3) / 1e12 if g_ms > 0 else 0.0
+    by_shape = {}
+    for key, fl, s, e in records:
+        d = by_shape.setdefault(key, [0, 0.0, 0.0]); d[0] += 1; d[1] += fl; d[2] += s.elapsed_time(e)
+
+    if rank != 0:
+        return
+    h2d = sum(t.numel() * t.element_size() + l.numel() * l.element_size() for t, l in host[-1])
+    value = tokens_per_step * args.steps / (ms_dev * 1e-3)
+    e2e = tokens_per_step * args.steps / (ms_e2e * 1e-3)
+    step_flops = cfg.flops_per_token() * tokens_per_step
+    line = {
+        "metric": METRIC, "value": value, "unit": METRIC, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.model} ({cfg.layers} layers, hidden {cfg.hidden}, seq {cfg.seq}, vocab {cfg.vocab}) "
+                               f"pipeline step, {world} stage(s) x 1 replica, micro-batch {MICRO_BATCH} x {MICRO_BATCHES}",
+                   "rc": rc, "parallelism": f"pp{world}", "global_batch": MICRO_BATCH * MICRO_BATCHES, "seq_len": cfg.seq,
+                   "l2": "working set per step is far larger than L2 (no flush needed)"},
+        "e2e": {"value": e2e, "unit": METRIC, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+                "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": launches, "clocks": clocks, "device_status": status,
+        "loss": float(loss_e2e) if loss_e2e is not None else None,
+        "model_tflops_per_gpu": step_flops * args.steps / (ms_dev * 1e-3) / 1e12 / world,
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                     "traffic": None, "kernel": "gemm_bf16_tcgen05_kernel", "peak_source": peak_src,
+                     "launches_per_step": len(records), "gemm_ms_per_step": g_ms,
+                     "note": "sum of algorithmic 2MNK over every GEMM launch of one step / sum of their CUDA-event durations"},
+    }
+    if not args.no_cpu_baseline and world == 1:
+        line["cpu_baseline"] = cpu_baseline(cfg)
+    print(json.dumps(line), flush=True)
+    for key, (n, fl, ms) in sorted(by_shape.items(), key=lambda kv: -kv[1][2]):
+        print(f"# gemm M{key[0]} N{key[1]} K{key[2]} a_mn{key[3]} b_mn{key[4]} epi{key[5]}: {n} launches, {ms:.2f} ms, "
+              f"{fl / ms / 1e9:.0f} TFLOP/s", file=sys.stderr)
+
+
+if __name__ == "__main__":
+    main()

@@ -145,6 +145,33 @@ int bb_adam_step(float* master, float* grad, float* exp_avg, float* exp_avg_sq, 
  * (PipelineModule.build_layers(stage, buffer), DS/runtime/pipe/module.py:262-332). */
 int bb_cast_f32_to_bf16(const float* src, void* dst, long long n, void* stream);
 
+/* ---- inter-stage transfer --------------------------------------------------------- */
+/* Set-up (these four are the only entry points that allocate or map device memory; call
+ * them when a channel to a neighbour is created, not per message): a receive mailbox in
+ * this GPU's memory with its 64-byte CUDA-IPC handle, and the mapping of a neighbour's. */
+int bb_ipc_alloc(long long bytes, void** dev_ptr, void* handle_out64);
+int bb_ipc_open(const void* handle64, void** dev_ptr);
+int bb_ipc_close(void* dev_ptr);
+int bb_ipc_free(void* dev_ptr);
+/* Store `bytes` from local `src` into the neighbour's mailbox slot `dst_peer`, then release
+ * `seq` into the slot's flag (`flag_peer`, 8 bytes in the neighbour's memory).
+ * `done_counter`: 4 zero-initialised bytes of local device memory owned by the channel.
+ * Replaces: p2p.send (DS/runtime/pipe/p2p_direct.py:11-13) as used by _exec_send_activations
+ * / _exec_send_grads (DS/runtime/pipe/engine.py:1894-1997) - NCCL send - and the shape
+ * handshake _send_tensor_meta (engine.py:1781-1841). */
+int bb_p2p_put(void* dst_peer, const void* src, long long bytes, void* flag_peer, unsigned long long seq,
+               void* done_counter, void* stream);
+/* Wait (at most timeout_ns) until the local flag equals `seq`, then copy the local slot to
+ * `dst`.  On expiry BB_STATUS_PEER_TIMEOUT is recorded in `status_word` (NULL: the
+ * library's status word, see bb_read_status) and nothing is copied.  bytes may be 0 (ping).
+ * Replaces: p2p.recv (p2p_direct.py:15-17) + the clone in _exec_recv_activations /
+ * _exec_recv_grads (engine.py:1999-2082); the bounded wait stands in for NCCL_BLOCKING_WAIT. */
+int bb_p2p_wait_copy(const void* slot, void* dst, long long bytes, const void* flag, unsigned long long seq,
+                     unsigned long long timeout_ns, int* status_word, void* stream);
+/* Release `seq` into a neighbour's flag without payload: the liveness ping of lazy
+ * redundancy (buffer_id = -1, engine.py:1902-1905). */
+int bb_p2p_signal(void* flag_peer, unsigned long long seq, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
