@@ -12,6 +12,7 @@
 #include "common.cuh"
 #include "bamboo_b200.h"
 #include <cuda.h>
+#include <stdio.h>
 
 namespace {
 
@@ -20,13 +21,19 @@ constexpr int BK = 64;        // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
+// Epilogue staging: output panels of 128 rows x 128 bytes (64 bf16 or 32 fp32 columns) in the
+// 128-byte-swizzled layout a TMA store expects.  Two panels: double-buffered for one output,
+// one each for the two outputs of the GeLU epilogue (shared memory is better spent on
+// main-loop stages: the kernel is bound by operand bytes in flight).
+constexpr int PANEL_BYTES = BM * 128;
+constexpr int NUM_PANELS = 2;
 
 template <int BN> struct Cfg {
   static constexpr int B_STAGE_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
   static constexpr int TMEM_COLS = 2 * BN;  // two accumulators
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + NUM_PANELS * PANEL_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
 struct GemmParams {
@@ -38,100 +45,62 @@ struct GemmParams {
   int* status;
 };
 
-__device__ __forceinline__ void store8_bf16(__nv_bfloat16* p, const float* v) {
-  uint4 q;
-  q.x = bb::pack_bf16x2(v[0], v[1]); q.y = bb::pack_bf16x2(v[2], v[3]);
-  q.z = bb::pack_bf16x2(v[4], v[5]); q.w = bb::pack_bf16x2(v[6], v[7]);
-  *reinterpret_cast<uint4*>(p) = q;
+__device__ __forceinline__ void unpack8(const uint4& q, float* f) {
+  f[0] = bb::bf16_lo(q.x); f[1] = bb::bf16_hi(q.x); f[2] = bb::bf16_lo(q.y); f[3] = bb::bf16_hi(q.y);
+  f[4] = bb::bf16_lo(q.z); f[5] = bb::bf16_hi(q.z); f[6] = bb::bf16_lo(q.w); f[7] = bb::bf16_hi(q.w);
 }
 
-// Epilogue for 32 consecutive columns of one output row held in registers.
-__device__ __forceinline__ void epilogue_row32(const GemmParams& p, int m, int n0, uint32_t* r) {
-  if (m >= p.M || n0 >= p.N) return;
-  float v[32];
+// One output row's slice of a panel (128 bytes = 8 chunks of 16 bytes) into swizzled shared memory.
+__device__ __forceinline__ void panel_store_row_bf16(uint8_t* panel, int row, const float* v /*64*/) {
+  uint8_t* base = panel + row * 128;
 #pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-  const bool full = (n0 + 32 <= p.N);
-  const int epi = p.epi;
-  if (epi == BB_EPI_BIAS || epi == BB_EPI_BIAS_GELU || epi == BB_EPI_BIAS_RESIDUAL) {
-    const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(p.bias) + n0;
-    if (full) {
-#pragma unroll
-      for (int i = 0; i < 32; i += 8) {
-        uint4 q = __ldg(reinterpret_cast<const uint4*>(b + i));
-        v[i + 0] += bb::bf16_lo(q.x); v[i + 1] += bb::bf16_hi(q.x);
-        v[i + 2] += bb::bf16_lo(q.y); v[i + 3] += bb::bf16_hi(q.y);
-        v[i + 4] += bb::bf16_lo(q.z); v[i + 5] += bb::bf16_hi(q.z);
-        v[i + 6] += bb::bf16_lo(q.w); v[i + 7] += bb::bf16_hi(q.w);
-      }
-    } else {
-      for (int i = 0; i < 32 && n0 + i < p.N; ++i) v[i] += __bfloat162float(b[i]);
-    }
+  for (int c = 0; c < 8; ++c) {
+    uint4 q;
+    q.x = bb::pack_bf16x2(v[8 * c + 0], v[8 * c + 1]); q.y = bb::pack_bf16x2(v[8 * c + 2], v[8 * c + 3]);
+    q.z = bb::pack_bf16x2(v[8 * c + 4], v[8 * c + 5]); q.w = bb::pack_bf16x2(v[8 * c + 6], v[8 * c + 7]);
+    *reinterpret_cast<uint4*>(base + ((c ^ (row & 7)) << 4)) = q;
   }
-  if (epi == BB_EPI_ACCUM_F32 || epi == BB_EPI_STORE_F32) {
-    float* d = reinterpret_cast<float*>(p.D) + (long long)m * p.ldd + n0;
-    if (full) {
+}
+__device__ __forceinline__ void panel_store_row_f32(uint8_t* panel, int row, const float* v /*32*/) {
+  uint8_t* base = panel + row * 128;
 #pragma unroll
-      for (int i = 0; i < 32; i += 4) {
-        float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-        if (epi == BB_EPI_ACCUM_F32) {
-          float4 c = *reinterpret_cast<const float4*>(d + i);
-          o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w;
-        }
-        *reinterpret_cast<float4*>(d + i) = o;
-      }
-    } else {
-      for (int i = 0; i < 32 && n0 + i < p.N; ++i) d[i] = (epi == BB_EPI_ACCUM_F32 ? d[i] : 0.f) + v[i];
+  for (int c = 0; c < 8; ++c)
+    *reinterpret_cast<float4*>(base + ((c ^ (row & 7)) << 4)) = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+}
+
+// bias[n0 .. n0+W) added to v; columns past N read as zero
+template <int W>
+__device__ __forceinline__ void add_bias(const GemmParams& p, int n0, float* v) {
+  const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(p.bias) + n0;
+  if (n0 + W <= p.N) {
+#pragma unroll
+    for (int i = 0; i < W; i += 8) {
+      float f[8]; unpack8(__ldg(reinterpret_cast<const uint4*>(b + i)), f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[i + k] += f[k];
     }
-    return;
-  }
-  __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)m * p.ldd + n0;
-  if (epi == BB_EPI_BIAS_GELU) {
-    __nv_bfloat16* d2 = reinterpret_cast<__nv_bfloat16*>(p.D2) + (long long)m * p.ldd + n0;
-    if (full) {
-#pragma unroll
-      for (int i = 0; i < 32; i += 8) store8_bf16(d2 + i, v + i);
-    } else {
-      for (int i = 0; i < 32 && n0 + i < p.N; ++i) d2[i] = __float2bfloat16(v[i]);
-    }
-    // GeLU is evaluated on the bf16-rounded pre-activation so that forward and backward
-    // (which re-reads the stored pre-activation) see the same argument.
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = bb::gelu_tanh(__bfloat162float(__float2bfloat16(v[i])));
-  } else if (epi == BB_EPI_MUL_DGELU || epi == BB_EPI_BIAS_RESIDUAL) {
-    const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)m * p.ld_aux + n0;
-    float x[32];
-    if (full) {
-#pragma unroll
-      for (int i = 0; i < 32; i += 8) {
-        uint4 q = *reinterpret_cast<const uint4*>(a + i);
-        x[i + 0] = bb::bf16_lo(q.x); x[i + 1] = bb::bf16_hi(q.x);
-        x[i + 2] = bb::bf16_lo(q.y); x[i + 3] = bb::bf16_hi(q.y);
-        x[i + 4] = bb::bf16_lo(q.z); x[i + 5] = bb::bf16_hi(q.z);
-        x[i + 6] = bb::bf16_lo(q.w); x[i + 7] = bb::bf16_hi(q.w);
-      }
-    } else {
-      for (int i = 0; i < 32; ++i) x[i] = (n0 + i < p.N) ? __bfloat162float(a[i]) : 0.f;
-    }
-    if (epi == BB_EPI_MUL_DGELU) {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] *= bb::gelu_tanh_grad(x[i]);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] += x[i];
-    }
-  }
-  if (full) {
-#pragma unroll
-    for (int i = 0; i < 32; i += 8) store8_bf16(d + i, v + i);
   } else {
-    for (int i = 0; i < 32 && n0 + i < p.N; ++i) d[i] = __float2bfloat16(v[i]);
+    for (int i = 0; i < W && n0 + i < p.N; ++i) v[i] += __bfloat162float(b[i]);
+  }
+}
+
+// aux[m, n0 .. n0+W) as floats (zero outside the matrix)
+template <int W>
+__device__ __forceinline__ void load_aux(const GemmParams& p, int m, int n0, float* x) {
+  if (m < p.M && n0 + W <= p.N) {
+    const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)m * p.ld_aux + n0;
+#pragma unroll
+    for (int i = 0; i < W; i += 8) unpack8(*reinterpret_cast<const uint4*>(a + i), x + i);
+  } else {
+    const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)m * p.ld_aux + n0;
+    for (int i = 0; i < W; ++i) x[i] = (m < p.M && n0 + i < p.N) ? __bfloat162float(a[i]) : 0.f;
   }
 }
 
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmD2,
                          const GemmParams p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -139,7 +108,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + C::STAGES * A_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint8_t* panels = smem + C::STAGES * C::STAGE_BYTES;   // NUM_PANELS x 16 KiB, 1024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(panels + NUM_PANELS * PANEL_BYTES);
   uint64_t* full_bar = bars;                      // [STAGES]
   uint64_t* empty_bar = bars + C::STAGES;         // [STAGES]
   uint64_t* tmem_full = bars + 2 * C::STAGES;     // [2]
@@ -161,6 +131,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     bb::fence_barrier_init();
     bb::tma_prefetch_desc(&tmA);
     bb::tma_prefetch_desc(&tmB);
+    bb::tma_prefetch_desc(&tmD);
+    if (p.epi == BB_EPI_BIAS_GELU) bb::tma_prefetch_desc(&tmD2);
   }
   if (warp == 1) {
     bb::tmem_alloc(tmem_slot, C::TMEM_COLS);
@@ -243,30 +215,95 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     }
   } else {
     // ------------------------------------------------ epilogue (4 warps, one TMEM lane quarter each)
+    // Per 128-byte-wide output panel: TMEM -> registers -> fused math -> swizzled shared
+    // memory -> one TMA store (or fp32 add-reduction) issued by a single thread.
     const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;           // row inside the tile == TMEM lane
+    const bool leader = (threadIdx.x == 64);       // first epilogue thread issues the stores
+    const int epi = p.epi;
+    const bool f32 = (epi == BB_EPI_ACCUM_F32 || epi == BB_EPI_STORE_F32);
     int acc = 0; uint32_t acc_phase = 0;
+    uint32_t group = 0;                            // store groups issued so far (buffer rotation)
     bool alive = true;
     for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
       const int m0 = (tile % num_m) * BM, n0 = (tile / num_m) * BN;
-      if (!bb::mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status)) { alive = false; break; }
+      // the four warps must agree (they share named barriers below): all continue or all leave
+      const bool got = bb::mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status);
+      if (!bb::named_bar_all(2, 128, got)) { alive = false; break; }
       bb::tc_fence_after_sync();
-      const int m = m0 + quarter * 32 + lane;
+      const int m = m0 + row;
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+      const int width = f32 ? 32 : 64;             // columns per panel
+      const int npanels = BN / width;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        bb::tmem_ld_32x32b_x32(t_row + c * 32, r);
-        bb::tmem_ld_wait();
-        if (c == BN / 32 - 1) {
-          // accumulator fully read: hand it back before the last stores
+      for (int pn = 0; pn < npanels; ++pn) {
+        const int nb = n0 + pn * width;
+        float v[64];
+        {
+          uint32_t r[32];
+          bb::tmem_ld_32x32b_x32(t_row + pn * width, r);
+          bb::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          if (!f32) {
+            bb::tmem_ld_32x32b_x32(t_row + pn * width + 32, r);
+            bb::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[32 + i] = __uint_as_float(r[i]);
+          }
+        }
+        if (pn == npanels - 1) {
+          // accumulator fully read: hand it back to the MMA warp before the last stores
           bb::tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) bb::mbar_arrive(&tmem_empty[acc]);
         }
-        epilogue_row32(p, m, n0 + c * 32, r);
+        if (nb >= p.N) continue;                   // panel entirely outside the matrix (uniform)
+        const bool dual = (epi == BB_EPI_BIAS_GELU);
+        uint8_t* pD = panels + (dual ? 0 : (group & 1) * PANEL_BYTES);
+        uint8_t* pD2 = panels + PANEL_BYTES;
+        // the panel about to be overwritten must have been read by its previous store
+        if (leader) { if (dual) bb::bulk_wait_group_read<0>(); else bb::bulk_wait_group_read<1>(); }
+        bb::named_bar_sync(1, 128);
+        if (f32) {
+          panel_store_row_f32(pD, row, v);
+        } else {
+          if (epi == BB_EPI_BIAS || epi == BB_EPI_BIAS_GELU || epi == BB_EPI_BIAS_RESIDUAL) add_bias<64>(p, nb, v);
+          if (epi == BB_EPI_BIAS_GELU) {
+            panel_store_row_bf16(pD2, row, v);
+            // GeLU of the bf16-rounded pre-activation: forward and backward (which re-reads the
+            // stored pre-activation) see the same argument
+#pragma unroll
+            for (int i = 0; i < 64; ++i) v[i] = bb::gelu_tanh(__bfloat162float(__float2bfloat16(v[i])));
+          } else if (epi == BB_EPI_MUL_DGELU || epi == BB_EPI_BIAS_RESIDUAL) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              float x[32];
+              load_aux<32>(p, m, nb + half * 32, x);
+              if (epi == BB_EPI_MUL_DGELU) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[half * 32 + i] *= bb::gelu_tanh_grad(x[i]);
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[half * 32 + i] += x[i];
+              }
+            }
+          }
+          panel_store_row_bf16(pD, row, v);
+        }
+        bb::fence_proxy_async();                   // generic-proxy writes -> visible to the TMA engine
+        bb::named_bar_sync(1, 128);
+        if (leader) {
+          if (epi == BB_EPI_ACCUM_F32) bb::tma_reduce_add_2d(&tmD, pD, nb, m0);
+          else bb::tma_store_2d(&tmD, pD, nb, m0);
+          if (epi == BB_EPI_BIAS_GELU) bb::tma_store_2d(&tmD2, pD2, nb, m0);
+          bb::bulk_commit_group();
+        }
+        ++group;
       }
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
+    if (leader) bb::bulk_wait_group<0>();          // all stores landed before shared memory goes away
   }
 
   bb::tc_fence_before_sync();
@@ -291,19 +328,24 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 2-D bf16 tensor map over a row-major [rows, cols] matrix with leading dimension ld (elements).
-int encode_2d(CUtensorMap* tm, const void* base, long long rows, long long cols, long long ld, int box_cols, int box_rows) {
+// 2-D tensor map over a row-major [rows, cols] matrix (bf16, or fp32 when f32 != 0) with leading
+// dimension ld (elements); 128-byte swizzle.
+int encode_2d(CUtensorMap* tm, const void* base, long long rows, long long cols, long long ld, int box_cols, int box_rows,
+              int f32 = 0) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) { bb_set_last_error_msg("cuTensorMapEncodeTiled entry point not available"); return BB_ERR_CUDA; }
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * (f32 ? 4 : 2)};
   cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = fn(tm, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
-    bb_set_last_error_msg("cuTensorMapEncodeTiled failed (operands need 16-byte aligned base and row pitch)");
+    char msg[256];
+    snprintf(msg, sizeof(msg), "cuTensorMapEncodeTiled failed with CUresult %d (base %p, rows %lld, cols %lld, ld %lld, box %dx%d, "
+             "f32 %d); operands need a 16-byte aligned base and row pitch", (int)r, base, rows, cols, ld, box_cols, box_rows, f32);
+    bb_set_last_error_msg(msg);
     return BB_ERR_INVALID_ARG;
   }
   return BB_OK;
@@ -312,8 +354,16 @@ int encode_2d(CUtensorMap* tm, const void* base, long long rows, long long cols,
 template <int BN>
 int launch(const bb_gemm_desc* g, cudaStream_t stream) {
   using C = Cfg<BN>;
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmD, tmD2;
   int rc;
+  const int out_f32 = (g->epilogue == BB_EPI_ACCUM_F32 || g->epilogue == BB_EPI_STORE_F32);
+  rc = encode_2d(&tmD, g->D, g->M, g->N, g->ldd, out_f32 ? 32 : 64, BM, out_f32);
+  if (rc) return rc;
+  tmD2 = tmD;
+  if (g->epilogue == BB_EPI_BIAS_GELU) {
+    rc = encode_2d(&tmD2, g->D2, g->M, g->N, g->ldd, 64, BM, 0);
+    if (rc) return rc;
+  }
   if (!g->a_mn_major) rc = encode_2d(&tmA, g->A, g->M, g->K, g->lda, BK, BM);
   else rc = encode_2d(&tmA, g->A, g->K, g->M, g->lda, 64, BK);
   if (rc) return rc;
@@ -333,7 +383,7 @@ int launch(const bb_gemm_desc* g, cudaStream_t stream) {
   int grid = bb_num_sms();
   if (g->max_ctas > 0 && g->max_ctas < grid) grid = g->max_ctas;
   if (tiles < grid) grid = tiles;
-  gemm_bf16_tcgen05_kernel<BN><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  gemm_bf16_tcgen05_kernel<BN><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, tmD, tmD2, p);
   BB_CUDA_CHECK(cudaGetLastError());
   return BB_OK;
 }
@@ -360,6 +410,10 @@ extern "C" int bb_gemm_bf16(const bb_gemm_desc* g, void* stream) {
     return BB_ERR_INVALID_ARG;
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // cuTensorMapEncodeTiled is a driver call and needs a context bound to the calling thread;
+  // a thread that has only ever set its device (autograd worker threads) has none yet.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) { BB_CUDA_CHECK(cudaFree(0)); ctx_bound = true; }
   int bn = g->tile_n;
   if (bn == 0) {
     // 256-wide tiles halve the A re-reads; use them when they still fill the machine

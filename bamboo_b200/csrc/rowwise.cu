@@ -4,6 +4,7 @@
 // row so no block-level synchronisation is needed on the hot loops; grids are sized as a
 // multiple of the SM count and stride over rows.
 #include "common.cuh"
+#include <stdio.h>
 
 namespace {
 
@@ -127,14 +128,25 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
   }
 }
 
-// out[j] += sum_p partials[p * stride + j]   (fixed order: deterministic)
-__global__ void reduce_partials_kernel(const float* __restrict__ partials, float* __restrict__ out, int nparts, int n,
-                                       long long stride) {
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= n) return;
+// out[j] += sum_p partials[p * stride + j].  A 32-column x 8-way block: eight threads share
+// a column, each sums every eighth partial, shared memory combines them in a fixed order
+// (deterministic).
+__global__ void __launch_bounds__(256)
+reduce_partials_kernel(const float* __restrict__ partials, float* __restrict__ out, int nparts, int n, long long stride) {
+  __shared__ float red[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int j = blockIdx.x * 32 + tx;
   float s = 0.f;
-  for (int p = 0; p < nparts; ++p) s += partials[(size_t)p * stride + j];
-  out[j] += s;
+  if (j < n)
+    for (int p = ty; p < nparts; p += 8) s += partials[(size_t)p * stride + j];
+  red[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && j < n) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w][tx];
+    out[j] += t;
+  }
 }
 
 // ------------------------------------------------------------------ bias gradient
@@ -277,8 +289,8 @@ extern "C" int bb_layernorm_bwd(const void* dy, const void* x, const void* gamma
                                                       (const __nv_bfloat16*)gamma, mean, rstd, (const __nv_bfloat16*)dres,
                                                       (__nv_bfloat16*)dx, ws, rows, h);
   BB_CUDA_CHECK(cudaGetLastError());
-  reduce_partials_kernel<<<(h + 255) / 256, 256, 0, s>>>(ws, dgamma, grid, h, 2LL * h);
-  reduce_partials_kernel<<<(h + 255) / 256, 256, 0, s>>>(ws + h, dbeta, grid, h, 2LL * h);
+  reduce_partials_kernel<<<(h + 31) / 32, 256, 0, s>>>(ws, dgamma, grid, h, 2LL * h);
+  reduce_partials_kernel<<<(h + 31) / 32, 256, 0, s>>>(ws + h, dbeta, grid, h, 2LL * h);
   BB_CUDA_CHECK(cudaGetLastError());
   return BB_OK;
 }
@@ -310,7 +322,7 @@ extern "C" int bb_colsum_accum(const void* dy, long long ld, float* out, void* w
   const int rps = (rows + splits - 1) / splits;
   dim3 grid((n + 255) / 256, splits);
   colsum_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)dy, (float*)workspace, rows, n, ld, rps);
-  reduce_partials_kernel<<<(n + 255) / 256, 256, 0, s>>>((const float*)workspace, out, splits, n, (long long)n);
+  reduce_partials_kernel<<<(n + 31) / 32, 256, 0, s>>>((const float*)workspace, out, splits, n, (long long)n);
   BB_CUDA_CHECK(cudaGetLastError());
   return BB_OK;
 }

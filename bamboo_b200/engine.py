@@ -160,10 +160,16 @@ class PipelineEngine:
         for info in self.rdzv_handler.get_global_decision():
             if info.rank == self.global_rank:
                 self.coordinates = [list(c) for c in info.active_coordinates]
+        if store is None and self.dist is not None and self.world_size > 1:
+            try:  # the job's own c10d store (env:// or rendezvous-provided) carries the bookkeeping keys
+                from torch.distributed.distributed_c10d import _get_default_store
+                store = self.dist.PrefixStore("bamboo_b200", _get_default_store())
+            except Exception:
+                store = None
         self.global_store = store or LocalStore()
         self.global_store.set(str(self.global_rank), "0")
         self.global_store.set(f"fail-step-{self.global_rank}", "[]")
-        if store is None or self.global_rank == 0:
+        if isinstance(self.global_store, LocalStore) or self.global_rank == 0:
             self.global_store.set("failures", "{}")
         self.fail_lock = self.rdzv_handler.create_lock("fail-lock")
         self.global_steps = self.rdzv_handler.get_current_step()

@@ -10,6 +10,7 @@ import threading
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libbamboo_b200.so")
 
+STATUS_PEER_TIMEOUT, STATUS_KERNEL_WAIT_TIMEOUT = 1, 2
 EPI_STORE, EPI_BIAS, EPI_BIAS_GELU, EPI_ACCUM_F32, EPI_STORE_F32, EPI_MUL_DGELU, EPI_BIAS_RESIDUAL = range(7)
 
 

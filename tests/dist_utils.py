@@ -7,14 +7,17 @@ import torch
 import torch.multiprocessing as mp
 
 
-def _entry(rank, world, store_path, fn, args, queue):
+def _entry(rank, world, store_path, fn, args, queue, backend="gloo"):
     try:
         os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), BAMBOO_QUIET="1",
                           MASTER_ADDR="127.0.0.1")
         torch.set_num_threads(1)
         import torch.distributed as dist
         store = dist.FileStore(store_path, world)
-        dist.init_process_group("gloo", store=dist.PrefixStore("pg", store), rank=rank, world_size=world)
+        if backend == "nccl":
+            os.environ.setdefault("NCCL_NVLS_ENABLE", "0")   # a rank may leave the job in these tests
+            torch.cuda.set_device(rank)
+        dist.init_process_group(backend, store=dist.PrefixStore("pg", store), rank=rank, world_size=world)
         out = fn(rank, world, dist.PrefixStore("engine", store), *args)
         queue.put((rank, "ok", out))
     except SystemExit as e:
@@ -23,12 +26,12 @@ def _entry(rank, world, store_path, fn, args, queue):
         queue.put((rank, "error", traceback.format_exc()))
 
 
-def run_ranks(fn, world, *args, timeout=240):
+def run_ranks(fn, world, *args, timeout=240, backend="gloo"):
     ctx = mp.get_context("spawn")
     queue = ctx.Queue()
     with tempfile.TemporaryDirectory() as d:
         path = os.path.join(d, "store")
-        procs = [ctx.Process(target=_entry, args=(r, world, path, fn, args, queue)) for r in range(world)]
+        procs = [ctx.Process(target=_entry, args=(r, world, path, fn, args, queue, backend)) for r in range(world)]
         for p in procs:
             p.start()
         results = {}
