@@ -295,6 +295,70 @@ extern "C" int bb_layernorm_bwd(const void* dy, const void* x, const void* gamma
   return BB_OK;
 }
 
+// ------------------------------------------------------------------ LayerNorm backward without caller scratch
+namespace {
+// Scratch of the allocation-free entry point: lives in the library image, one copy per GPU
+// that loads it, until the process exits.
+constexpr long long LN_STATIC_SCRATCH_FLOATS = 2LL * 1024 * 1024;   // 8 MiB
+static __device__ __align__(256) float g_ln_static_scratch[LN_STATIC_SCRATCH_FLOATS];
+
+// Device address of the scratch array on the current device.  The symbol's name in host code
+// is only a handle, so the address is looked up (once per device, with that device current).
+float* ln_static_scratch_ptr() {
+  static float* ptr[64] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!ptr[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_ln_static_scratch);
+    if (e != cudaSuccess) { bb_set_last_error("cudaGetSymbolAddress(g_ln_static_scratch)", e); return nullptr; }
+    ptr[dev] = static_cast<float*>(p);
+  }
+  return ptr[dev];
+}
+}  // namespace
+
+extern "C" long long bb_layernorm_bwd_static_capacity_bytes(void) {
+  return LN_STATIC_SCRATCH_FLOATS * (long long)sizeof(float);
+}
+
+extern "C" int bb_layernorm_bwd_static(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
+                                       const void* dres, void* dx, float* dgamma, float* dbeta, int rows, int h, void* stream) {
+  if (!dy || !x || !gamma || !mean || !rstd || !dx || !dgamma || !dbeta || rows <= 0 || h <= 0 || (h & 7)) {
+    bb_set_last_error_msg("bb_layernorm_bwd_static: null pointer or hidden size not a multiple of 8");
+    return BB_ERR_INVALID_ARG;
+  }
+  const int warps = ln_bwd_warps(h);
+  const long long need = bb_layernorm_bwd_workspace_bytes(rows, h);
+  if (warps < 1 || need <= 0 || need > bb_layernorm_bwd_static_capacity_bytes()) {
+    char msg[200];
+    snprintf(msg, sizeof(msg), "bb_layernorm_bwd_static: rows=%d h=%d needs %lld bytes of scratch, the built-in scratch holds %lld; "
+             "use bb_layernorm_bwd with a caller workspace", rows, h, need, bb_layernorm_bwd_static_capacity_bytes());
+    bb_set_last_error_msg(msg);
+    return BB_ERR_TOO_LARGE;
+  }
+  float* ws = ln_static_scratch_ptr();
+  if (!ws) return BB_ERR_CUDA;
+  cudaStream_t s = (cudaStream_t)stream;
+  static bool attr = false;
+  if (!attr) {
+    BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr = true;
+  }
+  const int grid = ln_bwd_grid(rows, h);
+  const size_t smem = (size_t)warps * 2 * h * sizeof(float);
+  // every partial row that the reduction reads is rewritten by this launch, so the scratch
+  // needs no clearing although it still holds the previous call's sums
+  layernorm_bwd_kernel<<<grid, warps * 32, smem, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                                      (const __nv_bfloat16*)gamma, mean, rstd, (const __nv_bfloat16*)dres,
+                                                      (__nv_bfloat16*)dx, ws, rows, h);
+  BB_CUDA_CHECK(cudaGetLastError());
+  reduce_partials_kernel<<<(h + 31) / 32, 256, 0, s>>>(ws, dgamma, grid, h, 2LL * h);
+  reduce_partials_kernel<<<(h + 31) / 32, 256, 0, s>>>(ws + h, dbeta, grid, h, 2LL * h);
+  BB_CUDA_CHECK(cudaGetLastError());
+  return BB_OK;
+}
+
 namespace {
 int colsum_splits(int rows) {
   int s = (rows + 255) / 256;

@@ -156,6 +156,18 @@ def layernorm_bwd(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta):
     return dx
 
 
+def layernorm_bwd_static(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta):
+    """LayerNorm backward through the entry point that allocates nothing: its scratch is an
+    array inside the library (see bb_layernorm_bwd_static in the header for the limits)."""
+    global LAUNCHES
+    LAUNCHES += 3
+    rows, h = x.numel() // x.shape[-1], x.shape[-1]
+    check(load().bb_layernorm_bwd_static(_ptr(dy), _ptr(x), _ptr(gamma), _ptr(mean), _ptr(rstd), _ptr(dres), _ptr(dx),
+                                         _ptr(dgamma), _ptr(dbeta), _I(rows), _I(h), _stream()),
+          "bb_layernorm_bwd_static")
+    return dx
+
+
 def colsum_accum(dy, out):
     """out(fp32)[n] += dy(bf16)[rows, n].sum(0)"""
     global LAUNCHES

@@ -86,6 +86,24 @@ int bb_layernorm_bwd(const void* dy, const void* x, const void* gamma, const flo
                      const void* dres, void* dx, float* dgamma, float* dbeta, void* workspace,
                      long long workspace_bytes, int rows, int h, void* stream);
 
+/* LayerNorm backward for callers that must not allocate device memory - code running inside
+ * a memory-pool callback, a fixed-footprint serving process, or any host that is not allowed to
+ * call cudaMalloc once it is up.  Same arguments and results as bb_layernorm_bwd, minus the
+ * workspace: the per-CTA partial sums go to an 8 MiB array built into the library's device
+ * image (every GPU that loads the library holds it until the process exits).  This entry point
+ * has no counterpart in the reference; it exists for those callers only.
+ *  - Limit: bb_layernorm_bwd_workspace_bytes(rows, h) must not exceed
+ *    bb_layernorm_bwd_static_capacity_bytes() (8 MiB; e.g. any row count up to h = 3456);
+ *    larger problems return BB_ERR_TOO_LARGE and launch nothing.
+ *  - The first call on a device resolves the array's device address (cudaGetSymbolAddress);
+ *    make that first call outside any stream capture.  No call allocates or frees memory.
+ *  - All calls on a device share the one array: two calls whose kernels may overlap on the
+ *    GPU (different streams) race on it and must be ordered by the caller.  The array keeps
+ *    the last call's partial sums; every call rewrites all it reads, nothing needs clearing. */
+long long bb_layernorm_bwd_static_capacity_bytes(void);
+int bb_layernorm_bwd_static(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
+                            const void* dres, void* dx, float* dgamma, float* dbeta, int rows, int h, void* stream);
+
 /* out[n] += sum_rows dy[row, n] : bias gradient of a linear layer (fp32 accumulate).
  * Replaces: the bias-gradient reduction autograd runs for nn.Linear
  * (EX/pipeline_parallelism/gpt2.py:52-64 via DS/runtime/pipe/engine.py:1680-1727). */
