@@ -34,6 +34,9 @@ def parse():
     ap.add_argument("--rc", default="auto", choices=["auto", "off", "lazy", "eager"])
     ap.add_argument("--model", default="gpt2-medium", choices=["gpt2-medium", "toy"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--failover", action="store_true",
+                    help="after the timed region: the last stage announces its preemption and leaves; reports the "
+                         "pause of the first step after it and the post-failover throughput")
     ap.add_argument("--micro-batches", type=int, default=0,
                     help="profiling only: fewer micro-batches per step than the benchmark configuration")
     return ap.parse_args()
@@ -254,7 +257,13 @@ def main():
     for key, fl, s, e in records:
         d = by_shape.setdefault(key, [0, 0.0, 0.0]); d[0] += 1; d[1] += fl; d[2] += s.elapsed_time(e)
 
+    failover = None
+    if args.failover and world > 1 and rc != "off":
+        failover = measure_failover(engine, host, rank, world, tokens_per_step, ms_dev / args.steps)
     if rank != 0:
+        if failover is not None:
+            sys.stdout.flush()
+            os._exit(0)        # the job lost a rank: skip collective teardown
         return
     h2d = sum(t.numel() * t.element_size() + l.numel() * l.element_size() for t, l in host[-1])
     value = tokens_per_step * args.steps / (ms_dev * 1e-3)
@@ -278,12 +287,48 @@ def main():
                      "launches_per_step": len(records), "gemm_ms_per_step": g_ms,
                      "note": "sum of algorithmic 2MNK over every GEMM launch of one step / sum of their CUDA-event durations"},
     }
+    if failover is not None:
+        line["failover"] = failover
     if not args.no_cpu_baseline and world == 1:
         line["cpu_baseline"] = cpu_baseline(cfg)
     print(json.dumps(line), flush=True)
     for key, (n, fl, ms) in sorted(by_shape.items(), key=lambda kv: -kv[1][2]):
         print(f"# gemm M{key[0]} N{key[1]} K{key[2]} a_mn{key[3]} b_mn{key[4]} epi{key[5]}: {n} launches, {ms:.2f} ms, "
               f"{fl / ms / 1e9:.0f} TFLOP/s", file=sys.stderr)
+
+
+    if failover is not None:
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
+
+def measure_failover(engine, host, rank, world, tokens_per_step, normal_ms):
+    """Host-side fault injection: the rank of the last stage announces its preemption (what its
+    SIGTERM handler would do) and exits at the next batch boundary; its predecessor promotes the
+    shadow stage.  No collective runs after the announcement.  Times are this rank's own."""
+    import torch
+    victim = world - 1
+    if rank == victim:
+        engine.announce_preemption()
+    engine.train_batch(data_iter=iter(host[0]))          # last step with the full pipeline
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    engine.train_batch(data_iter=iter(host[1 % len(host)]))   # victim leaves here; survivors fail over
+    torch.cuda.synchronize()
+    first = time.perf_counter() - t0
+    post = []
+    for i in range(3):
+        t0 = time.perf_counter()
+        engine.train_batch(data_iter=iter(host[(2 + i) % len(host)]))
+        torch.cuda.synchronize()
+        post.append(time.perf_counter() - t0)
+    post_s = sorted(post)[len(post) // 2]
+    return {"victim_stage": victim, "first_step_after_s": first, "normal_step_s": normal_ms * 1e-3,
+            "pause_s": max(first - post_s, 0.0), "post_failover_step_s": post_s,
+            "post_failover_tokens_per_s": tokens_per_step / post_s,
+            "promote_s": engine.timers.get("promote_s", 0.0),
+            "definition": "pause = first step after the victim left minus a steady post-failover step"}
 
 
 if __name__ == "__main__":
