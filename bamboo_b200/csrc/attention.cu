@@ -148,7 +148,7 @@ __device__ __forceinline__ void store_rows(__nv_bfloat16* g, long long stride, i
 
 // ------------------------------------------------------------------ forward
 template <int D>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, (D == 64) ? 2 : 1)
 attn_fwd_kernel(const AttnParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int QB = BLK_M * D * 2, KB = BLK_N * D * 2;

@@ -40,6 +40,7 @@ struct GemmParams {
   int M, N, K;
   int a_mn, b_mn;
   int epi;
+  int ksplit, kb_per_split;   // split-K work units (fp32 add-reduction epilogue only)
   void* D; void* D2; const void* bias; const void* aux;
   long long ldd, ld_aux;
   int* status;
@@ -121,8 +122,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   const int lane = threadIdx.x & 31;
   const int num_m = (p.M + BM - 1) / BM;
   const int num_n = (p.N + BN - 1) / BN;
-  const int num_tiles = num_m * num_n;
-  const int num_kb = (p.K + BK - 1) / BK;
+  const int num_mn = num_m * num_n;
+  const int num_tiles = num_mn * p.ksplit;        // work units: (m, n, k-split)
+  const int total_kb = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -149,8 +151,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       int s = 0; uint32_t phase = 0;
       bool alive = true;
       for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-        const int m0 = (tile % num_m) * BM, n0 = (tile / num_m) * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int mn = tile % num_mn, ks = tile / num_mn;
+        const int m0 = (mn % num_m) * BM, n0 = (mn / num_m) * BN;
+        const int kb0 = ks * p.kb_per_split, kb1 = min(total_kb, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!bb::mbar_wait(&empty_bar[s], phase ^ 1, abort_flag, p.status)) { alive = false; break; }
           bb::mbar_arrive_expect_tx(&full_bar[s], C::STAGE_BYTES);
           uint8_t* a = sA + s * A_STAGE_BYTES;
@@ -193,6 +197,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       if (!bb::mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status)) { alive = false; break; }
       bb::tc_fence_after_sync();
       const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+      const int ks = tile / num_mn;
+      const int num_kb = min(total_kb, (ks + 1) * p.kb_per_split) - ks * p.kb_per_split;
       for (int kb = 0; kb < num_kb; ++kb) {
         if (!bb::mbar_wait(&full_bar[s], phase, abort_flag, p.status)) { alive = false; break; }
         bb::tc_fence_after_sync();
@@ -226,7 +232,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     uint32_t group = 0;                            // store groups issued so far (buffer rotation)
     bool alive = true;
     for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-      const int m0 = (tile % num_m) * BM, n0 = (tile / num_m) * BN;
+      const int mn = tile % num_mn;
+      const int m0 = (mn % num_m) * BM, n0 = (mn / num_m) * BN;
       // the four warps must agree (they share named barriers below): all continue or all leave
       const bool got = bb::mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status);
       if (!bb::named_bar_all(2, 128, got)) { alive = false; break; }
@@ -374,12 +381,36 @@ int launch(const bb_gemm_desc* g, cudaStream_t stream) {
   p.M = g->M; p.N = g->N; p.K = g->K; p.a_mn = g->a_mn_major; p.b_mn = g->b_mn_major; p.epi = g->epilogue;
   p.D = g->D; p.D2 = g->D2; p.bias = g->bias; p.aux = g->aux; p.ldd = g->ldd; p.ld_aux = g->ld_aux ? g->ld_aux : g->ldd;
   p.status = bb_device_status_word();
+  const int total_kb = (g->K + BK - 1) / BK;
+  const int mn_tiles = ((g->M + BM - 1) / BM) * ((g->N + BN - 1) / BN);
+  int ksplit = 1;
+  if (g->epilogue == BB_EPI_ACCUM_F32) {
+    if (g->split_k > 0) {
+      ksplit = g->split_k;
+    } else {
+      // too few output tiles to fill the machine: split the reduction; partial sums meet in
+      // the fp32 add-reduction of the epilogue.  Cost model: waves x (k-blocks + fixed overhead).
+      const int sms = bb_num_sms();
+      long long best = -1;
+      for (int s = 1; s <= 16; ++s) {
+        const int kbs = (total_kb + s - 1) / s;
+        if (s > 1 && kbs < 8) break;
+        const long long waves = ((long long)mn_tiles * s + sms - 1) / sms;
+        const long long cost = waves * (kbs + 8);
+        if (best < 0 || cost < best) { best = cost; ksplit = s; }
+      }
+    }
+  }
+  if (ksplit > total_kb) ksplit = total_kb;
+  if (ksplit < 1) ksplit = 1;
+  p.kb_per_split = (total_kb + ksplit - 1) / ksplit;
+  p.ksplit = (total_kb + p.kb_per_split - 1) / p.kb_per_split;   // no empty splits
   static bool attr_set = false;
   if (!attr_set) {
     BB_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     attr_set = true;
   }
-  const int tiles = ((g->M + BM - 1) / BM) * ((g->N + BN - 1) / BN);
+  const int tiles = mn_tiles * p.ksplit;
   int grid = bb_num_sms();
   if (g->max_ctas > 0 && g->max_ctas < grid) grid = g->max_ctas;
   if (tiles < grid) grid = tiles;
@@ -418,7 +449,8 @@ extern "C" int bb_gemm_bf16(const bb_gemm_desc* g, void* stream) {
   if (bn == 0) {
     // 256-wide tiles halve the A re-reads; use them when they still fill the machine
     const long long tiles256 = (long long)((g->M + BM - 1) / BM) * ((g->N + 255) / 256);
-    bn = (g->N > 128 && tiles256 >= bb_num_sms()) ? 256 : 128;
+    // the add-reduction epilogue can split K to fill the machine, so it always takes wide tiles
+    bn = (g->N > 128 && (tiles256 >= bb_num_sms() || e == BB_EPI_ACCUM_F32)) ? 256 : 128;
   }
   if (bn == 256) return launch<256>(g, s);
   if (bn == 128) return launch<128>(g, s);

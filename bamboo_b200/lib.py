@@ -30,6 +30,7 @@ class GemmDesc(ctypes.Structure):
         ("aux", ctypes.c_void_p), ("ld_aux", ctypes.c_longlong),
         ("tile_n", ctypes.c_int),
         ("max_ctas", ctypes.c_int),
+        ("split_k", ctypes.c_int),
     ]
 
 
@@ -84,7 +85,7 @@ def _stream():
 
 
 def gemm(a, b, out, *, a_mn=False, b_mn=False, epilogue=EPI_STORE, bias=None, out2=None, aux=None,
-         M=None, N=None, K=None, tile_n=0, max_ctas=0):
+         M=None, N=None, K=None, tile_n=0, max_ctas=0, split_k=0):
     """out[M,N] = op(a)[M,K] @ op(b)[N,K]^T with a fused epilogue; see bb_gemm_bf16.
 
     ``a`` is [M,K] (or [K,M] when ``a_mn``), ``b`` is [N,K] (or [K,N] when ``b_mn``); 2-D,
@@ -102,7 +103,7 @@ def gemm(a, b, out, *, a_mn=False, b_mn=False, epilogue=EPI_STORE, bias=None, ou
     d = GemmDesc(M=M, N=N, K=K, A=_ptr(a), lda=a.stride(0), a_mn_major=int(a_mn),
                  B=_ptr(b), ldb=b.stride(0), b_mn_major=int(b_mn), D=_ptr(out), ldd=out.stride(0),
                  epilogue=epilogue, bias=_ptr(bias), D2=_ptr(out2), aux=_ptr(aux),
-                 ld_aux=aux.stride(0) if aux is not None else 0, tile_n=tile_n, max_ctas=max_ctas)
+                 ld_aux=aux.stride(0) if aux is not None else 0, tile_n=tile_n, max_ctas=max_ctas, split_k=split_k)
     global LAUNCHES
     LAUNCHES += 1
     if gemm_hook is not None:

@@ -97,6 +97,20 @@ def test_gemm_is_linear_and_deterministic_at_full_size(L):
     assert torch.equal(o1[:256], (A1[:256].float() @ B.float().t()))
 
 
+@pytest.mark.parametrize("split", [0, 1, 3, 8])
+def test_gemm_split_k_accumulation(L, split):
+    """Weight-gradient shape (few output tiles, long reduction): partial sums of the K splits
+    meet in the fp32 add-reduction."""
+    torch.manual_seed(11)
+    M, N, K = 1024, 1024, 8192
+    A = torch.randint(-3, 4, (K, M), device="cuda").bfloat16()      # stored [K, M]
+    B = torch.randint(-3, 4, (K, N), device="cuda").bfloat16()      # stored [K, N]
+    acc = torch.ones(M, N, device="cuda")
+    L.gemm(A, B, acc, a_mn=True, b_mn=True, epilogue=L.EPI_ACCUM_F32, M=M, N=N, K=K, split_k=split)
+    want = A.float().t() @ B.float() + 1
+    assert torch.equal(acc, want)                                    # small integers: exact
+
+
 def test_gemm_rejects_bad_arguments(L):
     A = torch.zeros(16, 12, device="cuda", dtype=torch.bfloat16)   # leading dimension not a multiple of 8
     B = torch.zeros(16, 12, device="cuda", dtype=torch.bfloat16)
