@@ -1,0 +1,642 @@
+// Fused attention for head dimension 64 on the 5th-generation tensor cores.
+//
+// Every contraction (Q.K^T, P.V, dO.V^T, dS.K, P^T.dO, dS^T.Q) is a tcgen05.mma with fp32
+// accumulators in tensor memory; tiles arrive by TMA into 128-byte-swizzled shared memory;
+// the same [128 x 64] tile serves as a K-major operand (reduction over the head dimension) and
+// as an MN-major operand (reduction over its rows) just by changing the matrix descriptor, so
+// nothing is transposed.  Probabilities are recomputed from the saved log-sum-exp in the
+// backward pass; scores never reach HBM.
+//
+// CTA = 192 threads: warp 0 issues TMA, warp 1 issues MMAs, warps 2-5 (one TMEM lane quarter
+// each, thread == tile row) do the softmax / elementwise work and the final stores.
+// Three kernels: forward (CTA owns 128 query rows), dQ (CTA owns 128 query rows), dK/dV (CTA
+// owns 128 key rows); the backward split keeps every sum in a fixed order (no atomics).
+#include "tma_host.cuh"
+#include <math.h>
+
+namespace {
+
+constexpr int TQ = 128;        // rows per tile (queries or keys)
+constexpr int HD = 64;         // head dimension
+constexpr int TILE_BYTES = TQ * HD * 2;          // 16 KiB: [128 x 64] bf16, 128-byte rows
+constexpr int SQ_BYTES = 2 * TILE_BYTES;         // 32 KiB: [128 x 128] bf16 as two 64-column atoms
+constexpr int NTHREADS = 192;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct TcParams {
+  const __nv_bfloat16* o;       // forward output (delta kernel)
+  __nv_bfloat16 *out, *dq, *dk, *dv;
+  float* lse;                   // [B, H, S]
+  float* delta;                 // [B, H, S]
+  long long stride_o, stride_dqkv;
+  int B, H, S;
+  int hidden;                   // H * 64: column offset between q, k and v in the packed projection
+  int causal;
+  float scale;
+  int* status;
+};
+
+// instruction descriptor: bf16 x bf16 -> fp32, M = 128
+__device__ __forceinline__ uint32_t idesc(int n, int a_mn, int b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TQ >> 4) << 24);
+}
+// [rows x 64] tile, reduction over the 64 columns: k-step = 16 columns = 32 bytes
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile, int kstep) {
+  return bb::make_smem_desc_sw128(tile + kstep * 32, 16, 1024);
+}
+// [rows x 64] tile, reduction over its rows (N or M = the 64 columns): k-step = 16 rows = 2 KiB
+__device__ __forceinline__ uint64_t desc_mnmajor64(uint32_t tile, int kstep) {
+  return bb::make_smem_desc_sw128(tile + kstep * 2048, 8192, 1024);
+}
+// [128 x 128] two-atom buffer, reduction over its 128 columns: k-step k lives in atom k/4
+__device__ __forceinline__ uint64_t desc_sq_kmajor(uint32_t buf, int kstep) {
+  return bb::make_smem_desc_sw128(buf + (kstep >> 2) * TILE_BYTES + (kstep & 3) * 32, 16, 1024);
+}
+// [128 x 128] two-atom buffer, reduction over its rows (M = the 128 columns, atoms 16 KiB apart)
+__device__ __forceinline__ uint64_t desc_sq_mnmajor(uint32_t buf, int kstep) {
+  return bb::make_smem_desc_sw128(buf + kstep * 2048, TILE_BYTES, 1024);
+}
+
+// 32 values of one row into a two-atom [128 x 128] bf16 buffer at columns c0 .. c0+31
+__device__ __forceinline__ void sq_store32(uint8_t* buf, int row, int c0, const float* v) {
+  uint8_t* base = buf + (c0 >> 6) * TILE_BYTES + row * 128;
+  const int chunk0 = (c0 & 63) >> 3;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint4 q;
+    q.x = bb::pack_bf16x2(v[8 * c + 0], v[8 * c + 1]); q.y = bb::pack_bf16x2(v[8 * c + 2], v[8 * c + 3]);
+    q.z = bb::pack_bf16x2(v[8 * c + 4], v[8 * c + 5]); q.w = bb::pack_bf16x2(v[8 * c + 6], v[8 * c + 7]);
+    *reinterpret_cast<uint4*>(base + (((chunk0 + c) ^ (row & 7)) << 4)) = q;
+  }
+}
+
+__device__ __forceinline__ void ld32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  bb::tmem_ld_32x32b_x32(taddr, r);
+  bb::tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// one row of 64 fp32 values -> bf16 in global memory (128 contiguous bytes)
+__device__ __forceinline__ void store_row64(__nv_bfloat16* dst, const float* v, float mul) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    uint4 q;
+    q.x = bb::pack_bf16x2(v[8 * c + 0] * mul, v[8 * c + 1] * mul); q.y = bb::pack_bf16x2(v[8 * c + 2] * mul, v[8 * c + 3] * mul);
+    q.z = bb::pack_bf16x2(v[8 * c + 4] * mul, v[8 * c + 5] * mul); q.w = bb::pack_bf16x2(v[8 * c + 6] * mul, v[8 * c + 7] * mul);
+    reinterpret_cast<uint4*>(dst)[c] = q;
+  }
+}
+
+// shared-memory bookkeeping common to the three kernels
+struct Ctl {
+  uint64_t bars[16];
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+
+// Compute warps wait together: the 128 threads either all proceed or all leave.
+__device__ __forceinline__ bool wait_all(uint64_t* bar, uint32_t parity, Ctl* ctl, int* status) {
+  const bool ok = bb::mbar_wait(bar, parity, &ctl->abort_flag, status);
+  return bb::named_bar_all(2, 128, ok);
+}
+
+// ------------------------------------------------------------------ dQ
+// CTA owns query rows q0..q0+127 of one (batch, head); streams key/value tiles.
+//   S = Q K^T, dP = dO V^T  ->  dS = P o (dP - delta)  ->  dQ += dS K
+// smem: Q, dO (once) | K, V (2 stages) | dS [128 q x 128 kv] ; TMEM: S 128 | dP 128 | dQ 64
+__global__ void __launch_bounds__(NTHREADS, 1)
+attn_tc_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do, const TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sDO = sQ + TILE_BYTES;
+  uint8_t* sK = sDO + TILE_BYTES;              // 2 stages
+  uint8_t* sV = sK + 2 * TILE_BYTES;           // 2 stages
+  uint8_t* sDS = sV + 2 * TILE_BYTES;          // 32 KiB
+  Ctl* ctl = reinterpret_cast<Ctl*>(sDS + SQ_BYTES);
+  uint64_t* q_full = &ctl->bars[0];
+  uint64_t* kv_full = &ctl->bars[1];           // [2]
+  uint64_t* kv_empty = &ctl->bars[3];          // [2]
+  uint64_t* s_full = &ctl->bars[5];
+  uint64_t* s_empty = &ctl->bars[6];
+  uint64_t* ds_full = &ctl->bars[7];
+  uint64_t* ds_empty = &ctl->bars[8];
+  uint64_t* acc_full = &ctl->bars[9];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+  const int q0 = qb * TQ;
+  const int row_base = batch * p.S;            // token row of this batch in the [T, *] matrices
+  const int colq = head * HD, colk = p.hidden + head * HD, colv = 2 * p.hidden + head * HD;
+  int nkv = (p.S + TQ - 1) / TQ;
+  if (p.causal) nkv = min(nkv, qb + 1);
+
+  if (threadIdx.x == 0) {
+    ctl->abort_flag = 0;
+    bb::mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) { bb::mbar_init(&kv_full[i], 1); bb::mbar_init(&kv_empty[i], 1); }
+    bb::mbar_init(s_full, 1); bb::mbar_init(s_empty, 4);
+    bb::mbar_init(ds_full, 4); bb::mbar_init(ds_empty, 1);
+    bb::mbar_init(acc_full, 1);
+    bb::fence_barrier_init();
+    bb::tma_prefetch_desc(&tm_qkv); bb::tma_prefetch_desc(&tm_do);
+  }
+  if (warp == 1) { bb::tmem_alloc(&ctl->tmem_slot, 512); bb::tmem_relinquish(); }
+  bb::tc_fence_before_sync();
+  __syncthreads();
+  bb::tc_fence_after_sync();
+  const uint32_t tmem = ctl->tmem_slot;
+  const uint32_t tS = tmem, tDP = tmem + 128, tDQ = tmem + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bb::mbar_arrive_expect_tx(q_full, 2 * TILE_BYTES);
+      bb::tma_load_2d(sQ, &tm_qkv, q_full, colq, row_base + q0);
+      bb::tma_load_2d(sDO, &tm_do, q_full, colq, row_base + q0);
+      for (int j = 0; j < nkv; ++j) {
+        const int s = j & 1;
+        if (!bb::mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        bb::mbar_arrive_expect_tx(&kv_full[s], 2 * TILE_BYTES);
+        bb::tma_load_2d(sK + s * TILE_BYTES, &tm_qkv, &kv_full[s], colk, row_base + j * TQ);
+        bb::tma_load_2d(sV + s * TILE_BYTES, &tm_qkv, &kv_full[s], colv, row_base + j * TQ);
+      }
+    }
+  } else if (warp == 1) {
+    const uint32_t aQ = bb::smem_u32(sQ), aDO = bb::smem_u32(sDO), aDS = bb::smem_u32(sDS);
+    const uint32_t i_s = idesc(128, 0, 0), i_dq = idesc(64, 0, 1);
+    bool alive = bb::mbar_wait(q_full, 0, &ctl->abort_flag, p.status);
+    for (int j = 0; j < nkv && alive; ++j) {
+      const int s = j & 1;
+      const uint32_t aK = bb::smem_u32(sK + s * TILE_BYTES), aV = bb::smem_u32(sV + s * TILE_BYTES);
+      if (!bb::mbar_wait(&kv_full[s], (j >> 1) & 1, &ctl->abort_flag, p.status)) break;
+      if (!bb::mbar_wait(s_empty, (j & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+      bb::tc_fence_after_sync();
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) bb::umma_f16(tS, desc_kmajor(aQ, k), desc_kmajor(aK, k), i_s, k > 0);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) bb::umma_f16(tDP, desc_kmajor(aDO, k), desc_kmajor(aV, k), i_s, k > 0);
+        bb::umma_commit(s_full);
+      }
+      __syncwarp();
+      if (!bb::mbar_wait(ds_full, j & 1, &ctl->abort_flag, p.status)) break;
+      bb::tc_fence_after_sync();
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) bb::umma_f16(tDQ, desc_sq_kmajor(aDS, k), desc_mnmajor64(aK, k), i_dq, (j > 0 || k > 0));
+        bb::umma_commit(ds_empty);
+        bb::umma_commit(&kv_empty[s]);
+        if (j == nkv - 1) bb::umma_commit(acc_full);
+      }
+      __syncwarp();
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;                   // query row inside the tile
+    const int qrow = q0 + row;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const float* lse_g = p.lse + ((long long)batch * p.H + head) * p.S;
+    const float* delta_g = p.delta + ((long long)batch * p.H + head) * p.S;
+    const float lse = (qrow < p.S) ? lse_g[qrow] * LOG2E : 0.f;
+    const float dl = (qrow < p.S) ? delta_g[qrow] : 0.f;
+    const float sl = p.scale * LOG2E;
+    bool alive = true;
+    for (int j = 0; j < nkv && alive; ++j) {
+      if (!wait_all(s_full, j & 1, ctl, p.status)) { alive = false; break; }
+      if (!wait_all(ds_empty, (j & 1) ^ 1, ctl, p.status)) { alive = false; break; }
+      bb::tc_fence_after_sync();
+      const int c0 = j * TQ;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float sv[32], dp[32];
+        ld32(tS + lane_addr + c * 32, sv);
+        ld32(tDP + lane_addr + c * 32, dp);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int col = c0 + c * 32 + i;
+          float pv = exp2f(sv[i] * sl - lse);
+          if (col >= p.S || qrow >= p.S || (p.causal && col > qrow)) pv = 0.f;
+          dp[i] = pv * (dp[i] - dl);
+        }
+        sq_store32(sDS, row, c * 32, dp);
+      }
+      bb::tc_fence_before_sync();
+      bb::fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) { bb::mbar_arrive(s_empty); bb::mbar_arrive(ds_full); }
+    }
+    if (alive && wait_all(acc_full, 0, ctl, p.status)) {
+      bb::tc_fence_after_sync();
+      float v[64];
+      ld32(tDQ + lane_addr, v);
+      ld32(tDQ + lane_addr + 32, v + 32);
+      if (qrow < p.S) store_row64(p.dq + (long long)(row_base + qrow) * p.stride_dqkv + colq, v, p.scale);
+    }
+  }
+  bb::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) bb::tmem_dealloc(tmem, 512);
+}
+
+// ------------------------------------------------------------------ dK, dV
+// CTA owns key rows k0..k0+127 of one (batch, head); streams query / dO tiles.
+//   S^T = K Q^T, dP^T = V dO^T  ->  P^T, dS^T = P^T o (dP^T - delta)  ->  dV += P^T dO, dK += dS^T Q
+// smem: K, V (once) | Q, dO (2 stages) | P^T, dS^T [128 kv x 128 q] ; TMEM: S^T 128 | dP^T 128 | dV 64 | dK 64
+__global__ void __launch_bounds__(NTHREADS, 1)
+attn_tc_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do, const TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TILE_BYTES;
+  uint8_t* sQ = sV + TILE_BYTES;               // 2 stages
+  uint8_t* sDO = sQ + 2 * TILE_BYTES;          // 2 stages
+  uint8_t* sP = sDO + 2 * TILE_BYTES;          // 32 KiB
+  uint8_t* sDS = sP + SQ_BYTES;                // 32 KiB
+  float* s_lse = reinterpret_cast<float*>(sDS + SQ_BYTES);   // [128]
+  float* s_delta = s_lse + TQ;                               // [128]
+  Ctl* ctl = reinterpret_cast<Ctl*>(s_delta + TQ);
+  uint64_t* kv_full = &ctl->bars[0];
+  uint64_t* q_full = &ctl->bars[1];            // [2]
+  uint64_t* q_empty = &ctl->bars[3];           // [2]
+  uint64_t* s_full = &ctl->bars[5];
+  uint64_t* s_empty = &ctl->bars[6];
+  uint64_t* p_full = &ctl->bars[7];
+  uint64_t* p_empty = &ctl->bars[8];
+  uint64_t* acc_full = &ctl->bars[9];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+  const int k0 = kb * TQ;
+  const int row_base = batch * p.S;
+  const int colq = head * HD, colk = p.hidden + head * HD, colv = 2 * p.hidden + head * HD;
+  const int nq = (p.S + TQ - 1) / TQ;
+  const int qstart = p.causal ? kb : 0;
+  const int nblk = nq - qstart;
+
+  if (threadIdx.x == 0) {
+    ctl->abort_flag = 0;
+    bb::mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; ++i) { bb::mbar_init(&q_full[i], 1); bb::mbar_init(&q_empty[i], 1); }
+    bb::mbar_init(s_full, 1); bb::mbar_init(s_empty, 4);
+    bb::mbar_init(p_full, 4); bb::mbar_init(p_empty, 1);
+    bb::mbar_init(acc_full, 1);
+    bb::fence_barrier_init();
+    bb::tma_prefetch_desc(&tm_qkv); bb::tma_prefetch_desc(&tm_do);
+  }
+  if (warp == 1) { bb::tmem_alloc(&ctl->tmem_slot, 512); bb::tmem_relinquish(); }
+  bb::tc_fence_before_sync();
+  __syncthreads();
+  bb::tc_fence_after_sync();
+  const uint32_t tmem = ctl->tmem_slot;
+  const uint32_t tS = tmem, tDP = tmem + 128, tDV = tmem + 256, tDK = tmem + 320;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bb::mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
+      bb::tma_load_2d(sK, &tm_qkv, kv_full, colk, row_base + k0);
+      bb::tma_load_2d(sV, &tm_qkv, kv_full, colv, row_base + k0);
+      for (int i = 0; i < nblk; ++i) {
+        const int s = i & 1;
+        if (!bb::mbar_wait(&q_empty[s], ((i >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        bb::mbar_arrive_expect_tx(&q_full[s], 2 * TILE_BYTES);
+        bb::tma_load_2d(sQ + s * TILE_BYTES, &tm_qkv, &q_full[s], colq, row_base + (qstart + i) * TQ);
+        bb::tma_load_2d(sDO + s * TILE_BYTES, &tm_do, &q_full[s], colq, row_base + (qstart + i) * TQ);
+      }
+    }
+  } else if (warp == 1) {
+    const uint32_t aK = bb::smem_u32(sK), aV = bb::smem_u32(sV), aP = bb::smem_u32(sP), aDS = bb::smem_u32(sDS);
+    const uint32_t i_s = idesc(128, 0, 0), i_acc = idesc(64, 0, 1);
+    bool alive = bb::mbar_wait(kv_full, 0, &ctl->abort_flag, p.status);
+    for (int i = 0; i < nblk && alive; ++i) {
+      const int s = i & 1;
+      const uint32_t aQ = bb::smem_u32(sQ + s * TILE_BYTES), aDO = bb::smem_u32(sDO + s * TILE_BYTES);
+      if (!bb::mbar_wait(&q_full[s], (i >> 1) & 1, &ctl->abort_flag, p.status)) break;
+      if (!bb::mbar_wait(s_empty, (i & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+      bb::tc_fence_after_sync();
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) bb::umma_f16(tS, desc_kmajor(aK, k), desc_kmajor(aQ, k), i_s, k > 0);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) bb::umma_f16(tDP, desc_kmajor(aV, k), desc_kmajor(aDO, k), i_s, k > 0);
+        bb::umma_commit(s_full);
+      }
+      __syncwarp();
+      if (!bb::mbar_wait(p_full, i & 1, &ctl->abort_flag, p.status)) break;
+      bb::tc_fence_after_sync();
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) bb::umma_f16(tDV, desc_sq_kmajor(aP, k), desc_mnmajor64(aDO, k), i_acc, (i > 0 || k > 0));
+#pragma unroll
+        for (int k = 0; k < 8; ++k) bb::umma_f16(tDK, desc_sq_kmajor(aDS, k), desc_mnmajor64(aQ, k), i_acc, (i > 0 || k > 0));
+        bb::umma_commit(p_empty);
+        bb::umma_commit(&q_empty[s]);
+        if (i == nblk - 1) bb::umma_commit(acc_full);
+      }
+      __syncwarp();
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;                   // key row inside the tile
+    const int krow = k0 + row;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const float* lse_g = p.lse + ((long long)batch * p.H + head) * p.S;
+    const float* delta_g = p.delta + ((long long)batch * p.H + head) * p.S;
+    const float sl = p.scale * LOG2E;
+    bool alive = true;
+    for (int i = 0; i < nblk && alive; ++i) {
+      const int qc0 = (qstart + i) * TQ;
+      // per-column statistics of this query block (the previous block's readers are past
+      // their last use: they all went through the waits below)
+      bb::named_bar_sync(1, 128);
+      {
+        const int q = qc0 + row;
+        s_lse[row] = (q < p.S) ? lse_g[q] * LOG2E : 0.f;
+        s_delta[row] = (q < p.S) ? delta_g[q] : 0.f;
+      }
+      bb::named_bar_sync(1, 128);
+      if (!wait_all(s_full, i & 1, ctl, p.status)) { alive = false; break; }
+      if (!wait_all(p_empty, (i & 1) ^ 1, ctl, p.status)) { alive = false; break; }
+      bb::tc_fence_after_sync();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float sv[32], dp[32];
+        ld32(tS + lane_addr + c * 32, sv);
+        ld32(tDP + lane_addr + c * 32, dp);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int qi = c * 32 + e;
+          const int q = qc0 + qi;
+          float pv = exp2f(sv[e] * sl - s_lse[qi]);
+          if (q >= p.S || krow >= p.S || (p.causal && krow > q)) pv = 0.f;
+          sv[e] = pv;
+          dp[e] = pv * (dp[e] - s_delta[qi]);
+        }
+        sq_store32(sP, row, c * 32, sv);
+        sq_store32(sDS, row, c * 32, dp);
+      }
+      bb::tc_fence_before_sync();
+      bb::fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) { bb::mbar_arrive(s_empty); bb::mbar_arrive(p_full); }
+    }
+    if (alive && nblk > 0 && wait_all(acc_full, 0, ctl, p.status)) {
+      bb::tc_fence_after_sync();
+      float v[64];
+      ld32(tDV + lane_addr, v);
+      ld32(tDV + lane_addr + 32, v + 32);
+      if (krow < p.S) store_row64(p.dv + (long long)(row_base + krow) * p.stride_dqkv + colq, v, 1.f);
+      ld32(tDK + lane_addr, v);
+      ld32(tDK + lane_addr + 32, v + 32);
+      if (krow < p.S) store_row64(p.dk + (long long)(row_base + krow) * p.stride_dqkv + colq, v, p.scale);
+    }
+  }
+  bb::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) bb::tmem_dealloc(tmem, 512);
+}
+
+constexpr int DKV_SMEM = 6 * TILE_BYTES + 2 * SQ_BYTES + 2 * TQ * (int)sizeof(float) + (int)sizeof(Ctl) + 1024;
+// ------------------------------------------------------------------ forward
+// CTA owns query rows q0..q0+127 of one (batch, head); streams key/value tiles.
+//   S = Q K^T -> online softmax -> P (bf16, shared memory) -> PV = P V (fresh TMEM tile per block),
+//   O = O * alpha + PV kept in registers (thread == query row), so tensor memory is never rescaled.
+// smem: Q | K, V (2 stages) | P [128 q x 128 kv] ; TMEM: S 128 | PV 64
+__global__ void __launch_bounds__(NTHREADS, 1)
+attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + TILE_BYTES;               // 2 stages
+  uint8_t* sV = sK + 2 * TILE_BYTES;           // 2 stages
+  uint8_t* sP = sV + 2 * TILE_BYTES;           // 32 KiB
+  Ctl* ctl = reinterpret_cast<Ctl*>(sP + SQ_BYTES);
+  uint64_t* q_full = &ctl->bars[0];
+  uint64_t* kv_full = &ctl->bars[1];           // [2]
+  uint64_t* kv_empty = &ctl->bars[3];          // [2]
+  uint64_t* s_full = &ctl->bars[5];
+  uint64_t* s_empty = &ctl->bars[6];
+  uint64_t* p_full = &ctl->bars[7];
+  uint64_t* pv_full = &ctl->bars[8];
+  uint64_t* pv_empty = &ctl->bars[9];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+  const int q0 = qb * TQ;
+  const int row_base = batch * p.S;
+  const int colq = head * HD, colk = p.hidden + head * HD, colv = 2 * p.hidden + head * HD;
+  int nkv = (p.S + TQ - 1) / TQ;
+  if (p.causal) nkv = min(nkv, qb + 1);
+
+  if (threadIdx.x == 0) {
+    ctl->abort_flag = 0;
+    bb::mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) { bb::mbar_init(&kv_full[i], 1); bb::mbar_init(&kv_empty[i], 1); }
+    bb::mbar_init(s_full, 1); bb::mbar_init(s_empty, 4);
+    bb::mbar_init(p_full, 4); bb::mbar_init(pv_full, 1); bb::mbar_init(pv_empty, 4);
+    bb::fence_barrier_init();
+    bb::tma_prefetch_desc(&tm_qkv);
+  }
+  if (warp == 1) { bb::tmem_alloc(&ctl->tmem_slot, 256); bb::tmem_relinquish(); }
+  bb::tc_fence_before_sync();
+  __syncthreads();
+  bb::tc_fence_after_sync();
+  const uint32_t tmem = ctl->tmem_slot;
+  const uint32_t tS = tmem, tPV = tmem + 128;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bb::mbar_arrive_expect_tx(q_full, TILE_BYTES);
+      bb::tma_load_2d(sQ, &tm_qkv, q_full, colq, row_base + q0);
+      for (int j = 0; j < nkv; ++j) {
+        const int s = j & 1;
+        if (!bb::mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        bb::mbar_arrive_expect_tx(&kv_full[s], 2 * TILE_BYTES);
+        bb::tma_load_2d(sK + s * TILE_BYTES, &tm_qkv, &kv_full[s], colk, row_base + j * TQ);
+        bb::tma_load_2d(sV + s * TILE_BYTES, &tm_qkv, &kv_full[s], colv, row_base + j * TQ);
+      }
+    }
+  } else if (warp == 1) {
+    const uint32_t aQ = bb::smem_u32(sQ), aP = bb::smem_u32(sP);
+    const uint32_t i_s = idesc(128, 0, 0), i_pv = idesc(64, 0, 1);
+    bool alive = bb::mbar_wait(q_full, 0, &ctl->abort_flag, p.status);
+    for (int j = 0; j < nkv && alive; ++j) {
+      const int s = j & 1;
+      const uint32_t aK = bb::smem_u32(sK + s * TILE_BYTES), aV = bb::smem_u32(sV + s * TILE_BYTES);
+      if (!bb::mbar_wait(&kv_full[s], (j >> 1) & 1, &ctl->abort_flag, p.status)) break;
+      if (!bb::mbar_wait(s_empty, (j & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+      bb::tc_fence_after_sync();
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) bb::umma_f16(tS, desc_kmajor(aQ, k), desc_kmajor(aK, k), i_s, k > 0);
+        bb::umma_commit(s_full);
+      }
+      __syncwarp();
+      if (!bb::mbar_wait(p_full, j & 1, &ctl->abort_flag, p.status)) break;
+      if (!bb::mbar_wait(pv_empty, (j & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+      bb::tc_fence_after_sync();
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) bb::umma_f16(tPV, desc_sq_kmajor(aP, k), desc_mnmajor64(aV, k), i_pv, k > 0);
+        bb::umma_commit(pv_full);
+        bb::umma_commit(&kv_empty[s]);
+      }
+      __syncwarp();
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int qrow = q0 + row;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const float sl = p.scale * LOG2E;
+    float o[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) o[i] = 0.f;
+    float m_i = -INFINITY, l_i = 0.f;
+    bool alive = true;
+    for (int j = 0; j < nkv && alive; ++j) {
+      if (!wait_all(s_full, j & 1, ctl, p.status)) { alive = false; break; }
+      bb::tc_fence_after_sync();
+      const int c0 = j * TQ;
+      const bool need_mask = (c0 + TQ > p.S) || (p.causal && j == qb);
+      // pass 1: row maximum of the (masked) scores
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float sv[32];
+        ld32(tS + lane_addr + c * 32, sv);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int col = c0 + c * 32 + i;
+          const bool dead = need_mask && (col >= p.S || (p.causal && col > qrow));
+          mx = fmaxf(mx, dead ? -INFINITY : sv[i] * sl);
+        }
+      }
+      const float m_new = fmaxf(m_i, mx);
+      const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = exp2f(m_i - m_safe);
+      m_i = m_new;
+      // pass 2: probabilities -> shared memory (the previous P.V has been consumed: the wait on
+      // pv_full below, one block earlier, is behind us)
+      float rs = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float sv[32];
+        ld32(tS + lane_addr + c * 32, sv);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int col = c0 + c * 32 + i;
+          const bool dead = need_mask && (col >= p.S || (p.causal && col > qrow));
+          const float pv = dead ? 0.f : exp2f(sv[i] * sl - m_safe);
+          sv[i] = pv;
+          rs += pv;
+        }
+        sq_store32(sP, row, c * 32, sv);
+      }
+      l_i = l_i * alpha + rs;
+      bb::tc_fence_before_sync();
+      bb::fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) { bb::mbar_arrive(s_empty); bb::mbar_arrive(p_full); }
+      // O = O * alpha + P V
+      if (!wait_all(pv_full, j & 1, ctl, p.status)) { alive = false; break; }
+      bb::tc_fence_after_sync();
+      {
+        float pv[32];
+        ld32(tPV + lane_addr, pv);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = o[i] * alpha + pv[i];
+        ld32(tPV + lane_addr + 32, pv);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[32 + i] = o[32 + i] * alpha + pv[i];
+      }
+      bb::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) bb::mbar_arrive(pv_empty);
+    }
+    if (alive && qrow < p.S) {
+      const float inv = l_i > 0.f ? 1.f / l_i : 0.f;
+      store_row64(p.out + (long long)(row_base + qrow) * p.stride_o + colq, o, inv);
+      p.lse[((long long)batch * p.H + head) * p.S + qrow] = (l_i > 0.f) ? (m_i + log2f(l_i)) / LOG2E : -INFINITY;
+    }
+  }
+  bb::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) bb::tmem_dealloc(tmem, 256);
+}
+
+constexpr int FWD_SMEM = 5 * TILE_BYTES + SQ_BYTES + (int)sizeof(Ctl) + 1024;
+
+// delta[b, h, s] = sum_d dO * O : one warp per (token, head)
+__global__ void __launch_bounds__(256)
+attn_tc_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, const TcParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)p.B * p.S * p.H;
+  for (long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); w < total; w += (long long)gridDim.x * 8) {
+    const long long tok = w / p.H; const int head = (int)(w % p.H);
+    const uint32_t a = *reinterpret_cast<const uint32_t*>(o + tok * p.stride_o + head * HD + lane * 2);
+    const uint32_t b = *reinterpret_cast<const uint32_t*>(d_o + tok * p.stride_o + head * HD + lane * 2);
+    float s = bb::bf16_lo(a) * bb::bf16_lo(b) + bb::bf16_hi(a) * bb::bf16_hi(b);
+#pragma unroll
+    for (int k = 16; k > 0; k >>= 1) s += __shfl_xor_sync(0xffffffffu, s, k);
+    if (lane == 0) p.delta[((tok / p.S) * p.H + head) * p.S + (tok % p.S)] = s;
+  }
+}
+
+constexpr int DQ_SMEM = 6 * TILE_BYTES + SQ_BYTES + (int)sizeof(Ctl) + 1024;
+
+template <typename K> int set_smem(K kernel, int bytes) {
+  BB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  return BB_OK;
+}
+
+}  // namespace
+
+// Entry points used by attention.cu's dispatch when the head dimension is 64.
+int bb_attention_tc_fwd(const void* qkv_q, void* out, float* lse, int B, int H, int S, long long stride_qkv, long long stride_o,
+                        int causal, float scale, cudaStream_t stream) {
+  if (int rc = bbhost::bind_context()) return rc;
+  CUtensorMap tm_qkv;
+  const long long T = (long long)B * S;
+  // the packed projection [T, 3*H*64]: q, k, v blocks of H*64 columns each
+  if (int rc = bbhost::encode_2d(&tm_qkv, qkv_q, T, 3LL * H * HD, stride_qkv, HD, TQ)) return rc;
+  TcParams p = {};
+  p.out = (__nv_bfloat16*)out; p.lse = lse; p.stride_o = stride_o; p.B = B; p.H = H; p.S = S; p.hidden = H * HD;
+  p.causal = causal; p.scale = scale; p.status = bb_device_status_word();
+  static bool attr = false;
+  if (!attr) { if (int rc = set_smem(attn_tc_fwd_kernel, FWD_SMEM)) return rc; attr = true; }
+  dim3 grid((S + TQ - 1) / TQ, H, B);
+  attn_tc_fwd_kernel<<<grid, NTHREADS, FWD_SMEM, stream>>>(tm_qkv, p);
+  BB_CUDA_CHECK(cudaGetLastError());
+  return BB_OK;
+}
+
+int bb_attention_tc_bwd(const void* qkv_q, const void* out, const void* d_out, const float* lse, void* dq, void* dk, void* dv,
+                        float* delta, int B, int H, int S, long long stride_qkv, long long stride_o, long long stride_dqkv,
+                        int causal, float scale, cudaStream_t stream) {
+  if (int rc = bbhost::bind_context()) return rc;
+  CUtensorMap tm_qkv, tm_do;
+  const long long T = (long long)B * S;
+  if (int rc = bbhost::encode_2d(&tm_qkv, qkv_q, T, 3LL * H * HD, stride_qkv, HD, TQ)) return rc;
+  if (int rc = bbhost::encode_2d(&tm_do, d_out, T, (long long)H * HD, stride_o, HD, TQ)) return rc;
+  TcParams p = {};
+  p.dq = (__nv_bfloat16*)dq; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
+  p.lse = const_cast<float*>(lse); p.delta = delta; p.stride_o = stride_o; p.stride_dqkv = stride_dqkv;
+  p.B = B; p.H = H; p.S = S; p.hidden = H * HD; p.causal = causal; p.scale = scale; p.status = bb_device_status_word();
+  static bool attr = false;
+  if (!attr) {
+    if (int rc = set_smem(attn_tc_dq_kernel, DQ_SMEM)) return rc;
+    if (int rc = set_smem(attn_tc_dkv_kernel, DKV_SMEM)) return rc;
+    attr = true;
+  }
+  const long long units = T * H;
+  long long dgrid = (units + 7) / 8, cap = (long long)bb_num_sms() * 8;
+  attn_tc_delta_kernel<<<(int)(dgrid < cap ? dgrid : cap), 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out, p);
+  dim3 grid((S + TQ - 1) / TQ, H, B);
+  attn_tc_dkv_kernel<<<grid, NTHREADS, DKV_SMEM, stream>>>(tm_qkv, tm_do, p);
+  attn_tc_dq_kernel<<<grid, NTHREADS, DQ_SMEM, stream>>>(tm_qkv, tm_do, p);
+  BB_CUDA_CHECK(cudaGetLastError());
+  return BB_OK;
+}

@@ -11,15 +11,14 @@
 // (1,1) without a transpose pass.
 #include "common.cuh"
 #include "bamboo_b200.h"
-#include <cuda.h>
-#include <stdio.h>
+#include "tma_host.cuh"
 
 namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;        // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;   // TMA warp, MMA warp, two epilogue groups of four warps
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
 // Epilogue staging: output panels of 128 rows x 128 bytes (64 bf16 or 32 fp32 columns) in the
 // 128-byte-swizzled layout a TMA store expects.  Two panels: double-buffered for one output,
@@ -129,7 +128,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < C::STAGES; ++s) { bb::mbar_init(&full_bar[s], 1); bb::mbar_init(&empty_bar[s], 1); }
-    for (int a = 0; a < 2; ++a) { bb::mbar_init(&tmem_full[a], 1); bb::mbar_init(&tmem_empty[a], 4); }
+    for (int a = 0; a < 2; ++a) { bb::mbar_init(&tmem_full[a], 1); bb::mbar_init(&tmem_empty[a], 8); }
     bb::fence_barrier_init();
     bb::tma_prefetch_desc(&tmA);
     bb::tma_prefetch_desc(&tmB);
@@ -220,30 +219,35 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
   } else {
-    // ------------------------------------------------ epilogue (4 warps, one TMEM lane quarter each)
+    // ------------------------------------------------ epilogue: two groups of 4 warps (one TMEM lane quarter per warp)
     // Per 128-byte-wide output panel: TMEM -> registers -> fused math -> swizzled shared
-    // memory -> one TMA store (or fp32 add-reduction) issued by a single thread.
+    // memory -> one TMA store (or fp32 add-reduction) issued by the group's first thread.
+    // The groups take alternate panels.  GeLU (two outputs) sends the pre-activation and then the
+    // activation through the same staging panel; the GeLU math overlaps the first store's read.
+    const int eg = (warp - 2) >> 2;                // epilogue group 0 / 1
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;           // row inside the tile == TMEM lane
-    const bool leader = (threadIdx.x == 64);       // first epilogue thread issues the stores
+    const bool leader = (threadIdx.x == 64 + 128 * eg);
     const int epi = p.epi;
     const bool f32 = (epi == BB_EPI_ACCUM_F32 || epi == BB_EPI_STORE_F32);
+    const bool dual = (epi == BB_EPI_BIAS_GELU);
+    uint8_t* panel = panels + eg * PANEL_BYTES;    // this group's staging panel
     int acc = 0; uint32_t acc_phase = 0;
-    uint32_t group = 0;                            // store groups issued so far (buffer rotation)
     bool alive = true;
     for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
       const int mn = tile % num_mn;
       const int m0 = (mn % num_m) * BM, n0 = (mn / num_m) * BN;
-      // the four warps must agree (they share named barriers below): all continue or all leave
+      // the four warps of a group share named barriers below: all continue or all leave
       const bool got = bb::mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status);
-      if (!bb::named_bar_all(2, 128, got)) { alive = false; break; }
+      if (!bb::named_bar_all(3 + eg, 128, got)) { alive = false; break; }
       bb::tc_fence_after_sync();
       const int m = m0 + row;
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
       const int width = f32 ? 32 : 64;             // columns per panel
       const int npanels = BN / width;
+      const int first = eg, step = 2;
 #pragma unroll 1
-      for (int pn = 0; pn < npanels; ++pn) {
+      for (int pn = first; pn < npanels; pn += step) {
         const int nb = n0 + pn * width;
         float v[64];
         {
@@ -259,29 +263,31 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             for (int i = 0; i < 32; ++i) v[32 + i] = __uint_as_float(r[i]);
           }
         }
-        if (pn == npanels - 1) {
-          // accumulator fully read: hand it back to the MMA warp before the last stores
+        if (pn + step >= npanels) {
+          // this group has read its share of the accumulator: hand it back before the last stores
           bb::tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) bb::mbar_arrive(&tmem_empty[acc]);
         }
         if (nb >= p.N) continue;                   // panel entirely outside the matrix (uniform)
-        const bool dual = (epi == BB_EPI_BIAS_GELU);
-        uint8_t* pD = panels + (dual ? 0 : (group & 1) * PANEL_BYTES);
-        uint8_t* pD2 = panels + PANEL_BYTES;
-        // the panel about to be overwritten must have been read by its previous store
-        if (leader) { if (dual) bb::bulk_wait_group_read<0>(); else bb::bulk_wait_group_read<1>(); }
-        bb::named_bar_sync(1, 128);
+        // the panel must have been read by its previous store before it is overwritten
+        if (leader) bb::bulk_wait_group_read<0>();
+        bb::named_bar_sync(1 + eg, 128);
         if (f32) {
-          panel_store_row_f32(pD, row, v);
+          panel_store_row_f32(panel, row, v);
         } else {
-          if (epi == BB_EPI_BIAS || epi == BB_EPI_BIAS_GELU || epi == BB_EPI_BIAS_RESIDUAL) add_bias<64>(p, nb, v);
-          if (epi == BB_EPI_BIAS_GELU) {
-            panel_store_row_bf16(pD2, row, v);
+          if (epi == BB_EPI_BIAS || dual || epi == BB_EPI_BIAS_RESIDUAL) add_bias<64>(p, nb, v);
+          if (dual) {
+            panel_store_row_bf16(panel, row, v);   // pre-activation first
+            bb::fence_proxy_async();
+            bb::named_bar_sync(1 + eg, 128);
+            if (leader) { bb::tma_store_2d(&tmD2, panel, nb, m0); bb::bulk_commit_group(); }
             // GeLU of the bf16-rounded pre-activation: forward and backward (which re-reads the
             // stored pre-activation) see the same argument
 #pragma unroll
             for (int i = 0; i < 64; ++i) v[i] = bb::gelu_tanh(__bfloat162float(__float2bfloat16(v[i])));
+            if (leader) bb::bulk_wait_group_read<0>();
+            bb::named_bar_sync(1 + eg, 128);
           } else if (epi == BB_EPI_MUL_DGELU || epi == BB_EPI_BIAS_RESIDUAL) {
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
@@ -296,17 +302,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
               }
             }
           }
-          panel_store_row_bf16(pD, row, v);
+          panel_store_row_bf16(panel, row, v);
         }
         bb::fence_proxy_async();                   // generic-proxy writes -> visible to the TMA engine
-        bb::named_bar_sync(1, 128);
+        bb::named_bar_sync(1 + eg, 128);
         if (leader) {
-          if (epi == BB_EPI_ACCUM_F32) bb::tma_reduce_add_2d(&tmD, pD, nb, m0);
-          else bb::tma_store_2d(&tmD, pD, nb, m0);
-          if (epi == BB_EPI_BIAS_GELU) bb::tma_store_2d(&tmD2, pD2, nb, m0);
+          if (epi == BB_EPI_ACCUM_F32) bb::tma_reduce_add_2d(&tmD, panel, nb, m0);
+          else bb::tma_store_2d(&tmD, panel, nb, m0);
           bb::bulk_commit_group();
         }
-        ++group;
       }
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
@@ -319,44 +323,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 }
 
 // ---------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn) return fn;
-  void* sym = nullptr;
-  cudaDriverEntryPointQueryResult qres;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
-      qres != cudaDriverEntryPointSuccess)
-    return nullptr;
-  fn = reinterpret_cast<EncodeTiledFn>(sym);
-  return fn;
-}
-
-// 2-D tensor map over a row-major [rows, cols] matrix (bf16, or fp32 when f32 != 0) with leading
-// dimension ld (elements); 128-byte swizzle.
-int encode_2d(CUtensorMap* tm, const void* base, long long rows, long long cols, long long ld, int box_cols, int box_rows,
-              int f32 = 0) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (!fn) { bb_set_last_error_msg("cuTensorMapEncodeTiled entry point not available"); return BB_ERR_CUDA; }
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * (f32 ? 4 : 2)};
-  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(tm, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    char msg[256];
-    snprintf(msg, sizeof(msg), "cuTensorMapEncodeTiled failed with CUresult %d (base %p, rows %lld, cols %lld, ld %lld, box %dx%d, "
-             "f32 %d); operands need a 16-byte aligned base and row pitch", (int)r, base, rows, cols, ld, box_cols, box_rows, f32);
-    bb_set_last_error_msg(msg);
-    return BB_ERR_INVALID_ARG;
-  }
-  return BB_OK;
-}
+using bbhost::encode_2d;
 
 template <int BN>
 int launch(const bb_gemm_desc* g, cudaStream_t stream) {
@@ -443,8 +410,7 @@ extern "C" int bb_gemm_bf16(const bb_gemm_desc* g, void* stream) {
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   // cuTensorMapEncodeTiled is a driver call and needs a context bound to the calling thread;
   // a thread that has only ever set its device (autograd worker threads) has none yet.
-  static thread_local bool ctx_bound = false;
-  if (!ctx_bound) { BB_CUDA_CHECK(cudaFree(0)); ctx_bound = true; }
+  if (int rc = bbhost::bind_context()) return rc;
   int bn = g->tile_n;
   if (bn == 0) {
     // 256-wide tiles halve the A re-reads; use them when they still fill the machine

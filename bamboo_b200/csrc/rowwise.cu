@@ -128,6 +128,74 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
   }
 }
 
+// Same computation with the per-lane dgamma/dbeta partial sums and the row's data held in
+// registers (hidden sizes that are a multiple of 256 up to 1024): shared memory is only touched
+// once per CTA, when the warps' partials are combined.
+template <int NCH>
+__global__ void __launch_bounds__(WARPS * 32)
+layernorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                         const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
+                         const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
+                         __nv_bfloat16* __restrict__ dx, float* __restrict__ partials, int rows) {
+  constexpr int h = NCH * 256;
+  extern __shared__ float acc[];  // [warps][2][h]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = blockDim.x >> 5;
+  float ag[NCH * 8], ab[NCH * 8], g[NCH * 8];
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    unpack8(__ldg(reinterpret_cast<const uint4*>(gamma) + lane + 32 * j), g + 8 * j);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { ag[8 * j + i] = 0.f; ab[8 * j + i] = 0.f; }
+  }
+  for (int row = blockIdx.x * nwarps + warp; row < rows; row += gridDim.x * nwarps) {
+    const uint4* dyr = reinterpret_cast<const uint4*>(dy + (size_t)row * h);
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * h);
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    uint4 qd[NCH], qx[NCH];
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) { qd[j] = dyr[lane + 32 * j]; qx[j] = xr[lane + 32 * j]; }
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      float d[8], f[8];
+      unpack8(qd[j], d); unpack8(qx[j], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { const float t = d[i] * g[8 * j + i]; s1 += t; s2 += t * (f[i] - mean) * rstd; }
+    }
+    const float c1 = warp_sum(s1) * (1.f / h), c2 = warp_sum(s2) * (1.f / h);
+    uint4* dxr = reinterpret_cast<uint4*>(dx + (size_t)row * h);
+    const uint4* rr = dres ? reinterpret_cast<const uint4*>(dres + (size_t)row * h) : nullptr;
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      float d[8], f[8], o[8], r[8];
+      unpack8(qd[j], d); unpack8(qx[j], f);
+      if (rr) unpack8(rr[lane + 32 * j], r);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float xh = (f[i] - mean) * rstd;
+        o[i] = rstd * (d[i] * g[8 * j + i] - c1 - xh * c2) + (rr ? r[i] : 0.f);
+        ag[8 * j + i] += d[i] * xh;
+        ab[8 * j + i] += d[i];
+      }
+      dxr[lane + 32 * j] = pack8(o);
+    }
+  }
+  float* my_g = acc + (size_t)warp * 2 * h;
+  float* my_b = my_g + h;
+#pragma unroll
+  for (int j = 0; j < NCH; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { my_g[(lane + 32 * j) * 8 + i] = ag[8 * j + i]; my_b[(lane + 32 * j) * 8 + i] = ab[8 * j + i]; }
+  __syncthreads();
+  float* out = partials + (size_t)blockIdx.x * 2 * h;
+  for (int j = threadIdx.x; j < 2 * h; j += blockDim.x) {
+    float s = 0.f;
+    for (int w = 0; w < nwarps; ++w) s += acc[(size_t)w * 2 * h + j];
+    out[j] = s;
+  }
+}
+
 // out[j] += sum_p partials[p * stride + j].  A 32-column x 8-way block: eight threads share
 // a column, each sums every eighth partial, shared memory combines them in a fixed order
 // (deterministic).
@@ -258,6 +326,31 @@ int ln_bwd_grid(int rows, int h) {
 }
 }  // namespace
 
+namespace {
+// launches the backward main kernel (register variant when the hidden size allows it)
+int ln_bwd_main(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, const void* dres,
+                void* dx, float* ws, int rows, int h, int grid, int warps, cudaStream_t s) {
+  const size_t smem = (size_t)warps * 2 * h * sizeof(float);
+  static bool attr = false;
+  if (!attr) {
+    BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_reg_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+    BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_reg_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+    attr = true;
+  }
+#define BB_LN_ARGS (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, mean, rstd, \
+                   (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, ws, rows
+  if (h == 256) layernorm_bwd_reg_kernel<1><<<grid, warps * 32, smem, s>>>(BB_LN_ARGS);
+  else if (h == 512) layernorm_bwd_reg_kernel<2><<<grid, warps * 32, smem, s>>>(BB_LN_ARGS);
+  else if (h == 768) layernorm_bwd_reg_kernel<3><<<grid, warps * 32, smem, s>>>(BB_LN_ARGS);
+  else if (h == 1024) layernorm_bwd_reg_kernel<4><<<grid, warps * 32, smem, s>>>(BB_LN_ARGS);
+  else layernorm_bwd_kernel<<<grid, warps * 32, smem, s>>>(BB_LN_ARGS, h);
+#undef BB_LN_ARGS
+  BB_CUDA_CHECK(cudaGetLastError());
+  return BB_OK;
+}
+}  // namespace
+
 extern "C" long long bb_layernorm_bwd_workspace_bytes(int rows, int h) {
   if (rows <= 0 || h <= 0 || ln_bwd_warps(h) < 1) return 0;
   return (long long)ln_bwd_grid(rows, h) * 2 * h * (long long)sizeof(float);
@@ -277,18 +370,9 @@ extern "C" int bb_layernorm_bwd(const void* dy, const void* x, const void* gamma
     return BB_ERR_INVALID_ARG;
   }
   cudaStream_t s = (cudaStream_t)stream;
-  static bool attr = false;
-  if (!attr) {
-    BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    attr = true;
-  }
   const int grid = ln_bwd_grid(rows, h);
-  const size_t smem = (size_t)warps * 2 * h * sizeof(float);
   float* ws = (float*)workspace;
-  layernorm_bwd_kernel<<<grid, warps * 32, smem, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
-                                                      (const __nv_bfloat16*)gamma, mean, rstd, (const __nv_bfloat16*)dres,
-                                                      (__nv_bfloat16*)dx, ws, rows, h);
-  BB_CUDA_CHECK(cudaGetLastError());
+  if (int rc = ln_bwd_main(dy, x, gamma, mean, rstd, dres, dx, ws, rows, h, grid, warps, s)) return rc;
   reduce_partials_kernel<<<(h + 31) / 32, 256, 0, s>>>(ws, dgamma, grid, h, 2LL * h);
   reduce_partials_kernel<<<(h + 31) / 32, 256, 0, s>>>(ws + h, dbeta, grid, h, 2LL * h);
   BB_CUDA_CHECK(cudaGetLastError());
@@ -340,19 +424,10 @@ extern "C" int bb_layernorm_bwd_static(const void* dy, const void* x, const void
   float* ws = ln_static_scratch_ptr();
   if (!ws) return BB_ERR_CUDA;
   cudaStream_t s = (cudaStream_t)stream;
-  static bool attr = false;
-  if (!attr) {
-    BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    attr = true;
-  }
   const int grid = ln_bwd_grid(rows, h);
-  const size_t smem = (size_t)warps * 2 * h * sizeof(float);
   // every partial row that the reduction reads is rewritten by this launch, so the scratch
   // needs no clearing although it still holds the previous call's sums
-  layernorm_bwd_kernel<<<grid, warps * 32, smem, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
-                                                      (const __nv_bfloat16*)gamma, mean, rstd, (const __nv_bfloat16*)dres,
-                                                      (__nv_bfloat16*)dx, ws, rows, h);
-  BB_CUDA_CHECK(cudaGetLastError());
+  if (int rc = ln_bwd_main(dy, x, gamma, mean, rstd, dres, dx, ws, rows, h, grid, warps, s)) return rc;
   reduce_partials_kernel<<<(h + 31) / 32, 256, 0, s>>>(ws, dgamma, grid, h, 2LL * h);
   reduce_partials_kernel<<<(h + 31) / 32, 256, 0, s>>>(ws + h, dbeta, grid, h, 2LL * h);
   BB_CUDA_CHECK(cudaGetLastError());

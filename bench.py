@@ -187,8 +187,18 @@ def main():
     rc = args.rc if args.rc != "auto" else ("eager" if world > 1 else "off")
     if world == 1:
         rc = "off"
+    # stage boundaries balanced by forward FLOPs per token (the embedding costs nothing, the
+    # vocabulary head about as much as 2hV / (24h^2 + 4sh) blocks)
+    from bamboo_b200.partition import partition_balanced
+    h = cfg.hidden
+    head_cost = 2.0 * h * cfg.vocab / (24.0 * h * h + 4.0 * cfg.seq * h)
+    costs = [0.0] + [1.0] * cfg.layers + [0.0, head_cost]
+    parts = partition_balanced([int(c * 1000) for c in costs], world)
+    for st in range(world - 1, 0, -1):          # no stage may be empty: steal the predecessor's last layer
+        if parts[st] >= parts[st + 1]:
+            parts[st] = parts[st + 1] - 1
     model = PipelineModule(models.transformer_layer_specs(cfg, 0), num_stages=world, loss_fn=models.transformer_loss(cfg),
-                           partition_method="type:TransformerBlock" if world > 1 else "uniform")
+                           partition_method="custom", custom_partitions=parts)
     engine, *_ = api.initialize(model=model, config={
         "train_micro_batch_size_per_gpu": MICRO_BATCH, "gradient_accumulation_steps": MICRO_BATCHES,
         "bf16": {"enabled": True}, "optimizer": {"type": "Adam", "params": {"lr": 1e-4}},
@@ -275,7 +285,7 @@ def main():
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{args.model} ({cfg.layers} layers, hidden {cfg.hidden}, seq {cfg.seq}, vocab {cfg.vocab}) "
                                f"pipeline step, {world} stage(s) x 1 replica, micro-batch {MICRO_BATCH} x {MICRO_BATCHES}",
-                   "rc": rc, "parallelism": f"pp{world}", "global_batch": MICRO_BATCH * MICRO_BATCHES, "seq_len": cfg.seq,
+                   "rc": rc, "parallelism": f"pp{world}", "stage_boundaries": parts, "global_batch": MICRO_BATCH * MICRO_BATCHES, "seq_len": cfg.seq,
                    "l2": "working set per step is far larger than L2 (no flush needed)"},
         "e2e": {"value": e2e, "unit": METRIC, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                 "ms_per_step": ms_e2e / args.steps},
