@@ -585,6 +585,349 @@ attn_tc_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* _
   }
 }
 
+// =====================================================================================
+// Pipelined backward kernels: 64-wide sub-blocks, every hand-off double-buffered, two compute
+// groups (warps 2-5 and 6-9) that take alternate sub-blocks, so the tensor core always has the
+// next S / dP and the previous dK / dV / dQ update queued while a group does its elementwise work.
+// =====================================================================================
+constexpr int SUB = 64;                          // streamed rows per sub-block
+constexpr int SUB_BYTES = SUB * HD * 2;          // 8 KiB: [64 x 64] bf16
+constexpr int NT2 = 320;
+
+// ------------------------------------------------------------------ dQ (pipelined)
+// smem: Q, dO [128 x 64] | K, V sub-tiles [64 x 64] x 3 stages | dS [128 q x 64 kv] x 2
+// TMEM: S 2 x 64 | dP 2 x 64 | dQ 64
+__global__ void __launch_bounds__(NT2, 1)
+attn_tc_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
+                   const __grid_constant__ CUtensorMap tm_do, const TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sDO = sQ + TILE_BYTES;
+  uint8_t* sK = sDO + TILE_BYTES;              // 3 stages x 8 KiB
+  uint8_t* sV = sK + 3 * SUB_BYTES;            // 3 stages x 8 KiB
+  uint8_t* sDS = sV + 3 * SUB_BYTES;           // 2 x 16 KiB
+  Ctl* ctl = reinterpret_cast<Ctl*>(sDS + 2 * TILE_BYTES);
+  uint64_t* q_full = &ctl->bars[0];
+  uint64_t* kv_full = &ctl->bars[1];           // [3]
+  uint64_t* kv_empty = &ctl->bars[4];          // [3]
+  uint64_t* s_full = &ctl->bars[7];            // [2]
+  uint64_t* s_empty = &ctl->bars[9];           // [2]
+  uint64_t* ds_full = &ctl->bars[11];          // [2]
+  uint64_t* ds_empty = &ctl->bars[13];         // [2]
+  uint64_t* acc_full = &ctl->bars[15];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+  const int q0 = qb * TQ;
+  const int row_base = batch * p.S;
+  const int colq = head * HD, colk = p.hidden + head * HD, colv = 2 * p.hidden + head * HD;
+  int nblk = (p.S + SUB - 1) / SUB;
+  if (p.causal) nblk = min(nblk, (q0 + TQ) / SUB);
+
+  if (threadIdx.x == 0) {
+    ctl->abort_flag = 0;
+    bb::mbar_init(q_full, 1);
+    for (int i = 0; i < 3; ++i) { bb::mbar_init(&kv_full[i], 1); bb::mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) {
+      bb::mbar_init(&s_full[i], 1); bb::mbar_init(&s_empty[i], 4);
+      bb::mbar_init(&ds_full[i], 4); bb::mbar_init(&ds_empty[i], 1);
+    }
+    bb::mbar_init(acc_full, 1);
+    bb::fence_barrier_init();
+    bb::tma_prefetch_desc(&tm_q); bb::tma_prefetch_desc(&tm_kv); bb::tma_prefetch_desc(&tm_do);
+  }
+  if (warp == 1) { bb::tmem_alloc(&ctl->tmem_slot, 512); bb::tmem_relinquish(); }
+  bb::tc_fence_before_sync();
+  __syncthreads();
+  bb::tc_fence_after_sync();
+  const uint32_t tmem = ctl->tmem_slot;
+  const uint32_t tDQ = tmem + 256;             // S[b] at tmem + 64 b, dP[b] at tmem + 128 + 64 b
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bb::mbar_arrive_expect_tx(q_full, 2 * TILE_BYTES);
+      bb::tma_load_2d(sQ, &tm_q, q_full, colq, row_base + q0);
+      bb::tma_load_2d(sDO, &tm_do, q_full, colq, row_base + q0);
+      for (int j = 0; j < nblk; ++j) {
+        const int s = j % 3;
+        if (!bb::mbar_wait(&kv_empty[s], ((j / 3) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        bb::mbar_arrive_expect_tx(&kv_full[s], 2 * SUB_BYTES);
+        bb::tma_load_2d(sK + s * SUB_BYTES, &tm_kv, &kv_full[s], colk, row_base + j * SUB);
+        bb::tma_load_2d(sV + s * SUB_BYTES, &tm_kv, &kv_full[s], colv, row_base + j * SUB);
+      }
+    }
+  } else if (warp == 1) {
+    const uint32_t aQ = bb::smem_u32(sQ), aDO = bb::smem_u32(sDO);
+    const uint32_t i_s = idesc(64, 0, 0), i_dq = idesc(64, 0, 1);
+    bool alive = bb::mbar_wait(q_full, 0, &ctl->abort_flag, p.status);
+    // software pipeline: scores of sub-block j are issued before the dQ update of sub-block j-1
+    for (int j = 0; j <= nblk && alive; ++j) {
+      if (j < nblk) {
+        const int s = j % 3, b = j & 1;
+        const uint32_t aK = bb::smem_u32(sK + s * SUB_BYTES), aV = bb::smem_u32(sV + s * SUB_BYTES);
+        if (!bb::mbar_wait(&kv_full[s], (j / 3) & 1, &ctl->abort_flag, p.status)) break;
+        if (!bb::mbar_wait(&s_empty[b], ((j >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        bb::tc_fence_after_sync();
+        if (lane == 0) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) bb::umma_f16(tmem + 64 * b, desc_kmajor(aQ, k), desc_kmajor(aK, k), i_s, k > 0);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) bb::umma_f16(tmem + 128 + 64 * b, desc_kmajor(aDO, k), desc_kmajor(aV, k), i_s, k > 0);
+          bb::umma_commit(&s_full[b]);
+        }
+        __syncwarp();
+      }
+      if (j >= 1) {
+        const int jj = j - 1, s = jj % 3, b = jj & 1;
+        const uint32_t aK = bb::smem_u32(sK + s * SUB_BYTES), aDS = bb::smem_u32(sDS + b * TILE_BYTES);
+        if (!bb::mbar_wait(&ds_full[b], (jj >> 1) & 1, &ctl->abort_flag, p.status)) break;
+        bb::tc_fence_after_sync();
+        if (lane == 0) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) bb::umma_f16(tDQ, desc_kmajor(aDS, k), desc_mnmajor64(aK, k), i_dq, (jj > 0 || k > 0));
+          bb::umma_commit(&ds_empty[b]);
+          bb::umma_commit(&kv_empty[s]);
+          if (jj == nblk - 1) bb::umma_commit(acc_full);
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    const int g = (warp - 2) >> 2;                           // compute group = buffer index
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int qrow = q0 + row;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const float* lse_g = p.lse + ((long long)batch * p.H + head) * p.S;
+    const float* delta_g = p.delta + ((long long)batch * p.H + head) * p.S;
+    const float lse = (qrow < p.S) ? lse_g[qrow] * LOG2E : 0.f;
+    const float dl = (qrow < p.S) ? delta_g[qrow] : 0.f;
+    const float sl = p.scale * LOG2E;
+    uint8_t* myDS = sDS + g * TILE_BYTES;
+    const uint32_t tS = tmem + 64 * g, tDP = tmem + 128 + 64 * g;
+    bool alive = true;
+    int n = 0;                                               // this group's iteration count
+    for (int j = g; j < nblk && alive; j += 2, ++n) {
+      bool ok = bb::mbar_wait(&s_full[g], n & 1, &ctl->abort_flag, p.status);
+      ok = ok && bb::mbar_wait(&ds_empty[g], (n & 1) ^ 1, &ctl->abort_flag, p.status);
+      if (!bb::named_bar_all(3 + g, 128, ok)) { alive = false; break; }
+      bb::tc_fence_after_sync();
+      const int c0 = j * SUB;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        float sv[32], dp[32];
+        ld32(tS + lane_addr + c * 32, sv);
+        ld32(tDP + lane_addr + c * 32, dp);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int col = c0 + c * 32 + i;
+          float pv = exp2f(sv[i] * sl - lse);
+          if (col >= p.S || qrow >= p.S || (p.causal && col > qrow)) pv = 0.f;
+          dp[i] = pv * (dp[i] - dl);
+        }
+        sq_store32(myDS, row, c * 32, dp);
+      }
+      bb::tc_fence_before_sync();
+      bb::fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) { bb::mbar_arrive(&s_empty[g]); bb::mbar_arrive(&ds_full[g]); }
+    }
+    const bool fin = alive && bb::mbar_wait(acc_full, 0, &ctl->abort_flag, p.status);
+    if (bb::named_bar_all(3 + g, 128, fin) && g == 0) {
+      bb::tc_fence_after_sync();
+      float v[64];
+      ld32(tDQ + lane_addr, v);
+      ld32(tDQ + lane_addr + 32, v + 32);
+      if (qrow < p.S) store_row64(p.dq + (long long)(row_base + qrow) * p.stride_dqkv + colq, v, p.scale);
+    }
+  }
+  bb::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) bb::tmem_dealloc(tmem, 512);
+}
+
+constexpr int DQ2_SMEM = 2 * TILE_BYTES + 6 * SUB_BYTES + 2 * TILE_BYTES + (int)sizeof(Ctl) + 1024;
+
+// ------------------------------------------------------------------ dK, dV (pipelined)
+// smem: K, V [128 x 64] | Q, dO sub-tiles [64 x 64] x 3 stages | P^T, dS^T [128 kv x 64 q] x 2 each
+//       | per-group lse / delta of the sub-block's 64 query columns
+// TMEM: S^T 2 x 64 | dP^T 2 x 64 | dV 64 | dK 64
+__global__ void __launch_bounds__(NT2, 1)
+attn_tc_dkv2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_constant__ CUtensorMap tm64,
+                    const __grid_constant__ CUtensorMap tm_do64, const TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TILE_BYTES;
+  uint8_t* sQ = sV + TILE_BYTES;               // 3 stages x 8 KiB
+  uint8_t* sDO = sQ + 3 * SUB_BYTES;           // 3 stages x 8 KiB
+  uint8_t* sP = sDO + 3 * SUB_BYTES;           // 2 x 16 KiB
+  uint8_t* sDS = sP + 2 * TILE_BYTES;          // 2 x 16 KiB
+  float* s_lse = reinterpret_cast<float*>(sDS + 2 * TILE_BYTES);   // [2][64]
+  float* s_delta = s_lse + 2 * SUB;                                // [2][64]
+  Ctl* ctl = reinterpret_cast<Ctl*>(s_delta + 2 * SUB);
+  uint64_t* kv_full = &ctl->bars[0];
+  uint64_t* q_full = &ctl->bars[1];            // [3]
+  uint64_t* q_empty = &ctl->bars[4];           // [3]
+  uint64_t* s_full = &ctl->bars[7];            // [2]
+  uint64_t* s_empty = &ctl->bars[9];           // [2]
+  uint64_t* p_full = &ctl->bars[11];           // [2]
+  uint64_t* p_empty = &ctl->bars[13];          // [2]
+  uint64_t* acc_full = &ctl->bars[15];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+  const int k0 = kb * TQ;
+  const int row_base = batch * p.S;
+  const int colq = head * HD, colk = p.hidden + head * HD, colv = 2 * p.hidden + head * HD;
+  const int nq = (p.S + SUB - 1) / SUB;
+  const int qstart = p.causal ? (k0 / SUB) : 0;
+  const int nblk = nq - qstart;
+
+  if (threadIdx.x == 0) {
+    ctl->abort_flag = 0;
+    bb::mbar_init(kv_full, 1);
+    for (int i = 0; i < 3; ++i) { bb::mbar_init(&q_full[i], 1); bb::mbar_init(&q_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) {
+      bb::mbar_init(&s_full[i], 1); bb::mbar_init(&s_empty[i], 4);
+      bb::mbar_init(&p_full[i], 4); bb::mbar_init(&p_empty[i], 1);
+    }
+    bb::mbar_init(acc_full, 1);
+    bb::fence_barrier_init();
+    bb::tma_prefetch_desc(&tm128); bb::tma_prefetch_desc(&tm64); bb::tma_prefetch_desc(&tm_do64);
+  }
+  if (warp == 1) { bb::tmem_alloc(&ctl->tmem_slot, 512); bb::tmem_relinquish(); }
+  bb::tc_fence_before_sync();
+  __syncthreads();
+  bb::tc_fence_after_sync();
+  const uint32_t tmem = ctl->tmem_slot;
+  const uint32_t tDV = tmem + 256, tDK = tmem + 320;   // S^T[b] at tmem + 64 b, dP^T[b] at tmem + 128 + 64 b
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bb::mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
+      bb::tma_load_2d(sK, &tm128, kv_full, colk, row_base + k0);
+      bb::tma_load_2d(sV, &tm128, kv_full, colv, row_base + k0);
+      for (int i = 0; i < nblk; ++i) {
+        const int s = i % 3;
+        if (!bb::mbar_wait(&q_empty[s], ((i / 3) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        bb::mbar_arrive_expect_tx(&q_full[s], 2 * SUB_BYTES);
+        bb::tma_load_2d(sQ + s * SUB_BYTES, &tm64, &q_full[s], colq, row_base + (qstart + i) * SUB);
+        bb::tma_load_2d(sDO + s * SUB_BYTES, &tm_do64, &q_full[s], colq, row_base + (qstart + i) * SUB);
+      }
+    }
+  } else if (warp == 1) {
+    const uint32_t aK = bb::smem_u32(sK), aV = bb::smem_u32(sV);
+    const uint32_t i_s = idesc(64, 0, 0), i_acc = idesc(64, 0, 1);
+    bool alive = bb::mbar_wait(kv_full, 0, &ctl->abort_flag, p.status);
+    for (int i = 0; i <= nblk && alive; ++i) {
+      if (i < nblk) {
+        const int s = i % 3, b = i & 1;
+        const uint32_t aQ = bb::smem_u32(sQ + s * SUB_BYTES), aDO = bb::smem_u32(sDO + s * SUB_BYTES);
+        if (!bb::mbar_wait(&q_full[s], (i / 3) & 1, &ctl->abort_flag, p.status)) break;
+        if (!bb::mbar_wait(&s_empty[b], ((i >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        bb::tc_fence_after_sync();
+        if (lane == 0) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) bb::umma_f16(tmem + 64 * b, desc_kmajor(aK, k), desc_kmajor(aQ, k), i_s, k > 0);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) bb::umma_f16(tmem + 128 + 64 * b, desc_kmajor(aV, k), desc_kmajor(aDO, k), i_s, k > 0);
+          bb::umma_commit(&s_full[b]);
+        }
+        __syncwarp();
+      }
+      if (i >= 1) {
+        const int ii = i - 1, s = ii % 3, b = ii & 1;
+        const uint32_t aQ = bb::smem_u32(sQ + s * SUB_BYTES), aDO = bb::smem_u32(sDO + s * SUB_BYTES);
+        const uint32_t aP = bb::smem_u32(sP + b * TILE_BYTES), aDS = bb::smem_u32(sDS + b * TILE_BYTES);
+        if (!bb::mbar_wait(&p_full[b], (ii >> 1) & 1, &ctl->abort_flag, p.status)) break;
+        bb::tc_fence_after_sync();
+        if (lane == 0) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) bb::umma_f16(tDV, desc_kmajor(aP, k), desc_mnmajor64(aDO, k), i_acc, (ii > 0 || k > 0));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) bb::umma_f16(tDK, desc_kmajor(aDS, k), desc_mnmajor64(aQ, k), i_acc, (ii > 0 || k > 0));
+          bb::umma_commit(&p_empty[b]);
+          bb::umma_commit(&q_empty[s]);
+          if (ii == nblk - 1) bb::umma_commit(acc_full);
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    const int g = (warp - 2) >> 2;
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;                   // key row inside the tile
+    const int gt = threadIdx.x - 64 - 128 * g;             // thread index inside the group
+    const int krow = k0 + row;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const float* lse_g = p.lse + ((long long)batch * p.H + head) * p.S;
+    const float* delta_g = p.delta + ((long long)batch * p.H + head) * p.S;
+    const float sl = p.scale * LOG2E;
+    uint8_t* myP = sP + g * TILE_BYTES;
+    uint8_t* myDS = sDS + g * TILE_BYTES;
+    float* my_lse = s_lse + g * SUB;
+    float* my_delta = s_delta + g * SUB;
+    const uint32_t tS = tmem + 64 * g, tDP = tmem + 128 + 64 * g;
+    bool alive = true;
+    int n = 0;
+    for (int i = g; i < nblk && alive; i += 2, ++n) {
+      const int qc0 = (qstart + i) * SUB;
+      // statistics of this sub-block's 64 query columns (the group's previous readers are past
+      // their last use once everybody is through this barrier)
+      bb::named_bar_sync(1 + g, 128);
+      if (gt < SUB) {
+        const int q = qc0 + gt;
+        my_lse[gt] = (q < p.S) ? lse_g[q] * LOG2E : 0.f;
+        my_delta[gt] = (q < p.S) ? delta_g[q] : 0.f;
+      }
+      bb::named_bar_sync(1 + g, 128);
+      bool ok = bb::mbar_wait(&s_full[g], n & 1, &ctl->abort_flag, p.status);
+      ok = ok && bb::mbar_wait(&p_empty[g], (n & 1) ^ 1, &ctl->abort_flag, p.status);
+      if (!bb::named_bar_all(3 + g, 128, ok)) { alive = false; break; }
+      bb::tc_fence_after_sync();
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        float sv[32], dp[32];
+        ld32(tS + lane_addr + c * 32, sv);
+        ld32(tDP + lane_addr + c * 32, dp);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int qi = c * 32 + e;
+          const int q = qc0 + qi;
+          float pv = exp2f(sv[e] * sl - my_lse[qi]);
+          if (q >= p.S || krow >= p.S || (p.causal && krow > q)) pv = 0.f;
+          sv[e] = pv;
+          dp[e] = pv * (dp[e] - my_delta[qi]);
+        }
+        sq_store32(myP, row, c * 32, sv);
+        sq_store32(myDS, row, c * 32, dp);
+      }
+      bb::tc_fence_before_sync();
+      bb::fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) { bb::mbar_arrive(&s_empty[g]); bb::mbar_arrive(&p_full[g]); }
+    }
+    const bool fin = alive && nblk > 0 && bb::mbar_wait(acc_full, 0, &ctl->abort_flag, p.status);
+    if (bb::named_bar_all(3 + g, 128, fin)) {
+      bb::tc_fence_after_sync();
+      float v[64];
+      // the two groups split the final stores: group 0 writes dV, group 1 writes dK
+      const uint32_t src = (g == 0) ? tDV : tDK;
+      ld32(src + lane_addr, v);
+      ld32(src + lane_addr + 32, v + 32);
+      __nv_bfloat16* dst = (g == 0) ? p.dv : p.dk;
+      if (krow < p.S) store_row64(dst + (long long)(row_base + krow) * p.stride_dqkv + colq, v, g == 0 ? 1.f : p.scale);
+    }
+  }
+  bb::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) bb::tmem_dealloc(tmem, 512);
+}
+
+constexpr int DKV2_SMEM = 2 * TILE_BYTES + 6 * SUB_BYTES + 4 * TILE_BYTES + 4 * SUB * (int)sizeof(float) + (int)sizeof(Ctl) + 1024;
+
 constexpr int DQ_SMEM = 6 * TILE_BYTES + SQ_BYTES + (int)sizeof(Ctl) + 1024;
 
 template <typename K> int set_smem(K kernel, int bytes) {
@@ -625,18 +968,21 @@ int bb_attention_tc_bwd(const void* qkv_q, const void* out, const void* d_out, c
   p.dq = (__nv_bfloat16*)dq; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
   p.lse = const_cast<float*>(lse); p.delta = delta; p.stride_o = stride_o; p.stride_dqkv = stride_dqkv;
   p.B = B; p.H = H; p.S = S; p.hidden = H * HD; p.causal = causal; p.scale = scale; p.status = bb_device_status_word();
+  CUtensorMap tm_qkv64, tm_do64;
+  if (int rc = bbhost::encode_2d(&tm_qkv64, qkv_q, T, 3LL * H * HD, stride_qkv, HD, SUB)) return rc;
+  if (int rc = bbhost::encode_2d(&tm_do64, d_out, T, (long long)H * HD, stride_o, HD, SUB)) return rc;
   static bool attr = false;
   if (!attr) {
-    if (int rc = set_smem(attn_tc_dq_kernel, DQ_SMEM)) return rc;
-    if (int rc = set_smem(attn_tc_dkv_kernel, DKV_SMEM)) return rc;
+    if (int rc = set_smem(attn_tc_dq2_kernel, DQ2_SMEM)) return rc;
+    if (int rc = set_smem(attn_tc_dkv2_kernel, DKV2_SMEM)) return rc;
     attr = true;
   }
   const long long units = T * H;
   long long dgrid = (units + 7) / 8, cap = (long long)bb_num_sms() * 8;
   attn_tc_delta_kernel<<<(int)(dgrid < cap ? dgrid : cap), 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out, p);
   dim3 grid((S + TQ - 1) / TQ, H, B);
-  attn_tc_dkv_kernel<<<grid, NTHREADS, DKV_SMEM, stream>>>(tm_qkv, tm_do, p);
-  attn_tc_dq_kernel<<<grid, NTHREADS, DQ_SMEM, stream>>>(tm_qkv, tm_do, p);
+  attn_tc_dkv2_kernel<<<grid, NT2, DKV2_SMEM, stream>>>(tm_qkv, tm_qkv64, tm_do64, p);
+  attn_tc_dq2_kernel<<<grid, NT2, DQ2_SMEM, stream>>>(tm_qkv, tm_qkv64, tm_do, p);
   BB_CUDA_CHECK(cudaGetLastError());
   return BB_OK;
 }
