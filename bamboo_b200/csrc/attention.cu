@@ -480,17 +480,19 @@ int bb_attention_tc_bwd(const void* qkv_q, const void* out, const void* d_out, c
 
 namespace {
 // The tcgen05 kernels (attention_tc.cu) read q, k, v through one tensor map over the packed
-// projection [tokens, 3*H*64].  They are correct but their producer / MMA / softmax hand-offs are
-// still serial per key block, which makes them slower than the warp-level kernels above at the
-// benchmark shapes (measured on B200, B8 H16 S1024 causal: forward 379 vs 158 us, backward 672
-// vs 595 us), so they are opt-in: BB_ATTENTION_IMPL=tc in the environment.
-bool use_tc_path(const void* q, const void* k, const void* v, int H, int D, long long stride_qkv) {
-  static int wanted = -1;
-  if (wanted < 0) {
+// projection [tokens, 3*H*64].  Measured on B200 (B8 H16 S1024 causal): the pipelined tcgen05
+// backward takes 288 us against 593 us for the warp-level kernels above, so it is the default
+// for head dimension 64; the tcgen05 forward still hands off serially per key block (379 us
+// against 120 us) and stays opt-in.  BB_ATTENTION_IMPL=tc / mma in the environment forces one
+// implementation for both directions.
+bool use_tc_path(const void* q, const void* k, const void* v, int H, int D, long long stride_qkv, bool backward) {
+  static int mode = -1;   // 0 = default split, 1 = all tcgen05, 2 = all warp-level
+  if (mode < 0) {
     const char* e = getenv("BB_ATTENTION_IMPL");
-    wanted = (e && e[0] == 't') ? 1 : 0;
+    mode = (e && e[0] == 't') ? 1 : (e && e[0] == 'm') ? 2 : 0;
   }
-  if (!wanted || D != 64) return false;
+  if (D != 64 || mode == 2) return false;
+  if (mode == 0 && !backward) return false;
   const long long hb = (long long)H * D * 2;
   return (const char*)k - (const char*)q == hb && (const char*)v - (const char*)q == 2 * hb && stride_qkv >= 3LL * H * D &&
          (long long)H * D * 3 < (1LL << 31);
@@ -507,7 +509,7 @@ extern "C" int bb_attention_fwd(const void* q, const void* k, const void* v, voi
   AttnParams p = {};
   p.q = (const __nv_bfloat16*)q; p.k = (const __nv_bfloat16*)k; p.v = (const __nv_bfloat16*)v; p.out = (__nv_bfloat16*)out;
   p.lse = lse; p.stride_qkv = stride_qkv; p.stride_o = stride_o; p.B = B; p.H = H; p.S = S; p.causal = causal; p.scale = scale;
-  if (use_tc_path(q, k, v, H, D, stride_qkv))
+  if (use_tc_path(q, k, v, H, D, stride_qkv, false))
     return bb_attention_tc_fwd(q, out, lse, B, H, S, stride_qkv, stride_o, causal, scale, (cudaStream_t)stream);
   if (D == 64) return launch_fwd<64>(p, (cudaStream_t)stream);
   if (D == 128) return launch_fwd<128>(p, (cudaStream_t)stream);
@@ -540,7 +542,7 @@ extern "C" int bb_attention_bwd(const void* q, const void* k, const void* v, con
   p.lse = const_cast<float*>(lse); p.delta = (float*)workspace;
   p.stride_qkv = stride_qkv; p.stride_o = stride_o; p.stride_dqkv = stride_dqkv;
   p.B = B; p.H = H; p.S = S; p.causal = causal; p.scale = scale;
-  if (use_tc_path(q, k, v, H, D, stride_qkv))
+  if (use_tc_path(q, k, v, H, D, stride_qkv, true))
     return bb_attention_tc_bwd(q, out, d_out, lse, dq, dk, dv, (float*)workspace, B, H, S, stride_qkv, stride_o, stride_dqkv,
                                causal, scale, (cudaStream_t)stream);
   if (D == 64) return launch_bwd<64>(p, (cudaStream_t)stream);

@@ -34,6 +34,7 @@ struct TcParams {
   int causal;
   float scale;
   int* status;
+  long long* dbg;               // optional cycle counters (development aid), NULL in normal use
 };
 
 // instruction descriptor: bf16 x bf16 -> fp32, M = 128
@@ -71,6 +72,31 @@ __device__ __forceinline__ void sq_store32(uint8_t* buf, int row, int c0, const 
   }
 }
 
+__device__ __forceinline__ void pack32(const float* v, uint32_t* out16) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) out16[i] = bb::pack_bf16x2(v[2 * i], v[2 * i + 1]);
+}
+// one row of a [128 x 64] bf16 atom (128 bytes) from 32 packed registers
+__device__ __forceinline__ void atom_store_row(uint8_t* atom, int row, const uint32_t* pk) {
+  uint8_t* base = atom + row * 128;
+#pragma unroll
+  for (int c = 0; c < 8; ++c)
+    *reinterpret_cast<uint4*>(base + ((c ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// two 32-column TMEM reads in flight, one wait
+__device__ __forceinline__ void ld32x2(uint32_t ta, uint32_t tb, float* a, float* b) {
+  uint32_t ra[32], rb[32];
+  bb::tmem_ld_32x32b_x32(ta, ra);
+  bb::tmem_ld_32x32b_x32(tb, rb);
+  bb::tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) { a[i] = __uint_as_float(ra[i]); b[i] = __uint_as_float(rb[i]); }
+}
 __device__ __forceinline__ void ld32(uint32_t taddr, float* v) {
   uint32_t r[32];
   bb::tmem_ld_32x32b_x32(taddr, r);
@@ -92,14 +118,14 @@ __device__ __forceinline__ void store_row64(__nv_bfloat16* dst, const float* v, 
 
 // shared-memory bookkeeping common to the three kernels
 struct Ctl {
-  uint64_t bars[16];
+  uint64_t bars[32];
   uint32_t tmem_slot;
   int abort_flag;
 };
 
 // Compute warps wait together: the 128 threads either all proceed or all leave.
 __device__ __forceinline__ bool wait_all(uint64_t* bar, uint32_t parity, Ctl* ctl, int* status) {
-  const bool ok = bb::mbar_wait(bar, parity, &ctl->abort_flag, status);
+  const bool ok = bb::mbar_wait_spin(bar, parity, &ctl->abort_flag, status);
   return bb::named_bar_all(2, 128, ok);
 }
 
@@ -158,7 +184,7 @@ attn_tc_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_const
       bb::tma_load_2d(sDO, &tm_do, q_full, colq, row_base + q0);
       for (int j = 0; j < nkv; ++j) {
         const int s = j & 1;
-        if (!bb::mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        if (!bb::mbar_wait_spin(&kv_empty[s], ((j >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
         bb::mbar_arrive_expect_tx(&kv_full[s], 2 * TILE_BYTES);
         bb::tma_load_2d(sK + s * TILE_BYTES, &tm_qkv, &kv_full[s], colk, row_base + j * TQ);
         bb::tma_load_2d(sV + s * TILE_BYTES, &tm_qkv, &kv_full[s], colv, row_base + j * TQ);
@@ -167,12 +193,12 @@ attn_tc_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_const
   } else if (warp == 1) {
     const uint32_t aQ = bb::smem_u32(sQ), aDO = bb::smem_u32(sDO), aDS = bb::smem_u32(sDS);
     const uint32_t i_s = idesc(128, 0, 0), i_dq = idesc(64, 0, 1);
-    bool alive = bb::mbar_wait(q_full, 0, &ctl->abort_flag, p.status);
+    bool alive = bb::mbar_wait_spin(q_full, 0, &ctl->abort_flag, p.status);
     for (int j = 0; j < nkv && alive; ++j) {
       const int s = j & 1;
       const uint32_t aK = bb::smem_u32(sK + s * TILE_BYTES), aV = bb::smem_u32(sV + s * TILE_BYTES);
-      if (!bb::mbar_wait(&kv_full[s], (j >> 1) & 1, &ctl->abort_flag, p.status)) break;
-      if (!bb::mbar_wait(s_empty, (j & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+      if (!bb::mbar_wait_spin(&kv_full[s], (j >> 1) & 1, &ctl->abort_flag, p.status)) break;
+      if (!bb::mbar_wait_spin(s_empty, (j & 1) ^ 1, &ctl->abort_flag, p.status)) break;
       bb::tc_fence_after_sync();
       if (lane == 0) {
 #pragma unroll
@@ -182,7 +208,7 @@ attn_tc_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_const
         bb::umma_commit(s_full);
       }
       __syncwarp();
-      if (!bb::mbar_wait(ds_full, j & 1, &ctl->abort_flag, p.status)) break;
+      if (!bb::mbar_wait_spin(ds_full, j & 1, &ctl->abort_flag, p.status)) break;
       bb::tc_fence_after_sync();
       if (lane == 0) {
 #pragma unroll
@@ -300,7 +326,7 @@ attn_tc_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
       bb::tma_load_2d(sV, &tm_qkv, kv_full, colv, row_base + k0);
       for (int i = 0; i < nblk; ++i) {
         const int s = i & 1;
-        if (!bb::mbar_wait(&q_empty[s], ((i >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        if (!bb::mbar_wait_spin(&q_empty[s], ((i >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
         bb::mbar_arrive_expect_tx(&q_full[s], 2 * TILE_BYTES);
         bb::tma_load_2d(sQ + s * TILE_BYTES, &tm_qkv, &q_full[s], colq, row_base + (qstart + i) * TQ);
         bb::tma_load_2d(sDO + s * TILE_BYTES, &tm_do, &q_full[s], colq, row_base + (qstart + i) * TQ);
@@ -309,12 +335,12 @@ attn_tc_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
   } else if (warp == 1) {
     const uint32_t aK = bb::smem_u32(sK), aV = bb::smem_u32(sV), aP = bb::smem_u32(sP), aDS = bb::smem_u32(sDS);
     const uint32_t i_s = idesc(128, 0, 0), i_acc = idesc(64, 0, 1);
-    bool alive = bb::mbar_wait(kv_full, 0, &ctl->abort_flag, p.status);
+    bool alive = bb::mbar_wait_spin(kv_full, 0, &ctl->abort_flag, p.status);
     for (int i = 0; i < nblk && alive; ++i) {
       const int s = i & 1;
       const uint32_t aQ = bb::smem_u32(sQ + s * TILE_BYTES), aDO = bb::smem_u32(sDO + s * TILE_BYTES);
-      if (!bb::mbar_wait(&q_full[s], (i >> 1) & 1, &ctl->abort_flag, p.status)) break;
-      if (!bb::mbar_wait(s_empty, (i & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+      if (!bb::mbar_wait_spin(&q_full[s], (i >> 1) & 1, &ctl->abort_flag, p.status)) break;
+      if (!bb::mbar_wait_spin(s_empty, (i & 1) ^ 1, &ctl->abort_flag, p.status)) break;
       bb::tc_fence_after_sync();
       if (lane == 0) {
 #pragma unroll
@@ -324,7 +350,7 @@ attn_tc_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_cons
         bb::umma_commit(s_full);
       }
       __syncwarp();
-      if (!bb::mbar_wait(p_full, i & 1, &ctl->abort_flag, p.status)) break;
+      if (!bb::mbar_wait_spin(p_full, i & 1, &ctl->abort_flag, p.status)) break;
       bb::tc_fence_after_sync();
       if (lane == 0) {
 #pragma unroll
@@ -452,7 +478,7 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const TcParams p)
       bb::tma_load_2d(sQ, &tm_qkv, q_full, colq, row_base + q0);
       for (int j = 0; j < nkv; ++j) {
         const int s = j & 1;
-        if (!bb::mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        if (!bb::mbar_wait_spin(&kv_empty[s], ((j >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
         bb::mbar_arrive_expect_tx(&kv_full[s], 2 * TILE_BYTES);
         bb::tma_load_2d(sK + s * TILE_BYTES, &tm_qkv, &kv_full[s], colk, row_base + j * TQ);
         bb::tma_load_2d(sV + s * TILE_BYTES, &tm_qkv, &kv_full[s], colv, row_base + j * TQ);
@@ -461,12 +487,12 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const TcParams p)
   } else if (warp == 1) {
     const uint32_t aQ = bb::smem_u32(sQ), aP = bb::smem_u32(sP);
     const uint32_t i_s = idesc(128, 0, 0), i_pv = idesc(64, 0, 1);
-    bool alive = bb::mbar_wait(q_full, 0, &ctl->abort_flag, p.status);
+    bool alive = bb::mbar_wait_spin(q_full, 0, &ctl->abort_flag, p.status);
     for (int j = 0; j < nkv && alive; ++j) {
       const int s = j & 1;
       const uint32_t aK = bb::smem_u32(sK + s * TILE_BYTES), aV = bb::smem_u32(sV + s * TILE_BYTES);
-      if (!bb::mbar_wait(&kv_full[s], (j >> 1) & 1, &ctl->abort_flag, p.status)) break;
-      if (!bb::mbar_wait(s_empty, (j & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+      if (!bb::mbar_wait_spin(&kv_full[s], (j >> 1) & 1, &ctl->abort_flag, p.status)) break;
+      if (!bb::mbar_wait_spin(s_empty, (j & 1) ^ 1, &ctl->abort_flag, p.status)) break;
       bb::tc_fence_after_sync();
       if (lane == 0) {
 #pragma unroll
@@ -474,8 +500,8 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const TcParams p)
         bb::umma_commit(s_full);
       }
       __syncwarp();
-      if (!bb::mbar_wait(p_full, j & 1, &ctl->abort_flag, p.status)) break;
-      if (!bb::mbar_wait(pv_empty, (j & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+      if (!bb::mbar_wait_spin(p_full, j & 1, &ctl->abort_flag, p.status)) break;
+      if (!bb::mbar_wait_spin(pv_empty, (j & 1) ^ 1, &ctl->abort_flag, p.status)) break;
       bb::tc_fence_after_sync();
       if (lane == 0) {
 #pragma unroll
@@ -593,6 +619,8 @@ attn_tc_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* _
 constexpr int SUB = 64;                          // streamed rows per sub-block
 constexpr int SUB_BYTES = SUB * HD * 2;          // 8 KiB: [64 x 64] bf16
 constexpr int NT2 = 320;
+constexpr int NST = 6;                           // streamed sub-tile ring depth
+constexpr int NSB = 3;                           // score buffers in tensor memory
 
 // ------------------------------------------------------------------ dQ (pipelined)
 // smem: Q, dO [128 x 64] | K, V sub-tiles [64 x 64] x 3 stages | dS [128 q x 64 kv] x 2
@@ -604,18 +632,18 @@ attn_tc_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sDO = sQ + TILE_BYTES;
-  uint8_t* sK = sDO + TILE_BYTES;              // 3 stages x 8 KiB
-  uint8_t* sV = sK + 3 * SUB_BYTES;            // 3 stages x 8 KiB
-  uint8_t* sDS = sV + 3 * SUB_BYTES;           // 2 x 16 KiB
+  uint8_t* sK = sDO + TILE_BYTES;              // NST stages x 8 KiB
+  uint8_t* sV = sK + NST * SUB_BYTES;          // NST stages x 8 KiB
+  uint8_t* sDS = sV + NST * SUB_BYTES;         // 2 x 16 KiB
   Ctl* ctl = reinterpret_cast<Ctl*>(sDS + 2 * TILE_BYTES);
   uint64_t* q_full = &ctl->bars[0];
-  uint64_t* kv_full = &ctl->bars[1];           // [3]
-  uint64_t* kv_empty = &ctl->bars[4];          // [3]
-  uint64_t* s_full = &ctl->bars[7];            // [2]
-  uint64_t* s_empty = &ctl->bars[9];           // [2]
-  uint64_t* ds_full = &ctl->bars[11];          // [2]
-  uint64_t* ds_empty = &ctl->bars[13];         // [2]
-  uint64_t* acc_full = &ctl->bars[15];
+  uint64_t* kv_full = &ctl->bars[1];           // [NST]
+  uint64_t* kv_empty = &ctl->bars[1 + NST];    // [NST]
+  uint64_t* s_full = &ctl->bars[1 + 2 * NST];  // [NSB]
+  uint64_t* s_empty = s_full + NSB;            // [NSB]
+  uint64_t* ds_full = s_empty + NSB;           // [2]
+  uint64_t* ds_empty = ds_full + 2;            // [2]
+  uint64_t* acc_full = ds_empty + 2;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qb = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
@@ -628,11 +656,9 @@ attn_tc_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   if (threadIdx.x == 0) {
     ctl->abort_flag = 0;
     bb::mbar_init(q_full, 1);
-    for (int i = 0; i < 3; ++i) { bb::mbar_init(&kv_full[i], 1); bb::mbar_init(&kv_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) {
-      bb::mbar_init(&s_full[i], 1); bb::mbar_init(&s_empty[i], 4);
-      bb::mbar_init(&ds_full[i], 4); bb::mbar_init(&ds_empty[i], 1);
-    }
+    for (int i = 0; i < NST; ++i) { bb::mbar_init(&kv_full[i], 1); bb::mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < NSB; ++i) { bb::mbar_init(&s_full[i], 1); bb::mbar_init(&s_empty[i], 4); }
+    for (int i = 0; i < 2; ++i) { bb::mbar_init(&ds_full[i], 4); bb::mbar_init(&ds_empty[i], 1); }
     bb::mbar_init(acc_full, 1);
     bb::fence_barrier_init();
     bb::tma_prefetch_desc(&tm_q); bb::tma_prefetch_desc(&tm_kv); bb::tma_prefetch_desc(&tm_do);
@@ -642,7 +668,7 @@ attn_tc_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   __syncthreads();
   bb::tc_fence_after_sync();
   const uint32_t tmem = ctl->tmem_slot;
-  const uint32_t tDQ = tmem + 256;             // S[b] at tmem + 64 b, dP[b] at tmem + 128 + 64 b
+  const uint32_t tDQ = tmem + 384;             // S[b] at tmem + 64 b, dP[b] at tmem + 192 + 64 b (b < 3)
 
   if (warp == 0) {
     if (lane == 0) {
@@ -650,8 +676,8 @@ attn_tc_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       bb::tma_load_2d(sQ, &tm_q, q_full, colq, row_base + q0);
       bb::tma_load_2d(sDO, &tm_do, q_full, colq, row_base + q0);
       for (int j = 0; j < nblk; ++j) {
-        const int s = j % 3;
-        if (!bb::mbar_wait(&kv_empty[s], ((j / 3) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        const int s = j % NST;
+        if (!bb::mbar_wait_spin(&kv_empty[s], ((j / NST) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
         bb::mbar_arrive_expect_tx(&kv_full[s], 2 * SUB_BYTES);
         bb::tma_load_2d(sK + s * SUB_BYTES, &tm_kv, &kv_full[s], colk, row_base + j * SUB);
         bb::tma_load_2d(sV + s * SUB_BYTES, &tm_kv, &kv_full[s], colv, row_base + j * SUB);
@@ -660,34 +686,35 @@ attn_tc_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   } else if (warp == 1) {
     const uint32_t aQ = bb::smem_u32(sQ), aDO = bb::smem_u32(sDO);
     const uint32_t i_s = idesc(64, 0, 0), i_dq = idesc(64, 0, 1);
-    bool alive = bb::mbar_wait(q_full, 0, &ctl->abort_flag, p.status);
-    // software pipeline: scores of sub-block j are issued before the dQ update of sub-block j-1
-    for (int j = 0; j <= nblk && alive; ++j) {
+    bool alive = bb::mbar_wait_spin(q_full, 0, &ctl->abort_flag, p.status);
+    // software pipeline: the scores run two sub-blocks ahead of the dQ updates
+    for (int j = 0; j < nblk + 2 && alive; ++j) {
       if (j < nblk) {
-        const int s = j % 3, b = j & 1;
-        const uint32_t aK = bb::smem_u32(sK + s * SUB_BYTES), aV = bb::smem_u32(sV + s * SUB_BYTES);
-        if (!bb::mbar_wait(&kv_full[s], (j / 3) & 1, &ctl->abort_flag, p.status)) break;
-        if (!bb::mbar_wait(&s_empty[b], ((j >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        const int s = j % NST, b = j % NSB;
+        if (!bb::mbar_wait_spin(&kv_full[s], (j / NST) & 1, &ctl->abort_flag, p.status)) break;
+        if (!bb::mbar_wait_spin(&s_empty[b], ((j / NSB) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
         bb::tc_fence_after_sync();
         if (lane == 0) {
+          const uint32_t aK = bb::smem_u32(sK + s * SUB_BYTES), aV = bb::smem_u32(sV + s * SUB_BYTES);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) bb::umma_f16(tmem + 64 * b, desc_kmajor(aQ, k), desc_kmajor(aK, k), i_s, k > 0);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) bb::umma_f16(tmem + 128 + 64 * b, desc_kmajor(aDO, k), desc_kmajor(aV, k), i_s, k > 0);
+          for (int k = 0; k < 4; ++k) {
+            bb::umma_f16(tmem + 64 * b, desc_kmajor(aQ, k), desc_kmajor(aK, k), i_s, k > 0);
+            bb::umma_f16(tmem + 192 + 64 * b, desc_kmajor(aDO, k), desc_kmajor(aV, k), i_s, k > 0);
+          }
           bb::umma_commit(&s_full[b]);
         }
         __syncwarp();
       }
-      if (j >= 1) {
-        const int jj = j - 1, s = jj % 3, b = jj & 1;
-        const uint32_t aK = bb::smem_u32(sK + s * SUB_BYTES), aDS = bb::smem_u32(sDS + b * TILE_BYTES);
-        if (!bb::mbar_wait(&ds_full[b], (jj >> 1) & 1, &ctl->abort_flag, p.status)) break;
+      if (j >= 2) {
+        const int jj = j - 2, s2 = jj % NST, b2 = jj & 1;
+        if (!bb::mbar_wait_spin(&ds_full[b2], (jj >> 1) & 1, &ctl->abort_flag, p.status)) break;
         bb::tc_fence_after_sync();
         if (lane == 0) {
+          const uint32_t aK2 = bb::smem_u32(sK + s2 * SUB_BYTES), aDS = bb::smem_u32(sDS + b2 * TILE_BYTES);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) bb::umma_f16(tDQ, desc_kmajor(aDS, k), desc_mnmajor64(aK, k), i_dq, (jj > 0 || k > 0));
-          bb::umma_commit(&ds_empty[b]);
-          bb::umma_commit(&kv_empty[s]);
+          for (int k = 0; k < 4; ++k) bb::umma_f16(tDQ, desc_kmajor(aDS, k), desc_mnmajor64(aK2, k), i_dq, (jj > 0 || k > 0));
+          bb::umma_commit(&ds_empty[b2]);
+          bb::umma_commit(&kv_empty[s2]);
           if (jj == nblk - 1) bb::umma_commit(acc_full);
         }
         __syncwarp();
@@ -705,35 +732,61 @@ attn_tc_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const float dl = (qrow < p.S) ? delta_g[qrow] : 0.f;
     const float sl = p.scale * LOG2E;
     uint8_t* myDS = sDS + g * TILE_BYTES;
-    const uint32_t tS = tmem + 64 * g, tDP = tmem + 128 + 64 * g;
     bool alive = true;
     int n = 0;                                               // this group's iteration count
+    long long tacc[6] = {0, 0, 0, 0, 0, 0};
+    long long tprev = clock64();
+#define BB_TICK(ix) { const long long _t = clock64(); tacc[ix] += _t - tprev; tprev = _t; }
     for (int j = g; j < nblk && alive; j += 2, ++n) {
-      bool ok = bb::mbar_wait(&s_full[g], n & 1, &ctl->abort_flag, p.status);
-      ok = ok && bb::mbar_wait(&ds_empty[g], (n & 1) ^ 1, &ctl->abort_flag, p.status);
+      const int sb = j % NSB;
+      const uint32_t tS = tmem + 64 * sb, tDP = tmem + 192 + 64 * sb;
+      const bool ok = bb::mbar_wait_spin(&s_full[sb], (j / NSB) & 1, &ctl->abort_flag, p.status);
       if (!bb::named_bar_all(3 + g, 128, ok)) { alive = false; break; }
+      BB_TICK(0)
       bb::tc_fence_after_sync();
       const int c0 = j * SUB;
-#pragma unroll 1
+      // only sub-blocks that touch the sequence end or the causal diagonal need per-element masks
+      const bool need_mask = (c0 + SUB > p.S) || (p.causal && c0 + SUB - 1 > q0);
+      const float nlse = -lse;
+      uint32_t pk[32];                                       // the row's 64 dS values as bf16 pairs
+#pragma unroll
       for (int c = 0; c < 2; ++c) {
         float sv[32], dp[32];
-        ld32(tS + lane_addr + c * 32, sv);
-        ld32(tDP + lane_addr + c * 32, dp);
+        ld32x2(tS + lane_addr + c * 32, tDP + lane_addr + c * 32, sv, dp);
+        if (!need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int col = c0 + c * 32 + i;
-          float pv = exp2f(sv[i] * sl - lse);
-          if (col >= p.S || qrow >= p.S || (p.causal && col > qrow)) pv = 0.f;
-          dp[i] = pv * (dp[i] - dl);
+          for (int i = 0; i < 32; ++i) dp[i] = ex2(fmaf(sv[i], sl, nlse)) * (dp[i] - dl);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = c0 + c * 32 + i;
+            float pv = ex2(fmaf(sv[i], sl, nlse));
+            if (col >= p.S || (p.causal && col > qrow)) pv = 0.f;
+            dp[i] = pv * (dp[i] - dl);
+          }
         }
-        sq_store32(myDS, row, c * 32, dp);
+        pack32(dp, pk + 16 * c);
       }
+      BB_TICK(1)
       bb::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) bb::mbar_arrive(&s_empty[sb]);          // scores consumed: the MMA warp may refill
+      // the staging buffer is free once the dQ update that read it two sub-blocks ago retired
+      const bool ok2 = bb::mbar_wait_spin(&ds_empty[g], (n & 1) ^ 1, &ctl->abort_flag, p.status);
+      if (!bb::named_bar_all(3 + g, 128, ok2)) { alive = false; break; }
+      BB_TICK(2)
+      atom_store_row(myDS, row, pk);
       bb::fence_proxy_async();
       __syncwarp();
-      if (lane == 0) { bb::mbar_arrive(&s_empty[g]); bb::mbar_arrive(&ds_full[g]); }
+      if (lane == 0) bb::mbar_arrive(&ds_full[g]);
+      BB_TICK(3)
     }
-    const bool fin = alive && bb::mbar_wait(acc_full, 0, &ctl->abort_flag, p.status);
+    if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 64) {
+      for (int i = 0; i < 4; ++i) p.dbg[i] = tacc[i];
+      p.dbg[4] = n;
+    }
+#undef BB_TICK
+    const bool fin = alive && bb::mbar_wait_spin(acc_full, 0, &ctl->abort_flag, p.status);
     if (bb::named_bar_all(3 + g, 128, fin) && g == 0) {
       bb::tc_fence_after_sync();
       float v[64];
@@ -747,7 +800,7 @@ attn_tc_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   if (warp == 1) bb::tmem_dealloc(tmem, 512);
 }
 
-constexpr int DQ2_SMEM = 2 * TILE_BYTES + 6 * SUB_BYTES + 2 * TILE_BYTES + (int)sizeof(Ctl) + 1024;
+constexpr int DQ2_SMEM = 2 * TILE_BYTES + 2 * NST * SUB_BYTES + 2 * TILE_BYTES + (int)sizeof(Ctl) + 1024;
 
 // ------------------------------------------------------------------ dK, dV (pipelined)
 // smem: K, V [128 x 64] | Q, dO sub-tiles [64 x 64] x 3 stages | P^T, dS^T [128 kv x 64 q] x 2 each
@@ -760,21 +813,21 @@ attn_tc_dkv2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
   uint8_t* sV = sK + TILE_BYTES;
-  uint8_t* sQ = sV + TILE_BYTES;               // 3 stages x 8 KiB
-  uint8_t* sDO = sQ + 3 * SUB_BYTES;           // 3 stages x 8 KiB
-  uint8_t* sP = sDO + 3 * SUB_BYTES;           // 2 x 16 KiB
+  uint8_t* sQ = sV + TILE_BYTES;               // NST stages x 8 KiB
+  uint8_t* sDO = sQ + NST * SUB_BYTES;         // NST stages x 8 KiB
+  uint8_t* sP = sDO + NST * SUB_BYTES;         // 2 x 16 KiB
   uint8_t* sDS = sP + 2 * TILE_BYTES;          // 2 x 16 KiB
   float* s_lse = reinterpret_cast<float*>(sDS + 2 * TILE_BYTES);   // [2][64]
   float* s_delta = s_lse + 2 * SUB;                                // [2][64]
   Ctl* ctl = reinterpret_cast<Ctl*>(s_delta + 2 * SUB);
   uint64_t* kv_full = &ctl->bars[0];
-  uint64_t* q_full = &ctl->bars[1];            // [3]
-  uint64_t* q_empty = &ctl->bars[4];           // [3]
-  uint64_t* s_full = &ctl->bars[7];            // [2]
-  uint64_t* s_empty = &ctl->bars[9];           // [2]
-  uint64_t* p_full = &ctl->bars[11];           // [2]
-  uint64_t* p_empty = &ctl->bars[13];          // [2]
-  uint64_t* acc_full = &ctl->bars[15];
+  uint64_t* q_full = &ctl->bars[1];            // [NST]
+  uint64_t* q_empty = &ctl->bars[1 + NST];     // [NST]
+  uint64_t* s_full = &ctl->bars[1 + 2 * NST];  // [NSB]
+  uint64_t* s_empty = s_full + NSB;            // [NSB]
+  uint64_t* p_full = s_empty + NSB;            // [2]
+  uint64_t* p_empty = p_full + 2;              // [2]
+  uint64_t* acc_full = p_empty + 2;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kb = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
@@ -788,11 +841,9 @@ attn_tc_dkv2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
   if (threadIdx.x == 0) {
     ctl->abort_flag = 0;
     bb::mbar_init(kv_full, 1);
-    for (int i = 0; i < 3; ++i) { bb::mbar_init(&q_full[i], 1); bb::mbar_init(&q_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) {
-      bb::mbar_init(&s_full[i], 1); bb::mbar_init(&s_empty[i], 4);
-      bb::mbar_init(&p_full[i], 4); bb::mbar_init(&p_empty[i], 1);
-    }
+    for (int i = 0; i < NST; ++i) { bb::mbar_init(&q_full[i], 1); bb::mbar_init(&q_empty[i], 1); }
+    for (int i = 0; i < NSB; ++i) { bb::mbar_init(&s_full[i], 1); bb::mbar_init(&s_empty[i], 4); }
+    for (int i = 0; i < 2; ++i) { bb::mbar_init(&p_full[i], 4); bb::mbar_init(&p_empty[i], 1); }
     bb::mbar_init(acc_full, 1);
     bb::fence_barrier_init();
     bb::tma_prefetch_desc(&tm128); bb::tma_prefetch_desc(&tm64); bb::tma_prefetch_desc(&tm_do64);
@@ -802,7 +853,7 @@ attn_tc_dkv2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
   __syncthreads();
   bb::tc_fence_after_sync();
   const uint32_t tmem = ctl->tmem_slot;
-  const uint32_t tDV = tmem + 256, tDK = tmem + 320;   // S^T[b] at tmem + 64 b, dP^T[b] at tmem + 128 + 64 b
+  const uint32_t tDV = tmem + 384, tDK = tmem + 448;   // S^T[b] at tmem + 64 b, dP^T[b] at tmem + 192 + 64 b (b < 3)
 
   if (warp == 0) {
     if (lane == 0) {
@@ -810,8 +861,8 @@ attn_tc_dkv2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
       bb::tma_load_2d(sK, &tm128, kv_full, colk, row_base + k0);
       bb::tma_load_2d(sV, &tm128, kv_full, colv, row_base + k0);
       for (int i = 0; i < nblk; ++i) {
-        const int s = i % 3;
-        if (!bb::mbar_wait(&q_empty[s], ((i / 3) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        const int s = i % NST;
+        if (!bb::mbar_wait_spin(&q_empty[s], ((i / NST) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
         bb::mbar_arrive_expect_tx(&q_full[s], 2 * SUB_BYTES);
         bb::tma_load_2d(sQ + s * SUB_BYTES, &tm64, &q_full[s], colq, row_base + (qstart + i) * SUB);
         bb::tma_load_2d(sDO + s * SUB_BYTES, &tm_do64, &q_full[s], colq, row_base + (qstart + i) * SUB);
@@ -820,36 +871,39 @@ attn_tc_dkv2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
   } else if (warp == 1) {
     const uint32_t aK = bb::smem_u32(sK), aV = bb::smem_u32(sV);
     const uint32_t i_s = idesc(64, 0, 0), i_acc = idesc(64, 0, 1);
-    bool alive = bb::mbar_wait(kv_full, 0, &ctl->abort_flag, p.status);
-    for (int i = 0; i <= nblk && alive; ++i) {
+    bool alive = bb::mbar_wait_spin(kv_full, 0, &ctl->abort_flag, p.status);
+    // the score products run two sub-blocks ahead of the dV / dK updates
+    for (int i = 0; i < nblk + 2 && alive; ++i) {
       if (i < nblk) {
-        const int s = i % 3, b = i & 1;
-        const uint32_t aQ = bb::smem_u32(sQ + s * SUB_BYTES), aDO = bb::smem_u32(sDO + s * SUB_BYTES);
-        if (!bb::mbar_wait(&q_full[s], (i / 3) & 1, &ctl->abort_flag, p.status)) break;
-        if (!bb::mbar_wait(&s_empty[b], ((i >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        const int s = i % NST, b = i % NSB;
+        if (!bb::mbar_wait_spin(&q_full[s], (i / NST) & 1, &ctl->abort_flag, p.status)) break;
+        if (!bb::mbar_wait_spin(&s_empty[b], ((i / NSB) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
         bb::tc_fence_after_sync();
         if (lane == 0) {
+          const uint32_t aQ = bb::smem_u32(sQ + s * SUB_BYTES), aDO = bb::smem_u32(sDO + s * SUB_BYTES);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) bb::umma_f16(tmem + 64 * b, desc_kmajor(aK, k), desc_kmajor(aQ, k), i_s, k > 0);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) bb::umma_f16(tmem + 128 + 64 * b, desc_kmajor(aV, k), desc_kmajor(aDO, k), i_s, k > 0);
+          for (int k = 0; k < 4; ++k) {
+            bb::umma_f16(tmem + 64 * b, desc_kmajor(aK, k), desc_kmajor(aQ, k), i_s, k > 0);
+            bb::umma_f16(tmem + 192 + 64 * b, desc_kmajor(aV, k), desc_kmajor(aDO, k), i_s, k > 0);
+          }
           bb::umma_commit(&s_full[b]);
         }
         __syncwarp();
       }
-      if (i >= 1) {
-        const int ii = i - 1, s = ii % 3, b = ii & 1;
-        const uint32_t aQ = bb::smem_u32(sQ + s * SUB_BYTES), aDO = bb::smem_u32(sDO + s * SUB_BYTES);
-        const uint32_t aP = bb::smem_u32(sP + b * TILE_BYTES), aDS = bb::smem_u32(sDS + b * TILE_BYTES);
-        if (!bb::mbar_wait(&p_full[b], (ii >> 1) & 1, &ctl->abort_flag, p.status)) break;
+      if (i >= 2) {
+        const int ii = i - 2, s2 = ii % NST, b2 = ii & 1;
+        if (!bb::mbar_wait_spin(&p_full[b2], (ii >> 1) & 1, &ctl->abort_flag, p.status)) break;
         bb::tc_fence_after_sync();
         if (lane == 0) {
+          const uint32_t aQ2 = bb::smem_u32(sQ + s2 * SUB_BYTES), aDO2 = bb::smem_u32(sDO + s2 * SUB_BYTES);
+          const uint32_t aP = bb::smem_u32(sP + b2 * TILE_BYTES), aDS = bb::smem_u32(sDS + b2 * TILE_BYTES);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) bb::umma_f16(tDV, desc_kmajor(aP, k), desc_mnmajor64(aDO, k), i_acc, (ii > 0 || k > 0));
-#pragma unroll
-          for (int k = 0; k < 4; ++k) bb::umma_f16(tDK, desc_kmajor(aDS, k), desc_mnmajor64(aQ, k), i_acc, (ii > 0 || k > 0));
-          bb::umma_commit(&p_empty[b]);
-          bb::umma_commit(&q_empty[s]);
+          for (int k = 0; k < 4; ++k) {
+            bb::umma_f16(tDV, desc_kmajor(aP, k), desc_mnmajor64(aDO2, k), i_acc, (ii > 0 || k > 0));
+            bb::umma_f16(tDK, desc_kmajor(aDS, k), desc_mnmajor64(aQ2, k), i_acc, (ii > 0 || k > 0));
+          }
+          bb::umma_commit(&p_empty[b2]);
+          bb::umma_commit(&q_empty[s2]);
           if (ii == nblk - 1) bb::umma_commit(acc_full);
         }
         __syncwarp();
@@ -869,47 +923,69 @@ attn_tc_dkv2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
     uint8_t* myDS = sDS + g * TILE_BYTES;
     float* my_lse = s_lse + g * SUB;
     float* my_delta = s_delta + g * SUB;
-    const uint32_t tS = tmem + 64 * g, tDP = tmem + 128 + 64 * g;
     bool alive = true;
     int n = 0;
+    // per-column statistics are fetched one sub-block ahead so their latency is off the critical path
+    float nx_lse = 0.f, nx_delta = 0.f;
+    if (gt < SUB && g < nblk) {
+      const int q = (qstart + g) * SUB + gt;
+      if (q < p.S) { nx_lse = lse_g[q] * LOG2E; nx_delta = delta_g[q]; }
+    }
     for (int i = g; i < nblk && alive; i += 2, ++n) {
       const int qc0 = (qstart + i) * SUB;
-      // statistics of this sub-block's 64 query columns (the group's previous readers are past
-      // their last use once everybody is through this barrier)
+      // (the group's previous readers are past their last use once everybody is through this barrier)
       bb::named_bar_sync(1 + g, 128);
-      if (gt < SUB) {
-        const int q = qc0 + gt;
-        my_lse[gt] = (q < p.S) ? lse_g[q] * LOG2E : 0.f;
-        my_delta[gt] = (q < p.S) ? delta_g[q] : 0.f;
+      if (gt < SUB) { my_lse[gt] = nx_lse; my_delta[gt] = nx_delta; }
+      bb::named_bar_sync(1 + g, 128);
+      if (gt < SUB && i + 2 < nblk) {
+        const int q = (qstart + i + 2) * SUB + gt;
+        nx_lse = (q < p.S) ? lse_g[q] * LOG2E : 0.f;
+        nx_delta = (q < p.S) ? delta_g[q] : 0.f;
       }
-      bb::named_bar_sync(1 + g, 128);
-      bool ok = bb::mbar_wait(&s_full[g], n & 1, &ctl->abort_flag, p.status);
-      ok = ok && bb::mbar_wait(&p_empty[g], (n & 1) ^ 1, &ctl->abort_flag, p.status);
+      const int sb = i % NSB;
+      const uint32_t tS = tmem + 64 * sb, tDP = tmem + 192 + 64 * sb;
+      const bool ok = bb::mbar_wait_spin(&s_full[sb], (i / NSB) & 1, &ctl->abort_flag, p.status);
       if (!bb::named_bar_all(3 + g, 128, ok)) { alive = false; break; }
       bb::tc_fence_after_sync();
-#pragma unroll 1
+      const bool need_mask = (qc0 + SUB > p.S) || (p.causal && k0 + TQ - 1 > qc0);
+      uint32_t pkP[32], pkDS[32];                            // the row's 64 P^T and dS^T values as bf16 pairs
+#pragma unroll
       for (int c = 0; c < 2; ++c) {
         float sv[32], dp[32];
-        ld32(tS + lane_addr + c * 32, sv);
-        ld32(tDP + lane_addr + c * 32, dp);
+        ld32x2(tS + lane_addr + c * 32, tDP + lane_addr + c * 32, sv, dp);
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int qi = c * 32 + e;
-          const int q = qc0 + qi;
-          float pv = exp2f(sv[e] * sl - my_lse[qi]);
-          if (q >= p.S || krow >= p.S || (p.causal && krow > q)) pv = 0.f;
-          sv[e] = pv;
-          dp[e] = pv * (dp[e] - my_delta[qi]);
+        for (int e4 = 0; e4 < 32; e4 += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(my_lse + c * 32 + e4);
+          const float4 d4 = *reinterpret_cast<const float4*>(my_delta + c * 32 + e4);
+          const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, ds[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int e = e4 + u;
+            float pv = ex2(fmaf(sv[e], sl, -ls[u]));
+            if (need_mask) {
+              const int q = qc0 + c * 32 + e;
+              if (q >= p.S || (p.causal && krow > q)) pv = 0.f;
+            }
+            sv[e] = pv;
+            dp[e] = pv * (dp[e] - ds[u]);
+          }
         }
-        sq_store32(myP, row, c * 32, sv);
-        sq_store32(myDS, row, c * 32, dp);
+        pack32(sv, pkP + 16 * c);
+        pack32(dp, pkDS + 16 * c);
       }
       bb::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) bb::mbar_arrive(&s_empty[sb]);
+      // the staging buffers are free once the dV / dK update that read them retired
+      const bool ok2 = bb::mbar_wait_spin(&p_empty[g], (n & 1) ^ 1, &ctl->abort_flag, p.status);
+      if (!bb::named_bar_all(3 + g, 128, ok2)) { alive = false; break; }
+      atom_store_row(myP, row, pkP);
+      atom_store_row(myDS, row, pkDS);
       bb::fence_proxy_async();
       __syncwarp();
-      if (lane == 0) { bb::mbar_arrive(&s_empty[g]); bb::mbar_arrive(&p_full[g]); }
+      if (lane == 0) bb::mbar_arrive(&p_full[g]);
     }
-    const bool fin = alive && nblk > 0 && bb::mbar_wait(acc_full, 0, &ctl->abort_flag, p.status);
+    const bool fin = alive && nblk > 0 && bb::mbar_wait_spin(acc_full, 0, &ctl->abort_flag, p.status);
     if (bb::named_bar_all(3 + g, 128, fin)) {
       bb::tc_fence_after_sync();
       float v[64];
@@ -926,7 +1002,7 @@ attn_tc_dkv2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
   if (warp == 1) bb::tmem_dealloc(tmem, 512);
 }
 
-constexpr int DKV2_SMEM = 2 * TILE_BYTES + 6 * SUB_BYTES + 4 * TILE_BYTES + 4 * SUB * (int)sizeof(float) + (int)sizeof(Ctl) + 1024;
+constexpr int DKV2_SMEM = 2 * TILE_BYTES + 2 * NST * SUB_BYTES + 4 * TILE_BYTES + 4 * SUB * (int)sizeof(float) + (int)sizeof(Ctl) + 1024;
 
 constexpr int DQ_SMEM = 6 * TILE_BYTES + SQ_BYTES + (int)sizeof(Ctl) + 1024;
 
@@ -956,6 +1032,13 @@ int bb_attention_tc_fwd(const void* qkv_q, void* out, float* lse, int B, int H, 
   return BB_OK;
 }
 
+// development aid: cycle counters of one compute warp of the dQ kernel (see BB_TICK)
+static __device__ long long g_attn_dbg[8];
+extern "C" int bb_attention_debug_counters(long long* out8) {
+  BB_CUDA_CHECK(cudaMemcpyFromSymbol(out8, g_attn_dbg, sizeof(long long) * 8));
+  return BB_OK;
+}
+
 int bb_attention_tc_bwd(const void* qkv_q, const void* out, const void* d_out, const float* lse, void* dq, void* dk, void* dv,
                         float* delta, int B, int H, int S, long long stride_qkv, long long stride_o, long long stride_dqkv,
                         int causal, float scale, cudaStream_t stream) {
@@ -968,6 +1051,7 @@ int bb_attention_tc_bwd(const void* qkv_q, const void* out, const void* d_out, c
   p.dq = (__nv_bfloat16*)dq; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
   p.lse = const_cast<float*>(lse); p.delta = delta; p.stride_o = stride_o; p.stride_dqkv = stride_dqkv;
   p.B = B; p.H = H; p.S = S; p.hidden = H * HD; p.causal = causal; p.scale = scale; p.status = bb_device_status_word();
+  { void* d = nullptr; if (cudaGetSymbolAddress(&d, g_attn_dbg) == cudaSuccess) p.dbg = (long long*)d; }
   CUtensorMap tm_qkv64, tm_do64;
   if (int rc = bbhost::encode_2d(&tm_qkv64, qkv_q, T, 3LL * H * HD, stride_qkv, HD, SUB)) return rc;
   if (int rc = bbhost::encode_2d(&tm_do64, d_out, T, (long long)H * HD, stride_o, HD, SUB)) return rc;
