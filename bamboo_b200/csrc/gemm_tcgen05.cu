@@ -61,6 +61,11 @@ __device__ __forceinline__ void panel_store_row_bf16(uint8_t* panel, int row, co
     *reinterpret_cast<uint4*>(base + ((c ^ (row & 7)) << 4)) = q;
   }
 }
+__device__ __forceinline__ void panel_load_row_bf16(const uint8_t* panel, int row, float* x /*64*/) {
+  const uint8_t* base = panel + row * 128;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) unpack8(*reinterpret_cast<const uint4*>(base + ((c ^ (row & 7)) << 4)), x + 8 * c);
+}
 __device__ __forceinline__ void panel_store_row_f32(uint8_t* panel, int row, const float* v /*32*/) {
   uint8_t* base = panel + row * 128;
 #pragma unroll
@@ -84,19 +89,6 @@ __device__ __forceinline__ void add_bias(const GemmParams& p, int n0, float* v) 
   }
 }
 
-// aux[m, n0 .. n0+W) as floats (zero outside the matrix)
-template <int W>
-__device__ __forceinline__ void load_aux(const GemmParams& p, int m, int n0, float* x) {
-  if (m < p.M && n0 + W <= p.N) {
-    const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)m * p.ld_aux + n0;
-#pragma unroll
-    for (int i = 0; i < W; i += 8) unpack8(*reinterpret_cast<const uint4*>(a + i), x + i);
-  } else {
-    const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)m * p.ld_aux + n0;
-    for (int i = 0; i < W; ++i) x[i] = (m < p.M && n0 + i < p.N) ? __bfloat162float(a[i]) : 0.f;
-  }
-}
-
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -114,7 +106,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   uint64_t* empty_bar = bars + C::STAGES;         // [STAGES]
   uint64_t* tmem_full = bars + 2 * C::STAGES;     // [2]
   uint64_t* tmem_empty = bars + 2 * C::STAGES + 2;  // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 4);
+  uint64_t* aux_bar = bars + 2 * C::STAGES + 4;     // [2] one per epilogue group: aux panel landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 6);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -128,12 +121,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < C::STAGES; ++s) { bb::mbar_init(&full_bar[s], 1); bb::mbar_init(&empty_bar[s], 1); }
-    for (int a = 0; a < 2; ++a) { bb::mbar_init(&tmem_full[a], 1); bb::mbar_init(&tmem_empty[a], 8); }
+    for (int a = 0; a < 2; ++a) { bb::mbar_init(&tmem_full[a], 1); bb::mbar_init(&tmem_empty[a], 8); bb::mbar_init(&aux_bar[a], 1); }
     bb::fence_barrier_init();
     bb::tma_prefetch_desc(&tmA);
     bb::tma_prefetch_desc(&tmB);
     bb::tma_prefetch_desc(&tmD);
-    if (p.epi == BB_EPI_BIAS_GELU) bb::tma_prefetch_desc(&tmD2);
+    if (p.epi == BB_EPI_BIAS_GELU || p.epi == BB_EPI_MUL_DGELU || p.epi == BB_EPI_BIAS_RESIDUAL) bb::tma_prefetch_desc(&tmD2);
   }
   if (warp == 1) {
     bb::tmem_alloc(tmem_slot, C::TMEM_COLS);
@@ -231,6 +224,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     const int epi = p.epi;
     const bool f32 = (epi == BB_EPI_ACCUM_F32 || epi == BB_EPI_STORE_F32);
     const bool dual = (epi == BB_EPI_BIAS_GELU);
+    const bool has_aux = (epi == BB_EPI_MUL_DGELU || epi == BB_EPI_BIAS_RESIDUAL);
+    uint32_t aux_uses = 0;                         // completed aux loads of this group (barrier phase)
     uint8_t* panel = panels + eg * PANEL_BYTES;    // this group's staging panel
     int acc = 0; uint32_t acc_phase = 0;
     bool alive = true;
@@ -241,7 +236,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       const bool got = bb::mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status);
       if (!bb::named_bar_all(3 + eg, 128, got)) { alive = false; break; }
       bb::tc_fence_after_sync();
-      const int m = m0 + row;
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
       const int width = f32 ? 32 : 64;             // columns per panel
       const int npanels = BN / width;
@@ -272,7 +266,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         if (nb >= p.N) continue;                   // panel entirely outside the matrix (uniform)
         // the panel must have been read by its previous store before it is overwritten
         if (leader) bb::bulk_wait_group_read<0>();
-        bb::named_bar_sync(1 + eg, 128);
+        if (has_aux) {
+          // the [128 x 64] aux tile (second operand of the epilogue) comes in by TMA into the
+          // staging panel; each thread then reads and rewrites only its own row
+          if (leader) {
+            bb::mbar_arrive_expect_tx(&aux_bar[eg], PANEL_BYTES);
+            bb::tma_load_2d(panel, &tmD2, &aux_bar[eg], nb, m0);
+          }
+          const bool landed = bb::mbar_wait(&aux_bar[eg], aux_uses & 1, abort_flag, p.status);
+          if (!bb::named_bar_all(3 + eg, 128, landed)) { alive = false; break; }
+          ++aux_uses;
+        } else {
+          bb::named_bar_sync(1 + eg, 128);
+        }
         if (f32) {
           panel_store_row_f32(panel, row, v);
         } else {
@@ -288,18 +294,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             for (int i = 0; i < 64; ++i) v[i] = bb::gelu_tanh(__bfloat162float(__float2bfloat16(v[i])));
             if (leader) bb::bulk_wait_group_read<0>();
             bb::named_bar_sync(1 + eg, 128);
-          } else if (epi == BB_EPI_MUL_DGELU || epi == BB_EPI_BIAS_RESIDUAL) {
+          } else if (has_aux) {
+            float x[64];
+            panel_load_row_bf16(panel, row, x);
+            if (epi == BB_EPI_MUL_DGELU) {
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-              float x[32];
-              load_aux<32>(p, m, nb + half * 32, x);
-              if (epi == BB_EPI_MUL_DGELU) {
+              for (int i = 0; i < 64; ++i) v[i] *= bb::gelu_tanh_grad(x[i]);
+            } else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) v[half * 32 + i] *= bb::gelu_tanh_grad(x[i]);
-              } else {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) v[half * 32 + i] += x[i];
-              }
+              for (int i = 0; i < 64; ++i) v[i] += x[i];
             }
           }
           panel_store_row_bf16(panel, row, v);
@@ -336,6 +339,9 @@ int launch(const bb_gemm_desc* g, cudaStream_t stream) {
   tmD2 = tmD;
   if (g->epilogue == BB_EPI_BIAS_GELU) {
     rc = encode_2d(&tmD2, g->D2, g->M, g->N, g->ldd, 64, BM, 0);
+    if (rc) return rc;
+  } else if (g->epilogue == BB_EPI_MUL_DGELU || g->epilogue == BB_EPI_BIAS_RESIDUAL) {
+    rc = encode_2d(&tmD2, g->aux, g->M, g->N, g->ld_aux ? g->ld_aux : g->ldd, 64, BM, 0);   // the aux operand
     if (rc) return rc;
   }
   if (!g->a_mn_major) rc = encode_2d(&tmA, g->A, g->M, g->K, g->lda, BK, BM);
