@@ -544,6 +544,10 @@ class PipelineEngine:
         failover schedule with a redo window and run the batch again."""
         step_idx, exc = status
         self.rdzv_handler.write("/rdzv/last_reconfig", self.global_steps)
+        if (isinstance(exc, PrevStageException) and self.num_stages == 2 and self.next_stage not in self.stage_ids
+                and self.next_stage in self.param_buffers):
+            # two-stage ring: the silent predecessor is also the successor whose shadow lives here
+            exc = NextStageException(str(exc))
         if isinstance(exc, NextStageException):
             victim = self.next_stage
             victim_rank = self._promote_next_stage()
@@ -863,6 +867,15 @@ class PipelineEngine:
                         dp = self.grid._topo.get_coord(rank).data
                         msg = f"RANK {rank} FROM PIPELINE {dp} IN ALL-REDUCE GROUP FAILED. USING FALLBACK"
                         return i, AllReduceException(dp, f"{schedule.ReduceGrads}: {msg}")
+            if any(type(c) is schedule.OptimizerStep for c in step_cmds):
+                # The merged failover stream carries the dead stage's ReduceGrads *after* OptimizerStep
+                # (reference quirk, schedule.py:417-421).  The stream is kept as emitted; the executor
+                # runs every reduction of the step before the optimizer so that the promoted stage
+                # steps on averaged gradients.
+                reduces = [c for c in step_cmds if type(c) is schedule.ReduceGrads]
+                rest = [c for c in step_cmds if type(c) is not schedule.ReduceGrads]
+                k = next(i for i, c in enumerate(rest) if type(c) is schedule.OptimizerStep)
+                step_cmds = rest[:k] + reduces + rest[k:]
             for cmd in step_cmds:
                 try:
                     fn = self._INSTRUCTION_MAP.get(type(cmd))

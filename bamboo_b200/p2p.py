@@ -90,32 +90,44 @@ class DistTransport:
     def send(self, tensor, dst, kind, slot, seq):
         self._check_cpu(tensor)
         t = tensor.detach().contiguous()
-        if (dst, kind) not in self._sent_meta:
-            meta = torch.zeros(10, dtype=torch.int64)
-            meta[0], meta[1] = _DTYPES.index(t.dtype), t.dim()
-            meta[2:2 + t.dim()] = torch.tensor(list(t.shape), dtype=torch.int64)
-            self._pending.append((self.dist.isend(meta, dst, tag=kind), dst, meta))
-            self._sent_meta.add((dst, kind))
-        self._pending.append((self.dist.isend(t, dst, tag=kind), dst, t))
+        try:
+            if (dst, kind) not in self._sent_meta:
+                meta = torch.zeros(10, dtype=torch.int64)
+                meta[0], meta[1] = _DTYPES.index(t.dtype), t.dim()
+                meta[2:2 + t.dim()] = torch.tensor(list(t.shape), dtype=torch.int64)
+                self._pending.append((self.dist.isend(meta, dst, tag=kind), dst, meta))
+                self._sent_meta.add((dst, kind))
+            self._pending.append((self.dist.isend(t, dst, tag=kind), dst, t))
+        except RuntimeError as e:  # the connection to a dead peer is already closed
+            raise PeerTimeout(dst, f"peer rank {dst}: {str(e)[:200]}")
+
+    def _irecv(self, buf, src, tag):
+        try:
+            return self.dist.irecv(buf, src, tag=tag)
+        except RuntimeError as e:
+            raise PeerTimeout(src, f"peer rank {src}: {str(e)[:200]}")
 
     def recv(self, src, kind, slot, seq):
         if (src, kind) not in self._meta:
             meta = torch.zeros(10, dtype=torch.int64)
-            self._wait(self.dist.irecv(meta, src, tag=kind), src)
+            self._wait(self._irecv(meta, src, kind), src)
             nd = int(meta[1])
             self._meta[(src, kind)] = (torch.Size(meta[2:2 + nd].tolist()), _DTYPES[int(meta[0])])
         shape, dtype = self._meta[(src, kind)]
         buf = torch.empty(shape, dtype=dtype)
-        self._wait(self.dist.irecv(buf, src, tag=kind), src)
+        self._wait(self._irecv(buf, src, kind), src)
         return buf
 
     def send_ping(self, dst, seq):
         t = torch.full((1,), float(seq))
-        self._pending.append((self.dist.isend(t, dst, tag=PING), dst, t))
+        try:
+            self._pending.append((self.dist.isend(t, dst, tag=PING), dst, t))
+        except RuntimeError as e:
+            raise PeerTimeout(dst, f"peer rank {dst}: {str(e)[:200]}")
 
     def recv_ping(self, src, seq):
         t = torch.zeros(1)
-        self._wait(self.dist.irecv(t, src, tag=PING), src)
+        self._wait(self._irecv(t, src, PING), src)
 
     def exchange_state(self, send_to, tensors_out, recv_from, tensors_in, seq):
         """Ship this stage's flat optimizer state to the rank shadowing it and take the

@@ -36,9 +36,20 @@ def run_ranks(fn, world, *args, timeout=240, backend="gloo"):
             p.start()
         results = {}
         try:
-            for _ in range(world):
-                rank, status, payload = queue.get(timeout=timeout)
-                results[rank] = (status, payload)
+            import queue as _q
+            import time as _t
+            deadline = _t.monotonic() + timeout
+            while len(results) < world and _t.monotonic() < deadline:
+                try:
+                    rank, status, payload = queue.get(timeout=0.5)
+                    results[rank] = (status, payload)
+                except _q.Empty:
+                    # a rank that vanished without reporting (killed, os._exit) is recorded as such
+                    for r, p in enumerate(procs):
+                        if r not in results and not p.is_alive() and queue.empty():
+                            results[r] = ("dead", p.exitcode)
+            if len(results) < world:
+                raise AssertionError(f"ranks {sorted(set(range(world)) - set(results))} did not finish in {timeout} s")
         finally:
             for p in procs:
                 p.join(timeout=20)

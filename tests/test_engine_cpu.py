@@ -81,3 +81,117 @@ def test_failover_continues_the_same_trajectory(eager):
     assert out["losses"][3:] == pytest.approx(want[3:], rel=1e-5)
     total = sum(float(p.detach().double().sum()) for p in ref.P.values())
     assert sum(out["checksum"].values()) == pytest.approx(total, rel=1e-6)
+
+
+# ---------------------------------------------------------------------------------------------
+# pipeline x data parallel grid (2 stages x 2 replicas on 4 CPU ranks)
+def _train_grid(rank, world, store, stages, dp, rc, victim_rank, victim_step):
+    import cpu_layers
+    from bamboo_b200 import api
+    from bamboo_b200.module import PipelineModule
+    from bamboo_b200.topology import PipeDataParallelTopology
+    topo = PipeDataParallelTopology(num_pp=stages, num_dp=dp)
+    model = PipelineModule(cpu_layers.ref_layer_specs(CFG, 0), topology=topo, loss_fn=cpu_layers.ref_loss(CFG),
+                           partition_method="uniform", device="cpu")
+    config = {"train_micro_batch_size_per_gpu": MB, "gradient_accumulation_steps": GAS,
+              "train_batch_size": MB * GAS * dp,
+              "optimizer": {"type": "Adam", "params": {"lr": LR}}, "bamboo_b200": {"p2p_timeout_s": 20}}
+    engine, *_ = api.initialize(model=model, config=config, redundancy_level=rc, store=store)
+    replica = engine.grid.get_data_parallel_id()
+    data = gpt_ref.synthetic_batches(CFG, MB, GAS * dp, STEPS, seed=1)
+    losses = []
+    for step, batches in enumerate(data):
+        if victim_rank is not None and step == victim_step - 1 and rank == victim_rank:
+            engine.announce_preemption()
+        mine = batches[replica * GAS:(replica + 1) * GAS]        # each replica trains on its own slice
+        losses.append(float(engine.train_batch(data_iter=iter(mine))))
+    return {"losses": losses, "stage_ids": list(engine.stage_ids), "replica": replica,
+            "checksum": {s: float(engine.arenas[s].master.double().sum()) for s in engine.stage_ids}}
+
+
+def _oracle_grid(dp):
+    """Data parallelism = gradient averaging = one big accumulation over all replicas' micro-batches."""
+    ref = gpt_ref.RefTrainer(CFG, seed=0, lr=LR, micro_batches=GAS * dp)
+    per_replica = []
+    for batches in gpt_ref.synthetic_batches(CFG, MB, GAS * dp, STEPS, seed=1):
+        with torch.no_grad():
+            per_replica.append([sum(float(gpt_ref.forward_loss(CFG, ref.P, t, l)) for t, l in batches[r * GAS:(r + 1) * GAS]) / GAS
+                                for r in range(dp)])
+        ref.train_batch(batches)
+    return per_replica, ref
+
+
+def test_two_by_two_grid_averages_gradients_over_replicas():
+    from dist_utils import run_ranks
+    want, ref = _oracle_grid(2)
+    res = run_ranks(_train_grid, 4, 2, 2, 0, None, None)
+    for rank in (2, 3):                                           # last-stage ranks: rank = stage * dp + replica
+        status, out = res[rank]
+        assert status == "ok"
+        assert out["losses"] == pytest.approx([w[out["replica"]] for w in want], rel=1e-5)
+    total = sum(float(p.detach().double().sum()) for p in ref.P.values())
+    assert res[0][1]["checksum"][0] + res[2][1]["checksum"][1] == pytest.approx(total, rel=1e-6)
+    assert res[0][1]["checksum"] == res[1][1]["checksum"]        # replicas stay identical
+
+
+def test_grid_failover_uses_the_fallback_data_parallel_group():
+    """Rank 2 (stage 1 of replica 0) is preempted after step 3: rank 0 promotes its shadow of
+    stage 1 and takes rank 2's seat in stage 1's all-reduce; rank 3 switches to the fallback group."""
+    from dist_utils import run_ranks
+    want, ref = _oracle_grid(2)
+    res = run_ranks(_train_grid, 4, 2, 2, 1, 2, 3)
+    assert res[2] == ("exit", 13)
+    assert res[0][0] == "ok" and res[1][0] == "ok" and res[3][0] == "ok"
+    assert res[0][1]["stage_ids"] == [0, 1]
+    assert res[0][1]["losses"][3:] == pytest.approx([w[0] for w in want][3:], rel=1e-5)
+    assert res[3][1]["losses"] == pytest.approx([w[1] for w in want], rel=1e-5)
+    total = sum(float(p.detach().double().sum()) for p in ref.P.values())
+    assert sum(res[0][1]["checksum"].values()) == pytest.approx(total, rel=1e-6)
+    assert res[3][1]["checksum"][1] == pytest.approx(res[0][1]["checksum"][1], rel=1e-9)
+
+
+# ---------------------------------------------------------------------------------------------
+# unannounced death in the middle of a batch: detected through the transport, redo window
+def _train_sudden_death(rank, world, store, die_in_step, die_at_backward):
+    import cpu_layers
+    from bamboo_b200 import api, engine as E
+    from bamboo_b200.module import PipelineModule
+    model = PipelineModule(cpu_layers.ref_layer_specs(CFG, 0), num_stages=2, loss_fn=cpu_layers.ref_loss(CFG),
+                           partition_method="uniform", device="cpu")
+    config = {"train_micro_batch_size_per_gpu": MB, "gradient_accumulation_steps": GAS,
+              "optimizer": {"type": "Adam", "params": {"lr": LR}}, "bamboo_b200": {"p2p_timeout_s": 5}}
+    engine, *_ = api.initialize(model=model, config=config, redundancy_level=1, eager_recovery=False, store=store)
+    if rank == 1:
+        calls = {"n": 0}
+        orig = E.PipelineEngine._exec_backward_pass
+
+        def dying_backward(self, buffer_id, stage_id):
+            if self.global_steps == die_in_step:
+                calls["n"] += 1
+                if calls["n"] == die_at_backward:
+                    os._exit(0)                  # no announcement, no clean-up: the process is just gone
+            return orig(self, buffer_id, stage_id)
+        E.PipelineEngine._exec_backward_pass = dying_backward
+        E.PipelineEngine._INSTRUCTION_MAP[E.schedule.BackwardPass] = dying_backward
+    data = gpt_ref.synthetic_batches(CFG, MB, GAS, STEPS, seed=1)
+    losses = []
+    for batches in data:
+        losses.append(float(engine.train_batch(data_iter=iter(batches))))
+    return {"losses": losses, "stage_ids": list(engine.stage_ids),
+            "checksum": {s: float(engine.arenas[s].master.double().sum()) for s in engine.stage_ids}}
+
+
+@pytest.mark.parametrize("die_at_backward", [1, 3])
+def test_unannounced_death_mid_batch_is_recovered(die_at_backward):
+    """Stage 1 vanishes during step 3 after some of its backward passes; stage 0 notices on its
+    next receive, promotes its shadow, replays the dead stage's part of the batch and finishes
+    the run with the oracle's losses."""
+    from dist_utils import run_ranks
+    want, ref = _oracle_losses()
+    res = run_ranks(_train_sudden_death, 2, 3, die_at_backward)
+    status, out = res[0]
+    assert status == "ok", out
+    assert out["stage_ids"] == [0, 1]
+    assert out["losses"][3:] == pytest.approx(want[3:], rel=1e-5)
+    total = sum(float(p.detach().double().sum()) for p in ref.P.values())
+    assert sum(out["checksum"].values()) == pytest.approx(total, rel=1e-6)

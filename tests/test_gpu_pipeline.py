@@ -66,3 +66,39 @@ def test_failover_on_gpu_keeps_the_trajectory(eager):
     status, out = res[0]
     assert status == "ok" and out["stage_ids"] == [0, 1] and out["status"] == 0
     assert out["losses"][3:] == pytest.approx(want[3:], rel=2e-2)
+
+
+def _train_dp(rank, world, store):
+    """One stage, two replicas: the only collective is the NCCL all-reduce of the fp32 gradient arena."""
+    from bamboo_b200 import api, lib, models
+    from bamboo_b200.module import PipelineModule
+    from bamboo_b200.topology import PipeDataParallelTopology
+    tc = models.TransformerConfig(layers=CFG.layers, hidden=CFG.hidden, heads=CFG.heads, ffn=CFG.ffn, seq=CFG.seq,
+                                  vocab=CFG.vocab)
+    model = PipelineModule(models.transformer_layer_specs(tc, 0), topology=PipeDataParallelTopology(1, world),
+                           loss_fn=models.transformer_loss(tc), partition_method="uniform")
+    config = {"train_micro_batch_size_per_gpu": MB, "gradient_accumulation_steps": GAS,
+              "train_batch_size": MB * GAS * world, "bf16": {"enabled": True},
+              "optimizer": {"type": "Adam", "params": {"lr": LR}}}
+    engine, *_ = api.initialize(model=model, config=config, store=store)
+    data = gpt_ref.synthetic_batches(CFG, MB, GAS * world, 3, seed=1)
+    losses = [float(engine.train_batch(data_iter=iter(b[rank * GAS:(rank + 1) * GAS]))) for b in data]
+    torch.cuda.synchronize()
+    return {"losses": losses, "checksum": float(engine.arenas[0].master.double().sum()), "status": lib.read_status()}
+
+
+@needs2
+def test_data_parallel_replicas_average_gradients():
+    from dist_utils import run_ranks
+    ref = gpt_ref.RefTrainer(CFG, seed=0, lr=LR, micro_batches=GAS * 2)
+    want = []
+    for batches in gpt_ref.synthetic_batches(CFG, MB, GAS * 2, 3, seed=1):
+        with torch.no_grad():
+            want.append([sum(float(gpt_ref.forward_loss(CFG, ref.P, t, l)) for t, l in batches[r * GAS:(r + 1) * GAS]) / GAS
+                         for r in range(2)])
+        ref.train_batch(batches)
+    res = run_ranks(_train_dp, 2, backend="nccl")
+    for r in range(2):
+        assert res[r][0] == "ok" and res[r][1]["status"] == 0
+        assert res[r][1]["losses"] == pytest.approx([w[r] for w in want], rel=2e-2)
+    assert res[0][1]["checksum"] == res[1][1]["checksum"]          # replicas stay bit-identical
