@@ -34,7 +34,6 @@ struct TcParams {
   int causal;
   float scale;
   int* status;
-  long long* dbg;               // optional cycle counters (development aid), NULL in normal use
 };
 
 // instruction descriptor: bf16 x bf16 -> fp32, M = 128
@@ -734,15 +733,11 @@ attn_tc_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     uint8_t* myDS = sDS + g * TILE_BYTES;
     bool alive = true;
     int n = 0;                                               // this group's iteration count
-    long long tacc[6] = {0, 0, 0, 0, 0, 0};
-    long long tprev = clock64();
-#define BB_TICK(ix) { const long long _t = clock64(); tacc[ix] += _t - tprev; tprev = _t; }
     for (int j = g; j < nblk && alive; j += 2, ++n) {
       const int sb = j % NSB;
       const uint32_t tS = tmem + 64 * sb, tDP = tmem + 192 + 64 * sb;
       const bool ok = bb::mbar_wait_spin(&s_full[sb], (j / NSB) & 1, &ctl->abort_flag, p.status);
       if (!bb::named_bar_all(3 + g, 128, ok)) { alive = false; break; }
-      BB_TICK(0)
       bb::tc_fence_after_sync();
       const int c0 = j * SUB;
       // only sub-blocks that touch the sequence end or the causal diagonal need per-element masks
@@ -767,25 +762,17 @@ attn_tc_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
         pack32(dp, pk + 16 * c);
       }
-      BB_TICK(1)
       bb::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) bb::mbar_arrive(&s_empty[sb]);          // scores consumed: the MMA warp may refill
       // the staging buffer is free once the dQ update that read it two sub-blocks ago retired
       const bool ok2 = bb::mbar_wait_spin(&ds_empty[g], (n & 1) ^ 1, &ctl->abort_flag, p.status);
       if (!bb::named_bar_all(3 + g, 128, ok2)) { alive = false; break; }
-      BB_TICK(2)
       atom_store_row(myDS, row, pk);
       bb::fence_proxy_async();
       __syncwarp();
       if (lane == 0) bb::mbar_arrive(&ds_full[g]);
-      BB_TICK(3)
     }
-    if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 64) {
-      for (int i = 0; i < 4; ++i) p.dbg[i] = tacc[i];
-      p.dbg[4] = n;
-    }
-#undef BB_TICK
     const bool fin = alive && bb::mbar_wait_spin(acc_full, 0, &ctl->abort_flag, p.status);
     if (bb::named_bar_all(3 + g, 128, fin) && g == 0) {
       bb::tc_fence_after_sync();
@@ -1032,13 +1019,6 @@ int bb_attention_tc_fwd(const void* qkv_q, void* out, float* lse, int B, int H, 
   return BB_OK;
 }
 
-// development aid: cycle counters of one compute warp of the dQ kernel (see BB_TICK)
-static __device__ long long g_attn_dbg[8];
-extern "C" int bb_attention_debug_counters(long long* out8) {
-  BB_CUDA_CHECK(cudaMemcpyFromSymbol(out8, g_attn_dbg, sizeof(long long) * 8));
-  return BB_OK;
-}
-
 int bb_attention_tc_bwd(const void* qkv_q, const void* out, const void* d_out, const float* lse, void* dq, void* dk, void* dv,
                         float* delta, int B, int H, int S, long long stride_qkv, long long stride_o, long long stride_dqkv,
                         int causal, float scale, cudaStream_t stream) {
@@ -1051,7 +1031,6 @@ int bb_attention_tc_bwd(const void* qkv_q, const void* out, const void* d_out, c
   p.dq = (__nv_bfloat16*)dq; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
   p.lse = const_cast<float*>(lse); p.delta = delta; p.stride_o = stride_o; p.stride_dqkv = stride_dqkv;
   p.B = B; p.H = H; p.S = S; p.hidden = H * HD; p.causal = causal; p.scale = scale; p.status = bb_device_status_word();
-  { void* d = nullptr; if (cudaGetSymbolAddress(&d, g_attn_dbg) == cudaSuccess) p.dbg = (long long*)d; }
   CUtensorMap tm_qkv64, tm_do64;
   if (int rc = bbhost::encode_2d(&tm_qkv64, qkv_q, T, 3LL * H * HD, stride_qkv, HD, SUB)) return rc;
   if (int rc = bbhost::encode_2d(&tm_do64, d_out, T, (long long)H * HD, stride_o, HD, SUB)) return rc;

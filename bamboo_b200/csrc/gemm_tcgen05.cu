@@ -1,8 +1,15 @@
 // bf16 GEMM on the 5th-generation tensor cores: D[M,N] = op(A)[M,K] * op(B)[N,K]^T with a
 // fused epilogue.  One persistent CTA per SM; warp 0 feeds shared memory with TMA
 // (128-byte swizzle, no cluster multicast), warp 1 issues tcgen05.mma into two TMEM
-// accumulators, warps 2-5 drain TMEM (tcgen05.ld) and run the epilogue while the next
-// tile's main loop is already running.
+// accumulators, warps 2-9 drain TMEM (tcgen05.ld) and run the epilogue (coalesced global
+// stores from warp-private staging slabs) while the next tile's main loop is already running.
+//
+// Large problems run as CTA pairs (cta_group::2, clusters of two): a pair owns a 256 x 256
+// tile, each CTA loads its own 128 rows of A and only HALF of the B tile, rank 0 issues one
+// 256-row MMA for both and each CTA drains its own 128 accumulator rows.  Per CTA that is a
+// third less operand traffic from L2 and a third less shared memory per k-block than the
+// single-CTA 128 x 256 tile, so six stages fit instead of four - the single-CTA kernel is
+// bound by operand bytes in flight, not by the tensor pipe.
 //
 // Operand storage (all row-major, bf16):
 //   a_mn = 0 : A is [M, K] (K contiguous)     a_mn = 1 : A is stored [K, M] (M contiguous)
@@ -20,19 +27,19 @@ constexpr int BK = 64;        // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 320;   // TMA warp, MMA warp, two epilogue groups of four warps
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
-// Epilogue staging: output panels of 128 rows x 128 bytes (64 bf16 or 32 fp32 columns) in the
-// 128-byte-swizzled layout a TMA store expects.  Two panels: double-buffered for one output,
-// one each for the two outputs of the GeLU epilogue (shared memory is better spent on
-// main-loop stages: the kernel is bound by operand bytes in flight).
-constexpr int PANEL_BYTES = BM * 128;
-constexpr int NUM_PANELS = 2;
+// Epilogue staging: one 4 KiB slab (32 rows x 128 bytes = 64 bf16 or 32 fp32 columns) per
+// epilogue warp; shared memory is better spent on main-loop stages.
+constexpr int SLAB_BYTES = 32 * 128;
+constexpr int NUM_SLABS = 8;
 
-template <int BN> struct Cfg {
-  static constexpr int B_STAGE_BYTES = BN * BK * 2;
+template <int BN, bool PAIR> struct Cfg {
+  static constexpr int B_ROWS = PAIR ? BN / 2 : BN;      // B rows (output columns) this CTA loads
+  static constexpr int B_STAGE_BYTES = B_ROWS * BK * 2;
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int STAGES = (B_ROWS == 256) ? 4 : 6;
+  static constexpr int TILE_M = PAIR ? 2 * BM : BM;      // rows of a work unit (both CTAs of a pair)
   static constexpr int TMEM_COLS = 2 * BN;  // two accumulators
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + NUM_PANELS * PANEL_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + NUM_SLABS * SLAB_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
 struct GemmParams {
@@ -61,16 +68,86 @@ __device__ __forceinline__ void panel_store_row_bf16(uint8_t* panel, int row, co
     *reinterpret_cast<uint4*>(base + ((c ^ (row & 7)) << 4)) = q;
   }
 }
-__device__ __forceinline__ void panel_load_row_bf16(const uint8_t* panel, int row, float* x /*64*/) {
-  const uint8_t* base = panel + row * 128;
-#pragma unroll
-  for (int c = 0; c < 8; ++c) unpack8(*reinterpret_cast<const uint4*>(base + ((c ^ (row & 7)) << 4)), x + 8 * c);
-}
 __device__ __forceinline__ void panel_store_row_f32(uint8_t* panel, int row, const float* v /*32*/) {
   uint8_t* base = panel + row * 128;
 #pragma unroll
   for (int c = 0; c < 8; ++c)
     *reinterpret_cast<float4*>(base + ((c ^ (row & 7)) << 4)) = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+}
+
+// ---- warp-private staging slab: 32 rows x 128 bytes, 16-byte chunks XOR-swizzled by the row.
+// Row side: lane == row (panel_store_row_* / panel_load_row_bf16 with row = lane).
+// Coalesced side: lane -> (row 4*i + lane/8, chunk lane%8), i = 0..7: one instruction moves four
+// complete 128-byte row segments.
+__device__ __forceinline__ uint32_t slab_off(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
+
+__device__ __forceinline__ void slab_put(uint8_t* slab, int lane, const uint4* ax) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) *reinterpret_cast<uint4*>(slab + slab_off(4 * i + (lane >> 3), lane & 7)) = ax[i];
+}
+// rows r0.., columns nb.. of a bf16 matrix -> ax (zero outside the matrix)
+__device__ __forceinline__ void slab_fetch_bf16(const __nv_bfloat16* src, long long ld, int r0, int nb, int M, int N, int lane, uint4* ax) {
+  const int c = nb + (lane & 7) * 8;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = r0 + 4 * i + (lane >> 3);
+    uint4 q = make_uint4(0, 0, 0, 0);
+    if (r < M) {
+      const __nv_bfloat16* g = src + (long long)r * ld + c;
+      if (c + 8 <= N) {
+        q = __ldg(reinterpret_cast<const uint4*>(g));
+      } else {
+        unsigned short e[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) e[k] = (c + k < N) ? __bfloat16_as_ushort(g[k]) : (unsigned short)0;
+        q.x = e[0] | ((uint32_t)e[1] << 16); q.y = e[2] | ((uint32_t)e[3] << 16);
+        q.z = e[4] | ((uint32_t)e[5] << 16); q.w = e[6] | ((uint32_t)e[7] << 16);
+      }
+    }
+    ax[i] = q;
+  }
+}
+__device__ __forceinline__ void slab_flush_bf16(const uint8_t* slab, __nv_bfloat16* dst, long long ld, int r0, int nb, int M, int N, int lane) {
+  const int c = nb + (lane & 7) * 8;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rl = 4 * i + (lane >> 3);
+    const int r = r0 + rl;
+    const uint4 q = *reinterpret_cast<const uint4*>(slab + slab_off(rl, lane & 7));
+    if (r < M) {
+      __nv_bfloat16* g = dst + (long long)r * ld + c;
+      if (c + 8 <= N) {
+        *reinterpret_cast<uint4*>(g) = q;
+      } else {
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) if (c + k < N) g[k] = __ushort_as_bfloat16((unsigned short)(w[k >> 1] >> (16 * (k & 1))));
+      }
+    }
+  }
+}
+template <bool ACCUM>
+__device__ __forceinline__ void slab_flush_f32(const uint8_t* slab, float* dst, long long ld, int r0, int nb, int M, int N, int lane) {
+  const int c = nb + (lane & 7) * 4;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rl = 4 * i + (lane >> 3);
+    const int r = r0 + rl;
+    const float4 q = *reinterpret_cast<const float4*>(slab + slab_off(rl, lane & 7));
+    if (r < M) {
+      float* g = dst + (long long)r * ld + c;
+      if (c + 4 <= N) {
+        if (ACCUM) asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(g), "f"(q.x), "f"(q.y), "f"(q.z), "f"(q.w) : "memory");
+        else *reinterpret_cast<float4*>(g) = q;
+      } else {
+        const float w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (c + k < N) { if (ACCUM) atomicAdd(g + k, w[k]); else g[k] = w[k]; }
+        }
+      }
+    }
+  }
 }
 
 // bias[n0 .. n0+W) added to v; columns past N read as zero
@@ -85,34 +162,38 @@ __device__ __forceinline__ void add_bias(const GemmParams& p, int n0, float* v) 
       for (int k = 0; k < 8; ++k) v[i + k] += f[k];
     }
   } else {
-    for (int i = 0; i < W && n0 + i < p.N; ++i) v[i] += __bfloat162float(b[i]);
+    // fully unrolled with predicates: a dynamically indexed v[] would live in local memory
+#pragma unroll
+    for (int i = 0; i < W; ++i) if (n0 + i < p.N) v[i] += __bfloat162float(b[i]);
   }
 }
 
-template <int BN>
+template <int BN, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                         const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmD2,
                          const GemmParams p) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, PAIR>;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle atoms need 1024-byte aligned stage buffers
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + C::STAGES * A_STAGE_BYTES;
-  uint8_t* panels = smem + C::STAGES * C::STAGE_BYTES;   // NUM_PANELS x 16 KiB, 1024-byte aligned
-  uint64_t* bars = reinterpret_cast<uint64_t*>(panels + NUM_PANELS * PANEL_BYTES);
+  uint8_t* panels = smem + C::STAGES * C::STAGE_BYTES;   // NUM_SLABS x 4 KiB epilogue staging
+  uint64_t* bars = reinterpret_cast<uint64_t*>(panels + NUM_SLABS * SLAB_BYTES);
   uint64_t* full_bar = bars;                      // [STAGES]
   uint64_t* empty_bar = bars + C::STAGES;         // [STAGES]
   uint64_t* tmem_full = bars + 2 * C::STAGES;     // [2]
   uint64_t* tmem_empty = bars + 2 * C::STAGES + 2;  // [2]
-  uint64_t* aux_bar = bars + 2 * C::STAGES + 4;     // [2] one per epilogue group: aux panel landed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 6);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_m = (p.M + BM - 1) / BM;
+  // work units are strided over CTAs (pairs: over clusters; both CTAs walk the same units)
+  const uint32_t rank = PAIR ? bb::cluster_ctarank() : 0u;
+  const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int num_workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int num_m = (p.M + C::TILE_M - 1) / C::TILE_M;
   const int num_n = (p.N + BN - 1) / BN;
   const int num_mn = num_m * num_n;
   const int num_tiles = num_mn * p.ksplit;        // work units: (m, n, k-split)
@@ -121,19 +202,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < C::STAGES; ++s) { bb::mbar_init(&full_bar[s], 1); bb::mbar_init(&empty_bar[s], 1); }
-    for (int a = 0; a < 2; ++a) { bb::mbar_init(&tmem_full[a], 1); bb::mbar_init(&tmem_empty[a], 8); bb::mbar_init(&aux_bar[a], 1); }
+    // accumulator hand-back: one arrival per epilogue warp (of both CTAs for a pair, on rank 0's barrier)
+    for (int a = 0; a < 2; ++a) { bb::mbar_init(&tmem_full[a], 1); bb::mbar_init(&tmem_empty[a], PAIR ? 16 : 8); }
     bb::fence_barrier_init();
     bb::tma_prefetch_desc(&tmA);
     bb::tma_prefetch_desc(&tmB);
-    bb::tma_prefetch_desc(&tmD);
-    if (p.epi == BB_EPI_BIAS_GELU || p.epi == BB_EPI_MUL_DGELU || p.epi == BB_EPI_BIAS_RESIDUAL) bb::tma_prefetch_desc(&tmD2);
   }
   if (warp == 1) {
-    bb::tmem_alloc(tmem_slot, C::TMEM_COLS);
-    bb::tmem_relinquish();
+    if (PAIR) { bb::tmem_alloc_pair(tmem_slot, C::TMEM_COLS); bb::tmem_relinquish_pair(); }
+    else { bb::tmem_alloc(tmem_slot, C::TMEM_COLS); bb::tmem_relinquish(); }
   }
   bb::tc_fence_before_sync();
-  __syncthreads();
+  if (PAIR) bb::cluster_sync();     // the peer's barriers are initialised before anything signals them
+  else __syncthreads();
   bb::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -142,28 +223,55 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     if (lane == 0) {
       int s = 0; uint32_t phase = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+      for (int tile = worker; tile < num_tiles && alive; tile += num_workers) {
         const int mn = tile % num_mn, ks = tile / num_mn;
-        const int m0 = (mn % num_m) * BM, n0 = (mn / num_m) * BN;
+        const int m0 = (mn % num_m) * C::TILE_M + (int)rank * BM;          // this CTA's A rows
+        const int n0 = (mn / num_m) * BN + (int)rank * C::B_ROWS;          // this CTA's share of B (pairs: half)
         const int kb0 = ks * p.kb_per_split, kb1 = min(total_kb, kb0 + p.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!bb::mbar_wait(&empty_bar[s], phase ^ 1, abort_flag, p.status)) { alive = false; break; }
-          bb::mbar_arrive_expect_tx(&full_bar[s], C::STAGE_BYTES);
           uint8_t* a = sA + s * A_STAGE_BYTES;
           uint8_t* b = sB + s * C::B_STAGE_BYTES;
           const int k0 = kb * BK;
-          if (!p.a_mn) {
-            bb::tma_load_2d(a, &tmA, &full_bar[s], k0, m0);
-          } else {
+          if constexpr (PAIR) {
+            // both CTAs' copies complete on rank 0's barrier, where the MMA issuer waits
+            if (rank == 0) bb::mbar_arrive_expect_tx(&full_bar[s], 2 * C::STAGE_BYTES);
+            const uint32_t fb = bb::mapa_shared(bb::smem_u32(&full_bar[s]), 0);
+            if (!p.a_mn) {
+              bb::tma_load_2d_pair(a, &tmA, fb, k0, m0);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) bb::tma_load_2d(a + j * 8192, &tmA, &full_bar[s], m0 + 64 * j, k0);
-          }
-          if (!p.b_mn) {
-            bb::tma_load_2d(b, &tmB, &full_bar[s], k0, n0);
-          } else {
+              for (int j = 0; j < BM / 64; ++j) bb::tma_load_2d_pair(a + j * 8192, &tmA, fb, m0 + 64 * j, k0);
+            }
+            if (!p.b_mn) {
+              bb::tma_load_2d_pair(b, &tmB, fb, k0, n0);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) bb::tma_load_2d(b + j * 8192, &tmB, &full_bar[s], n0 + 64 * j, k0);
+              for (int j = 0; j < C::B_ROWS / 64; ++j) bb::tma_load_2d_pair(b + j * 8192, &tmB, fb, n0 + 64 * j, k0);
+            }
+          } else {
+            bb::mbar_arrive_expect_tx(&full_bar[s], C::STAGE_BYTES);
+            if (!p.a_mn) {
+              bb::tma_load_2d(a, &tmA, &full_bar[s], k0, m0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j) bb::tma_load_2d(a + j * 8192, &tmA, &full_bar[s], m0 + 64 * j, k0);
+            }
+            if (!p.b_mn) {
+              bb::tma_load_2d(b, &tmB, &full_bar[s], k0, n0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j) bb::tma_load_2d(b + j * 8192, &tmB, &full_bar[s], n0 + 64 * j, k0);
+            }
           }
+          if (++s == C::STAGES) { s = 0; phase ^= 1; }
+        }
+      }
+      if constexpr (PAIR) {
+        // rank 0's MMA commits arrive on this CTA's barriers too: wait until the last one of every
+        // stage has landed, so that none is still on its way when the CTA leaves
+        for (int i = 0; i < C::STAGES && alive; ++i) {
+          if (!bb::mbar_wait(&empty_bar[s], phase ^ 1, abort_flag, p.status)) alive = false;
           if (++s == C::STAGES) { s = 0; phase ^= 1; }
         }
       }
@@ -177,7 +285,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   } else if (warp == 1) {
     // ------------------------------------------------ MMA issuer
     const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.a_mn ? 1 : 0) << 15) |
-                           ((uint32_t)(p.b_mn ? 1 : 0) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                           ((uint32_t)(p.b_mn ? 1 : 0) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(C::TILE_M >> 4) << 24);
     // K-major: 8-row groups 1024 B apart (LBO unused); MN-major: 64-wide column groups are
     // separate 8 KiB TMA boxes (LBO), 8 k-rows are 1024 B (SBO).
     const uint32_t a_lbo = p.a_mn ? 8192u : 16u, b_lbo = p.b_mn ? 8192u : 16u;
@@ -185,7 +293,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     int s = 0; uint32_t phase = 0;
     int acc = 0; uint32_t acc_phase = 0;
     bool alive = true;
-    for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+    // pairs: rank 0 issues for both CTAs; the other CTA's MMA warp only allocates and frees TMEM
+    for (int tile = worker; tile < num_tiles && alive && rank == 0; tile += num_workers) {
       if (!bb::mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status)) { alive = false; break; }
       bb::tc_fence_after_sync();
       const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
@@ -201,10 +310,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           for (int k = 0; k < BK / UMMA_K; ++k) {
             uint64_t ad = bb::make_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, 1024u);
             uint64_t bd = bb::make_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, 1024u);
-            bb::umma_f16(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            if (PAIR) bb::umma_f16_pair(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            else bb::umma_f16(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
-          bb::umma_commit(&empty_bar[s]);
-          if (kb == num_kb - 1) bb::umma_commit(&tmem_full[acc]);
+          if (PAIR) {
+            bb::umma_commit_pair(&empty_bar[s], 3);            // frees the stage in both CTAs
+            if (kb == num_kb - 1) bb::umma_commit_pair(&tmem_full[acc], 3);
+          } else {
+            bb::umma_commit(&empty_bar[s]);
+            if (kb == num_kb - 1) bb::umma_commit(&tmem_full[acc]);
+          }
         }
         __syncwarp();
         if (++s == C::STAGES) { s = 0; phase ^= 1; }
@@ -212,37 +327,42 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
   } else {
-    // ------------------------------------------------ epilogue: two groups of 4 warps (one TMEM lane quarter per warp)
-    // Per 128-byte-wide output panel: TMEM -> registers -> fused math -> swizzled shared
-    // memory -> one TMA store (or fp32 add-reduction) issued by the group's first thread.
-    // The groups take alternate panels.  GeLU (two outputs) sends the pre-activation and then the
-    // activation through the same staging panel; the GeLU math overlaps the first store's read.
-    const int eg = (warp - 2) >> 2;                // epilogue group 0 / 1
+    // ------------------------------------------------ epilogue: 8 independent warps
+    // A warp owns one TMEM lane quarter (32 rows of the tile); the two warps of a quarter take
+    // alternate 128-byte-wide column panels.  Per panel: TMEM -> registers (one row per lane) ->
+    // fused math -> the warp's private 4 KiB staging slab in shared memory -> coalesced 16-byte
+    // global stores (fp32 add-reduction: vector red) by the same warp.  Nothing here waits on
+    // another warp or on the TMA queue, which the producer keeps full of operand loads.
+    const int eg = (warp - 2) >> 2;                // which of the quarter's two warps
     const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;           // row inside the tile == TMEM lane
-    const bool leader = (threadIdx.x == 64 + 128 * eg);
     const int epi = p.epi;
     const bool f32 = (epi == BB_EPI_ACCUM_F32 || epi == BB_EPI_STORE_F32);
     const bool dual = (epi == BB_EPI_BIAS_GELU);
     const bool has_aux = (epi == BB_EPI_MUL_DGELU || epi == BB_EPI_BIAS_RESIDUAL);
-    uint32_t aux_uses = 0;                         // completed aux loads of this group (barrier phase)
-    uint8_t* panel = panels + eg * PANEL_BYTES;    // this group's staging panel
+    uint8_t* slab = panels + (warp - 2) * SLAB_BYTES;
     int acc = 0; uint32_t acc_phase = 0;
     bool alive = true;
-    for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+    for (int tile = worker; tile < num_tiles && alive; tile += num_workers) {
       const int mn = tile % num_mn;
-      const int m0 = (mn % num_m) * BM, n0 = (mn / num_m) * BN;
-      // the four warps of a group share named barriers below: all continue or all leave
+      const int m0 = (mn % num_m) * C::TILE_M + (int)rank * BM, n0 = (mn / num_m) * BN;
+      const int r0 = m0 + quarter * 32;            // first output row of this warp
       const bool got = bb::mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status);
-      if (!bb::named_bar_all(3 + eg, 128, got)) { alive = false; break; }
+      if (!__all_sync(0xffffffffu, got)) { alive = false; break; }
       bb::tc_fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
       const int width = f32 ? 32 : 64;             // columns per panel
       const int npanels = BN / width;
-      const int first = eg, step = 2;
 #pragma unroll 1
-      for (int pn = first; pn < npanels; pn += step) {
+      for (int pn = eg; pn < npanels; pn += 2) {
         const int nb = n0 + pn * width;
+        const bool inside = (nb < p.N) && (r0 < p.M);   // warp-uniform
+        if (has_aux && inside) {
+          // the aux tile comes in coalesced (rows spread over lanes) and is turned through the
+          // slab, so that every lane can pick up its own row after the accumulator arrived
+          uint4 ax[8];
+          slab_fetch_bf16(reinterpret_cast<const __nv_bfloat16*>(p.aux), p.ld_aux, r0, nb, p.M, p.N, lane, ax);
+          slab_put(slab, lane, ax);
+        }
         float v[64];
         {
           uint32_t r[32];
@@ -257,97 +377,83 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             for (int i = 0; i < 32; ++i) v[32 + i] = __uint_as_float(r[i]);
           }
         }
-        if (pn + step >= npanels) {
-          // this group has read its share of the accumulator: hand it back before the last stores
+        if (pn + 2 >= npanels) {
+          // this warp has read its share of the accumulator: hand it back before the last stores
           bb::tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) bb::mbar_arrive(&tmem_empty[acc]);
-        }
-        if (nb >= p.N) continue;                   // panel entirely outside the matrix (uniform)
-        // the panel must have been read by its previous store before it is overwritten
-        if (leader) bb::bulk_wait_group_read<0>();
-        if (has_aux) {
-          // the [128 x 64] aux tile (second operand of the epilogue) comes in by TMA into the
-          // staging panel; each thread then reads and rewrites only its own row
-          if (leader) {
-            bb::mbar_arrive_expect_tx(&aux_bar[eg], PANEL_BYTES);
-            bb::tma_load_2d(panel, &tmD2, &aux_bar[eg], nb, m0);
+          if (lane == 0) {
+            if (PAIR) bb::mbar_arrive_cluster(bb::mapa_shared(bb::smem_u32(&tmem_empty[acc]), 0));
+            else bb::mbar_arrive(&tmem_empty[acc]);
           }
-          const bool landed = bb::mbar_wait(&aux_bar[eg], aux_uses & 1, abort_flag, p.status);
-          if (!bb::named_bar_all(3 + eg, 128, landed)) { alive = false; break; }
-          ++aux_uses;
-        } else {
-          bb::named_bar_sync(1 + eg, 128);
         }
+        if (!inside) continue;                     // panel entirely outside the matrix
         if (f32) {
-          panel_store_row_f32(panel, row, v);
-        } else {
-          if (epi == BB_EPI_BIAS || dual || epi == BB_EPI_BIAS_RESIDUAL) add_bias<64>(p, nb, v);
-          if (dual) {
-            panel_store_row_bf16(panel, row, v);   // pre-activation first
-            bb::fence_proxy_async();
-            bb::named_bar_sync(1 + eg, 128);
-            if (leader) { bb::tma_store_2d(&tmD2, panel, nb, m0); bb::bulk_commit_group(); }
-            // GeLU of the bf16-rounded pre-activation: forward and backward (which re-reads the
-            // stored pre-activation) see the same argument
+          panel_store_row_f32(slab, lane, v);
+          __syncwarp();
+          if (epi == BB_EPI_ACCUM_F32) slab_flush_f32<true>(slab, reinterpret_cast<float*>(p.D), p.ldd, r0, nb, p.M, p.N, lane);
+          else slab_flush_f32<false>(slab, reinterpret_cast<float*>(p.D), p.ldd, r0, nb, p.M, p.N, lane);
+          __syncwarp();
+          continue;
+        }
+        if (epi == BB_EPI_BIAS || dual || epi == BB_EPI_BIAS_RESIDUAL) add_bias<64>(p, nb, v);
+        if (dual) {
+          panel_store_row_bf16(slab, lane, v);     // pre-activation first
+          __syncwarp();
+          slab_flush_bf16(slab, reinterpret_cast<__nv_bfloat16*>(p.D2), p.ldd, r0, nb, p.M, p.N, lane);
+          // GeLU of the bf16-rounded pre-activation: forward and backward (which re-reads the
+          // stored pre-activation) see the same argument
 #pragma unroll
-            for (int i = 0; i < 64; ++i) v[i] = bb::gelu_tanh(__bfloat162float(__float2bfloat16(v[i])));
-            if (leader) bb::bulk_wait_group_read<0>();
-            bb::named_bar_sync(1 + eg, 128);
-          } else if (has_aux) {
-            float x[64];
-            panel_load_row_bf16(panel, row, x);
+          for (int i = 0; i < 64; ++i) v[i] = bb::gelu_tanh(__bfloat162float(__float2bfloat16(v[i])));
+          __syncwarp();
+        } else if (has_aux) {
+          __syncwarp();
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            float x[32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) unpack8(*reinterpret_cast<const uint4*>(slab + slab_off(lane, 4 * h + c)), x + 8 * c);
             if (epi == BB_EPI_MUL_DGELU) {
 #pragma unroll
-              for (int i = 0; i < 64; ++i) v[i] *= bb::gelu_tanh_grad(x[i]);
+              for (int i = 0; i < 32; ++i) v[32 * h + i] *= bb::gelu_tanh_grad(x[i]);
             } else {
 #pragma unroll
-              for (int i = 0; i < 64; ++i) v[i] += x[i];
+              for (int i = 0; i < 32; ++i) v[32 * h + i] += x[i];
             }
           }
-          panel_store_row_bf16(panel, row, v);
+          __syncwarp();
         }
-        bb::fence_proxy_async();                   // generic-proxy writes -> visible to the TMA engine
-        bb::named_bar_sync(1 + eg, 128);
-        if (leader) {
-          if (epi == BB_EPI_ACCUM_F32) bb::tma_reduce_add_2d(&tmD, panel, nb, m0);
-          else bb::tma_store_2d(&tmD, panel, nb, m0);
-          bb::bulk_commit_group();
-        }
+        panel_store_row_bf16(slab, lane, v);
+        __syncwarp();
+        slab_flush_bf16(slab, reinterpret_cast<__nv_bfloat16*>(p.D), p.ldd, r0, nb, p.M, p.N, lane);
+        __syncwarp();
       }
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
-    if (leader) bb::bulk_wait_group<0>();          // all stores landed before shared memory goes away
   }
 
   bb::tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 1) bb::tmem_dealloc(tmem_base, C::TMEM_COLS);
+  if (PAIR) {
+    // neither CTA leaves (or frees TMEM) while the other may still signal its barriers
+    bb::cluster_sync();
+    if (warp == 1) bb::tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
+  } else {
+    __syncthreads();
+    if (warp == 1) bb::tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
 }
 
 // ---------------------------------------------------------------- host side
 using bbhost::encode_2d;
 
-template <int BN>
+template <int BN, bool PAIR>
 int launch(const bb_gemm_desc* g, cudaStream_t stream) {
-  using C = Cfg<BN>;
-  CUtensorMap tmA, tmB, tmD, tmD2;
+  using C = Cfg<BN, PAIR>;
+  CUtensorMap tmA, tmB;
   int rc;
-  const int out_f32 = (g->epilogue == BB_EPI_ACCUM_F32 || g->epilogue == BB_EPI_STORE_F32);
-  rc = encode_2d(&tmD, g->D, g->M, g->N, g->ldd, out_f32 ? 32 : 64, BM, out_f32);
-  if (rc) return rc;
-  tmD2 = tmD;
-  if (g->epilogue == BB_EPI_BIAS_GELU) {
-    rc = encode_2d(&tmD2, g->D2, g->M, g->N, g->ldd, 64, BM, 0);
-    if (rc) return rc;
-  } else if (g->epilogue == BB_EPI_MUL_DGELU || g->epilogue == BB_EPI_BIAS_RESIDUAL) {
-    rc = encode_2d(&tmD2, g->aux, g->M, g->N, g->ld_aux ? g->ld_aux : g->ldd, 64, BM, 0);   // the aux operand
-    if (rc) return rc;
-  }
   if (!g->a_mn_major) rc = encode_2d(&tmA, g->A, g->M, g->K, g->lda, BK, BM);
   else rc = encode_2d(&tmA, g->A, g->K, g->M, g->lda, 64, BK);
   if (rc) return rc;
-  if (!g->b_mn_major) rc = encode_2d(&tmB, g->B, g->N, g->K, g->ldb, BK, BN);
+  if (!g->b_mn_major) rc = encode_2d(&tmB, g->B, g->N, g->K, g->ldb, BK, C::B_ROWS);
   else rc = encode_2d(&tmB, g->B, g->K, g->N, g->ldb, 64, BK);
   if (rc) return rc;
   GemmParams p;
@@ -355,7 +461,8 @@ int launch(const bb_gemm_desc* g, cudaStream_t stream) {
   p.D = g->D; p.D2 = g->D2; p.bias = g->bias; p.aux = g->aux; p.ldd = g->ldd; p.ld_aux = g->ld_aux ? g->ld_aux : g->ldd;
   p.status = bb_device_status_word();
   const int total_kb = (g->K + BK - 1) / BK;
-  const int mn_tiles = ((g->M + BM - 1) / BM) * ((g->N + BN - 1) / BN);
+  const int mn_tiles = ((g->M + C::TILE_M - 1) / C::TILE_M) * ((g->N + BN - 1) / BN);
+  const int workers_max = PAIR ? bb_num_sms() / 2 : bb_num_sms();
   int ksplit = 1;
   if (g->epilogue == BB_EPI_ACCUM_F32) {
     if (g->split_k > 0) {
@@ -363,7 +470,7 @@ int launch(const bb_gemm_desc* g, cudaStream_t stream) {
     } else {
       // too few output tiles to fill the machine: split the reduction; partial sums meet in
       // the fp32 add-reduction of the epilogue.  Cost model: waves x (k-blocks + fixed overhead).
-      const int sms = bb_num_sms();
+      const int sms = workers_max;
       long long best = -1;
       for (int s = 1; s <= 16; ++s) {
         const int kbs = (total_kb + s - 1) / s;
@@ -380,14 +487,26 @@ int launch(const bb_gemm_desc* g, cudaStream_t stream) {
   p.ksplit = (total_kb + p.kb_per_split - 1) / p.kb_per_split;   // no empty splits
   static bool attr_set = false;
   if (!attr_set) {
-    BB_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    BB_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     attr_set = true;
   }
   const int tiles = mn_tiles * p.ksplit;
-  int grid = bb_num_sms();
-  if (g->max_ctas > 0 && g->max_ctas < grid) grid = g->max_ctas;
-  if (tiles < grid) grid = tiles;
-  gemm_bf16_tcgen05_kernel<BN><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, tmD, tmD2, p);
+  int workers = workers_max;
+  if (g->max_ctas > 0 && g->max_ctas / (PAIR ? 2 : 1) < workers) workers = g->max_ctas / (PAIR ? 2 : 1);
+  if (workers < 1) workers = 1;
+  if (tiles < workers) workers = tiles;
+  if constexpr (PAIR) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * workers); cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    BB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<BN, true>, tmA, tmB, p));
+  } else {
+    gemm_bf16_tcgen05_kernel<BN, false><<<workers, NUM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  }
   BB_CUDA_CHECK(cudaGetLastError());
   return BB_OK;
 }
@@ -417,6 +536,14 @@ extern "C" int bb_gemm_bf16(const bb_gemm_desc* g, void* stream) {
   // cuTensorMapEncodeTiled is a driver call and needs a context bound to the calling thread;
   // a thread that has only ever set its device (autograd worker threads) has none yet.
   if (int rc = bbhost::bind_context()) return rc;
+  // CTA pairs (256 x 256 per pair) pay off on long reductions and on long runs of tiles per
+  // CTA; short problems are quicker to start and drain as single CTAs (measured on B200:
+  // K >= 3072 or >= 40 tiles per CTA 2-6 % faster as pairs, K = 1024 with <= 7 tiles 4-8 % slower)
+  const long long tiles_single = (long long)((g->M + BM - 1) / BM) * ((g->N + 255) / 256);
+  const bool pair = g->cta_pair > 0 ||
+                    (g->cta_pair == 0 && g->tile_n == 0 && g->M > BM && g->N > 128 &&
+                     (g->K >= 2048 || tiles_single >= 16LL * bb_num_sms()));
+  if (pair) return launch<256, true>(g, s);
   int bn = g->tile_n;
   if (bn == 0) {
     // 256-wide tiles halve the A re-reads; use them when they still fill the machine
@@ -424,8 +551,8 @@ extern "C" int bb_gemm_bf16(const bb_gemm_desc* g, void* stream) {
     // the add-reduction epilogue can split K to fill the machine, so it always takes wide tiles
     bn = (g->N > 128 && (tiles256 >= bb_num_sms() || e == BB_EPI_ACCUM_F32)) ? 256 : 128;
   }
-  if (bn == 256) return launch<256>(g, s);
-  if (bn == 128) return launch<128>(g, s);
+  if (bn == 256) return launch<256, false>(g, s);
+  if (bn == 128) return launch<128, false>(g, s);
   bb_set_last_error_msg("bb_gemm_bf16: tile_n must be 0, 128 or 256");
   return BB_ERR_INVALID_ARG;
 }

@@ -774,9 +774,17 @@ class PipelineEngine:
             self.global_store.set(str(src), "1")
             raise NextStageException(e)
 
+    def _join_wgrad_stream(self):
+        """Weight gradients are produced on a side stream by the sm_100a layers; everything that
+        reads the gradient arena (all-reduce, optimizer, gradient capture) waits for it first."""
+        if self.native:
+            from .layers import wgrad_sync
+            wgrad_sync(self.device)
+
     def _exec_reduce_grads(self, stage_id):
         """Average the stage's gradients over its data-parallel column: one all-reduce over
         the flat fp32 gradient arena, 1/dp folded into the optimizer kernel."""
+        self._join_wgrad_stream()
         self._reduce_scale = getattr(self, "_reduce_scale", {})
         self._reduce_scale[stage_id] = 1.0
         if self.dp_world_size > 1 and self.dist is not None:
@@ -792,6 +800,7 @@ class PipelineEngine:
             # shadow forwards read the shadow weights the state transfer is about to overwrite
             torch.cuda.current_stream().wait_event(self._rc_event)
             self._rc_event = None
+        self._join_wgrad_stream()
         scales = getattr(self, "_reduce_scale", {})
         if getattr(self, "capture_grads", False):
             self.last_grads = {sid: self.arenas[sid].grad.clone() * scales.get(sid, 1.0) for sid in self.stage_ids}

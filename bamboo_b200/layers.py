@@ -38,17 +38,51 @@ def _main_grad(p):
 
 
 # ----------------------------------------------------------------------------------- functions
+_side_streams = {}
+# False: weight-gradient work stays on the launching stream (used when kernels are timed one by
+# one with events, which concurrent work on a second stream would distort)
+WGRAD_SIDE_STREAM = True
+
+
+def _wgrad_stream(device):
+    """Per-device side stream for weight-gradient work.  Weight gradients are off the backward
+    critical path (nothing downstream reads them before the optimizer step), so their GEMMs and
+    bias column sums run beside the input-gradient chain and fill the SMs that the tail of each
+    persistent GEMM leaves idle."""
+    st = _side_streams.get(device.index)
+    if st is None:
+        st = torch.cuda.Stream(device=device)
+        _side_streams[device.index] = st
+    return st
+
+
+def wgrad_sync(device):
+    """Make the current stream wait for all weight-gradient work issued so far on ``device``."""
+    st = _side_streams.get(device.index if device.index is not None else torch.cuda.current_device())
+    if st is not None:
+        torch.cuda.current_stream(device).wait_stream(st)
+
+
 def _linear_backward(dy2d, x2d, weight, bias, dx_out=None, dx_epilogue=L.EPI_STORE, aux=None, need_dx=True):
     """dx = dy @ W (optionally through a fused epilogue); dW += dy^T x ; db += colsum(dy)."""
     T, n_out = dy2d.shape
     n_in = weight.shape[1]
+    main = torch.cuda.current_stream(dy2d.device)
+    side = _wgrad_stream(dy2d.device) if WGRAD_SIDE_STREAM else main
+    if side is not main:
+        side.wait_stream(main)                   # dy (and x) are ready on the main stream
+    with torch.cuda.stream(side):
+        L.gemm(dy2d, x2d, _main_grad(weight), a_mn=True, b_mn=True, epilogue=L.EPI_ACCUM_F32, M=n_out, N=n_in, K=T)
+        if bias is not None:
+            L.colsum_accum(dy2d, _main_grad(bias), tag="wgrad")
+    if side is not main:
+        # the caching allocator must not hand these buffers out again before the side stream is done
+        dy2d.record_stream(side)
+        x2d.record_stream(side)
     dx = None
     if need_dx:
         dx = dx_out if dx_out is not None else torch.empty(T, n_in, dtype=torch.bfloat16, device=dy2d.device)
         L.gemm(dy2d, weight, dx, b_mn=True, epilogue=dx_epilogue, aux=aux, M=T, N=n_in, K=n_out)
-    L.gemm(dy2d, x2d, _main_grad(weight), a_mn=True, b_mn=True, epilogue=L.EPI_ACCUM_F32, M=n_out, N=n_in, K=T)
-    if bias is not None:
-        L.colsum_accum(dy2d, _main_grad(bias))
     return dx
 
 

@@ -31,6 +31,7 @@ class GemmDesc(ctypes.Structure):
         ("tile_n", ctypes.c_int),
         ("max_ctas", ctypes.c_int),
         ("split_k", ctypes.c_int),
+        ("cta_pair", ctypes.c_int),
     ]
 
 
@@ -84,8 +85,13 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+# Process-wide default for GemmDesc.cta_pair (0 = library heuristic, 1 = pairs, -1 = single CTAs);
+# BB_GEMM_CTA_PAIR in the environment sets it, for A/B measurements of the two kernels.
+GEMM_CTA_PAIR = int(os.environ.get("BB_GEMM_CTA_PAIR", "0"))
+
+
 def gemm(a, b, out, *, a_mn=False, b_mn=False, epilogue=EPI_STORE, bias=None, out2=None, aux=None,
-         M=None, N=None, K=None, tile_n=0, max_ctas=0, split_k=0):
+         M=None, N=None, K=None, tile_n=0, max_ctas=0, split_k=0, cta_pair=0):
     """out[M,N] = op(a)[M,K] @ op(b)[N,K]^T with a fused epilogue; see bb_gemm_bf16.
 
     ``a`` is [M,K] (or [K,M] when ``a_mn``), ``b`` is [N,K] (or [K,N] when ``b_mn``); 2-D,
@@ -103,7 +109,8 @@ def gemm(a, b, out, *, a_mn=False, b_mn=False, epilogue=EPI_STORE, bias=None, ou
     d = GemmDesc(M=M, N=N, K=K, A=_ptr(a), lda=a.stride(0), a_mn_major=int(a_mn),
                  B=_ptr(b), ldb=b.stride(0), b_mn_major=int(b_mn), D=_ptr(out), ldd=out.stride(0),
                  epilogue=epilogue, bias=_ptr(bias), D2=_ptr(out2), aux=_ptr(aux),
-                 ld_aux=aux.stride(0) if aux is not None else 0, tile_n=tile_n, max_ctas=max_ctas, split_k=split_k)
+                 ld_aux=aux.stride(0) if aux is not None else 0, tile_n=tile_n, max_ctas=max_ctas, split_k=split_k,
+                 cta_pair=cta_pair or GEMM_CTA_PAIR)
     global LAUNCHES
     LAUNCHES += 1
     if gemm_hook is not None:
@@ -169,15 +176,16 @@ def layernorm_bwd_static(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta):
     return dx
 
 
-def colsum_accum(dy, out):
-    """out(fp32)[n] += dy(bf16)[rows, n].sum(0)"""
+def colsum_accum(dy, out, tag="rowwise"):
+    """out(fp32)[n] += dy(bf16)[rows, n].sum(0); ``tag`` names the scratch buffer (calls that may
+    overlap on the GPU, e.g. on different streams, need different ones)"""
     global LAUNCHES
     LAUNCHES += 2
     rows, n = dy.shape
     lib = load()
     lib.bb_colsum_workspace_bytes.restype = _LL
     need = lib.bb_colsum_workspace_bytes(_I(rows), _I(n))
-    ws = workspace(need, "rowwise")
+    ws = workspace(need, tag)
     check(lib.bb_colsum_accum(_ptr(dy), _LL(dy.stride(0)), _ptr(out), _ptr(ws), _LL(ws.numel()), _I(rows), _I(n),
                               _stream()), "bb_colsum_accum")
     return out

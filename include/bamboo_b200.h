@@ -60,6 +60,7 @@ typedef struct bb_gemm_desc {
   int tile_n;                       /* 0 = choose, else 128 or 256                      */
   int max_ctas;                     /* 0 = one per SM; else cap (leaves SMs to a concurrent stream) */
   int split_k;                      /* BB_EPI_ACCUM_F32 only: 0 = choose, else number of K splits */
+  int cta_pair;                     /* 0 = choose, 1 = CTA pairs (cta_group::2, 256 x 256 tiles), -1 = single CTAs */
 } bb_gemm_desc;
 
 /* D[M,N] = op(A)[M,K] * op(B)[N,K]^T, bf16 operands, fp32 accumulation in tensor memory

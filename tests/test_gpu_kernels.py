@@ -28,8 +28,8 @@ def gelu(x):
 
 
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
-@pytest.mark.parametrize("tile_n", [128, 256])
-def test_gemm_operand_layouts(L, a_mn, b_mn, tile_n):
+@pytest.mark.parametrize("tile_n,cta_pair", [(128, -1), (256, -1), (0, 1)])
+def test_gemm_operand_layouts(L, a_mn, b_mn, tile_n, cta_pair):
     torch.manual_seed(0)
     M, N, K = 384, 512, 320
     A = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
@@ -37,23 +37,37 @@ def test_gemm_operand_layouts(L, a_mn, b_mn, tile_n):
     a = A.t().contiguous() if a_mn else A
     b = B.t().contiguous() if b_mn else B
     out = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
-    L.gemm(a, b, out, a_mn=a_mn, b_mn=b_mn, M=M, N=N, K=K, tile_n=tile_n)
+    L.gemm(a, b, out, a_mn=a_mn, b_mn=b_mn, M=M, N=N, K=K, tile_n=tile_n, cta_pair=cta_pair)
     close(out, A.float() @ B.float().t())
 
 
-@pytest.mark.parametrize("shape", [(128, 128, 64), (200, 136, 72), (130, 264, 200), (8, 8, 8), (1024, 1024, 1000)])
-def test_gemm_ragged_shapes(L, shape):
+@pytest.mark.parametrize("cta_pair", [-1, 1])
+@pytest.mark.parametrize("shape", [(128, 128, 64), (200, 136, 72), (130, 264, 200), (8, 8, 8), (1024, 1024, 1000),
+                                   (100, 260, 136), (520, 100, 72)])
+def test_gemm_ragged_shapes(L, shape, cta_pair):
+    """Edges: rows and columns that end inside a tile, inside a 16-byte store, or (pairs) before
+    the second CTA's rows begin."""
     torch.manual_seed(1)
     M, N, K = shape
     A = torch.randn(M, K, device="cuda").bfloat16()
     B = torch.randn(N, K, device="cuda").bfloat16()
-    bias = torch.randn(N, device="cuda").bfloat16()
-    out = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
-    L.gemm(A, B, out, epilogue=L.EPI_BIAS, bias=bias)
-    close(out, A.float() @ B.float().t() + bias.float())
+    bias = torch.randn(N + 8, device="cuda").bfloat16()[:N]
+    ldd = (N + 7) // 8 * 8 + 8                                       # guard columns after N
+    out = torch.full((M, ldd), 7.0, device="cuda", dtype=torch.bfloat16)
+    L.gemm(A, B, out[:, :N], epilogue=L.EPI_BIAS, bias=bias, cta_pair=cta_pair)
+    close(out[:, :N], A.float() @ B.float().t() + bias.float())
+    assert torch.all(out[:, N:] == 7)                               # nothing written past column N
+    aux = torch.randn(M, ldd, device="cuda").bfloat16()[:, :N]
+    L.gemm(A, B, out[:, :N], epilogue=L.EPI_BIAS_RESIDUAL, bias=bias, aux=aux, cta_pair=cta_pair)
+    close(out[:, :N], A.float() @ B.float().t() + bias.float() + aux.float())
+    acc = torch.full((M, ldd), 7.0, device="cuda")
+    L.gemm(A, B, acc[:, :N], epilogue=L.EPI_ACCUM_F32, cta_pair=cta_pair)
+    close(acc[:, :N], A.float() @ B.float().t() + 7, 1e-3)
+    assert torch.all(acc[:, N:] == 7)
 
 
-def test_gemm_epilogues(L):
+@pytest.mark.parametrize("cta_pair", [-1, 1])
+def test_gemm_epilogues(L, cta_pair):
     torch.manual_seed(2)
     M, N, K = 384, 768, 320
     A = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
@@ -63,20 +77,20 @@ def test_gemm_epilogues(L):
     ref = A.float() @ B.float().t()
     out = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
     out2 = torch.zeros_like(out)
-    L.gemm(A, B, out, epilogue=L.EPI_BIAS_GELU, bias=bias, out2=out2)
+    L.gemm(A, B, out, epilogue=L.EPI_BIAS_GELU, bias=bias, out2=out2, cta_pair=cta_pair)
     close(out2, ref + bias.float())
     close(out, gelu((ref + bias.float()).bfloat16().float()))
-    L.gemm(A, B, out, epilogue=L.EPI_BIAS_RESIDUAL, bias=bias, aux=aux)
+    L.gemm(A, B, out, epilogue=L.EPI_BIAS_RESIDUAL, bias=bias, aux=aux, cta_pair=cta_pair)
     close(out, ref + bias.float() + aux.float())
     x = aux.float().requires_grad_(True)
     gelu(x).sum().backward()
-    L.gemm(A, B, out, epilogue=L.EPI_MUL_DGELU, aux=aux)
+    L.gemm(A, B, out, epilogue=L.EPI_MUL_DGELU, aux=aux, cta_pair=cta_pair)
     close(out, ref * x.grad)
     acc = torch.randn(M, N, device="cuda")
     want = acc + ref
-    L.gemm(A, B, acc, epilogue=L.EPI_ACCUM_F32)
+    L.gemm(A, B, acc, epilogue=L.EPI_ACCUM_F32, cta_pair=cta_pair)
     close(acc, want, 1e-3)
-    L.gemm(A, B, acc, epilogue=L.EPI_STORE_F32)
+    L.gemm(A, B, acc, epilogue=L.EPI_STORE_F32, cta_pair=cta_pair)
     close(acc, ref, 1e-3)
 
 
@@ -97,8 +111,9 @@ def test_gemm_is_linear_and_deterministic_at_full_size(L):
     assert torch.equal(o1[:256], (A1[:256].float() @ B.float().t()))
 
 
+@pytest.mark.parametrize("cta_pair", [-1, 1])
 @pytest.mark.parametrize("split", [0, 1, 3, 8])
-def test_gemm_split_k_accumulation(L, split):
+def test_gemm_split_k_accumulation(L, split, cta_pair):
     """Weight-gradient shape (few output tiles, long reduction): partial sums of the K splits
     meet in the fp32 add-reduction."""
     torch.manual_seed(11)
@@ -106,7 +121,7 @@ def test_gemm_split_k_accumulation(L, split):
     A = torch.randint(-3, 4, (K, M), device="cuda").bfloat16()      # stored [K, M]
     B = torch.randint(-3, 4, (K, N), device="cuda").bfloat16()      # stored [K, N]
     acc = torch.ones(M, N, device="cuda")
-    L.gemm(A, B, acc, a_mn=True, b_mn=True, epilogue=L.EPI_ACCUM_F32, M=M, N=N, K=K, split_k=split)
+    L.gemm(A, B, acc, a_mn=True, b_mn=True, epilogue=L.EPI_ACCUM_F32, M=M, N=N, K=K, split_k=split, cta_pair=cta_pair)
     want = A.float().t() @ B.float() + 1
     assert torch.equal(acc, want)                                    # small integers: exact
 
