@@ -82,6 +82,13 @@ __device__ __forceinline__ void atom_store_row(uint8_t* atom, int row, const uin
   for (int c = 0; c < 8; ++c)
     *reinterpret_cast<uint4*>(base + ((c ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
 }
+// half a row (64 bytes: chunks 4*half .. 4*half+3) of a [128 x 64] bf16 atom from 16 packed registers
+__device__ __forceinline__ void atom_store_half_row(uint8_t* atom, int row, int half, const uint32_t* pk) {
+  uint8_t* base = atom + row * 128;
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+    *reinterpret_cast<uint4*>(base + (((4 * half + c) ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+}
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -108,6 +115,17 @@ __device__ __forceinline__ void ld32(uint32_t taddr, float* v) {
 __device__ __forceinline__ void store_row64(__nv_bfloat16* dst, const float* v, float mul) {
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
+    uint4 q;
+    q.x = bb::pack_bf16x2(v[8 * c + 0] * mul, v[8 * c + 1] * mul); q.y = bb::pack_bf16x2(v[8 * c + 2] * mul, v[8 * c + 3] * mul);
+    q.z = bb::pack_bf16x2(v[8 * c + 4] * mul, v[8 * c + 5] * mul); q.w = bb::pack_bf16x2(v[8 * c + 6] * mul, v[8 * c + 7] * mul);
+    reinterpret_cast<uint4*>(dst)[c] = q;
+  }
+}
+
+// 32 fp32 values of one row -> bf16 in global memory (64 contiguous bytes)
+__device__ __forceinline__ void store_row32(__nv_bfloat16* dst, const float* v, float mul) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
     uint4 q;
     q.x = bb::pack_bf16x2(v[8 * c + 0] * mul, v[8 * c + 1] * mul); q.y = bb::pack_bf16x2(v[8 * c + 2] * mul, v[8 * c + 3] * mul);
     q.z = bb::pack_bf16x2(v[8 * c + 4] * mul, v[8 * c + 5] * mul); q.w = bb::pack_bf16x2(v[8 * c + 6] * mul, v[8 * c + 7] * mul);
@@ -617,7 +635,12 @@ attn_tc_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* _
 // =====================================================================================
 constexpr int SUB = 64;                          // streamed rows per sub-block
 constexpr int SUB_BYTES = SUB * HD * 2;          // 8 KiB: [64 x 64] bf16
-constexpr int NT2 = 320;
+// Two compute groups of 8 warps.  A row's 64 scores are split between two threads (warps w and
+// w + 4 of a group reach the same TMEM lane quarter): the element-wise work has no row
+// reductions here, and four compute warps per scheduler hide the TMEM-load and ALU latencies that
+// two could not (issue slots were 35 % busy with 4-warp groups).
+constexpr int GROUP_THREADS = 256;
+constexpr int NT2 = 64 + 2 * GROUP_THREADS;
 constexpr int NST = 6;                           // streamed sub-tile ring depth
 constexpr int NSB = 3;                           // score buffers in tensor memory
 
@@ -656,8 +679,8 @@ attn_tc_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     ctl->abort_flag = 0;
     bb::mbar_init(q_full, 1);
     for (int i = 0; i < NST; ++i) { bb::mbar_init(&kv_full[i], 1); bb::mbar_init(&kv_empty[i], 1); }
-    for (int i = 0; i < NSB; ++i) { bb::mbar_init(&s_full[i], 1); bb::mbar_init(&s_empty[i], 4); }
-    for (int i = 0; i < 2; ++i) { bb::mbar_init(&ds_full[i], 4); bb::mbar_init(&ds_empty[i], 1); }
+    for (int i = 0; i < NSB; ++i) { bb::mbar_init(&s_full[i], 1); bb::mbar_init(&s_empty[i], GROUP_THREADS / 32); }
+    for (int i = 0; i < 2; ++i) { bb::mbar_init(&ds_full[i], GROUP_THREADS / 32); bb::mbar_init(&ds_empty[i], 1); }
     bb::mbar_init(acc_full, 1);
     bb::fence_barrier_init();
     bb::tma_prefetch_desc(&tm_q); bb::tma_prefetch_desc(&tm_kv); bb::tma_prefetch_desc(&tm_do);
@@ -720,7 +743,8 @@ attn_tc_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       }
     }
   } else {
-    const int g = (warp - 2) >> 2;                           // compute group = buffer index
+    const int g = (warp - 2) >> 3;                           // compute group = buffer index
+    const int hf = ((warp - 2) >> 2) & 1;                    // which 32 of the sub-block's 64 columns
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const int qrow = q0 + row;
@@ -737,49 +761,47 @@ attn_tc_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       const int sb = j % NSB;
       const uint32_t tS = tmem + 64 * sb, tDP = tmem + 192 + 64 * sb;
       const bool ok = bb::mbar_wait_spin(&s_full[sb], (j / NSB) & 1, &ctl->abort_flag, p.status);
-      if (!bb::named_bar_all(3 + g, 128, ok)) { alive = false; break; }
+      if (!bb::named_bar_all(3 + g, GROUP_THREADS, ok)) { alive = false; break; }
       bb::tc_fence_after_sync();
-      const int c0 = j * SUB;
+      const int c0 = j * SUB + hf * 32;
       // only sub-blocks that touch the sequence end or the causal diagonal need per-element masks
-      const bool need_mask = (c0 + SUB > p.S) || (p.causal && c0 + SUB - 1 > q0);
+      const bool need_mask = (c0 + 32 > p.S) || (p.causal && c0 + 32 - 1 > q0);
       const float nlse = -lse;
-      uint32_t pk[32];                                       // the row's 64 dS values as bf16 pairs
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      uint32_t pk[16];                                       // this thread's 32 dS values as bf16 pairs
+      {
         float sv[32], dp[32];
-        ld32x2(tS + lane_addr + c * 32, tDP + lane_addr + c * 32, sv, dp);
+        ld32x2(tS + lane_addr + hf * 32, tDP + lane_addr + hf * 32, sv, dp);
         if (!need_mask) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) dp[i] = ex2(fmaf(sv[i], sl, nlse)) * (dp[i] - dl);
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const int col = c0 + c * 32 + i;
+            const int col = c0 + i;
             float pv = ex2(fmaf(sv[i], sl, nlse));
             if (col >= p.S || (p.causal && col > qrow)) pv = 0.f;
             dp[i] = pv * (dp[i] - dl);
           }
         }
-        pack32(dp, pk + 16 * c);
+        pack32(dp, pk);
       }
       bb::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) bb::mbar_arrive(&s_empty[sb]);          // scores consumed: the MMA warp may refill
       // the staging buffer is free once the dQ update that read it two sub-blocks ago retired
       const bool ok2 = bb::mbar_wait_spin(&ds_empty[g], (n & 1) ^ 1, &ctl->abort_flag, p.status);
-      if (!bb::named_bar_all(3 + g, 128, ok2)) { alive = false; break; }
-      atom_store_row(myDS, row, pk);
+      if (!bb::named_bar_all(3 + g, GROUP_THREADS, ok2)) { alive = false; break; }
+      atom_store_half_row(myDS, row, hf, pk);
       bb::fence_proxy_async();
       __syncwarp();
       if (lane == 0) bb::mbar_arrive(&ds_full[g]);
     }
     const bool fin = alive && bb::mbar_wait_spin(acc_full, 0, &ctl->abort_flag, p.status);
-    if (bb::named_bar_all(3 + g, 128, fin) && g == 0) {
+    if (bb::named_bar_all(3 + g, GROUP_THREADS, fin) && g == 0) {
       bb::tc_fence_after_sync();
-      float v[64];
-      ld32(tDQ + lane_addr, v);
-      ld32(tDQ + lane_addr + 32, v + 32);
-      if (qrow < p.S) store_row64(p.dq + (long long)(row_base + qrow) * p.stride_dqkv + colq, v, p.scale);
+      float v[32];
+      ld32(tDQ + lane_addr + hf * 32, v);
+      if (qrow < p.S) store_row32(p.dq + (long long)(row_base + qrow) * p.stride_dqkv + colq + hf * 32, v, p.scale);
     }
   }
   bb::tc_fence_before_sync();
@@ -829,8 +851,8 @@ attn_tc_dkv2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
     ctl->abort_flag = 0;
     bb::mbar_init(kv_full, 1);
     for (int i = 0; i < NST; ++i) { bb::mbar_init(&q_full[i], 1); bb::mbar_init(&q_empty[i], 1); }
-    for (int i = 0; i < NSB; ++i) { bb::mbar_init(&s_full[i], 1); bb::mbar_init(&s_empty[i], 4); }
-    for (int i = 0; i < 2; ++i) { bb::mbar_init(&p_full[i], 4); bb::mbar_init(&p_empty[i], 1); }
+    for (int i = 0; i < NSB; ++i) { bb::mbar_init(&s_full[i], 1); bb::mbar_init(&s_empty[i], GROUP_THREADS / 32); }
+    for (int i = 0; i < 2; ++i) { bb::mbar_init(&p_full[i], GROUP_THREADS / 32); bb::mbar_init(&p_empty[i], 1); }
     bb::mbar_init(acc_full, 1);
     bb::fence_barrier_init();
     bb::tma_prefetch_desc(&tm128); bb::tma_prefetch_desc(&tm64); bb::tma_prefetch_desc(&tm_do64);
@@ -897,10 +919,11 @@ attn_tc_dkv2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
       }
     }
   } else {
-    const int g = (warp - 2) >> 2;
+    const int g = (warp - 2) >> 3;
+    const int hf = ((warp - 2) >> 2) & 1;                  // which 32 of the sub-block's 64 query columns
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;                   // key row inside the tile
-    const int gt = threadIdx.x - 64 - 128 * g;             // thread index inside the group
+    const int gt = threadIdx.x - 64 - GROUP_THREADS * g;   // thread index inside the group
     const int krow = k0 + row;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const float* lse_g = p.lse + ((long long)batch * p.H + head) * p.S;
@@ -921,9 +944,9 @@ attn_tc_dkv2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
     for (int i = g; i < nblk && alive; i += 2, ++n) {
       const int qc0 = (qstart + i) * SUB;
       // (the group's previous readers are past their last use once everybody is through this barrier)
-      bb::named_bar_sync(1 + g, 128);
+      bb::named_bar_sync(1 + g, GROUP_THREADS);
       if (gt < SUB) { my_lse[gt] = nx_lse; my_delta[gt] = nx_delta; }
-      bb::named_bar_sync(1 + g, 128);
+      bb::named_bar_sync(1 + g, GROUP_THREADS);
       if (gt < SUB && i + 2 < nblk) {
         const int q = (qstart + i + 2) * SUB + gt;
         nx_lse = (q < p.S) ? lse_g[q] * LOG2E : 0.f;
@@ -932,56 +955,54 @@ attn_tc_dkv2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
       const int sb = i % NSB;
       const uint32_t tS = tmem + 64 * sb, tDP = tmem + 192 + 64 * sb;
       const bool ok = bb::mbar_wait_spin(&s_full[sb], (i / NSB) & 1, &ctl->abort_flag, p.status);
-      if (!bb::named_bar_all(3 + g, 128, ok)) { alive = false; break; }
+      if (!bb::named_bar_all(3 + g, GROUP_THREADS, ok)) { alive = false; break; }
       bb::tc_fence_after_sync();
       const bool need_mask = (qc0 + SUB > p.S) || (p.causal && k0 + TQ - 1 > qc0);
-      uint32_t pkP[32], pkDS[32];                            // the row's 64 P^T and dS^T values as bf16 pairs
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      uint32_t pkP[16], pkDS[16];                            // this thread's 32 P^T and dS^T values as bf16 pairs
+      {
         float sv[32], dp[32];
-        ld32x2(tS + lane_addr + c * 32, tDP + lane_addr + c * 32, sv, dp);
+        ld32x2(tS + lane_addr + hf * 32, tDP + lane_addr + hf * 32, sv, dp);
 #pragma unroll
         for (int e4 = 0; e4 < 32; e4 += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(my_lse + c * 32 + e4);
-          const float4 d4 = *reinterpret_cast<const float4*>(my_delta + c * 32 + e4);
+          const float4 l4 = *reinterpret_cast<const float4*>(my_lse + hf * 32 + e4);
+          const float4 d4 = *reinterpret_cast<const float4*>(my_delta + hf * 32 + e4);
           const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, ds[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int e = e4 + u;
             float pv = ex2(fmaf(sv[e], sl, -ls[u]));
             if (need_mask) {
-              const int q = qc0 + c * 32 + e;
+              const int q = qc0 + hf * 32 + e;
               if (q >= p.S || (p.causal && krow > q)) pv = 0.f;
             }
             sv[e] = pv;
             dp[e] = pv * (dp[e] - ds[u]);
           }
         }
-        pack32(sv, pkP + 16 * c);
-        pack32(dp, pkDS + 16 * c);
+        pack32(sv, pkP);
+        pack32(dp, pkDS);
       }
       bb::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) bb::mbar_arrive(&s_empty[sb]);
       // the staging buffers are free once the dV / dK update that read them retired
       const bool ok2 = bb::mbar_wait_spin(&p_empty[g], (n & 1) ^ 1, &ctl->abort_flag, p.status);
-      if (!bb::named_bar_all(3 + g, 128, ok2)) { alive = false; break; }
-      atom_store_row(myP, row, pkP);
-      atom_store_row(myDS, row, pkDS);
+      if (!bb::named_bar_all(3 + g, GROUP_THREADS, ok2)) { alive = false; break; }
+      atom_store_half_row(myP, row, hf, pkP);
+      atom_store_half_row(myDS, row, hf, pkDS);
       bb::fence_proxy_async();
       __syncwarp();
       if (lane == 0) bb::mbar_arrive(&p_full[g]);
     }
     const bool fin = alive && nblk > 0 && bb::mbar_wait_spin(acc_full, 0, &ctl->abort_flag, p.status);
-    if (bb::named_bar_all(3 + g, 128, fin)) {
+    if (bb::named_bar_all(3 + g, GROUP_THREADS, fin)) {
       bb::tc_fence_after_sync();
-      float v[64];
+      float v[32];
       // the two groups split the final stores: group 0 writes dV, group 1 writes dK
       const uint32_t src = (g == 0) ? tDV : tDK;
-      ld32(src + lane_addr, v);
-      ld32(src + lane_addr + 32, v + 32);
+      ld32(src + lane_addr + hf * 32, v);
       __nv_bfloat16* dst = (g == 0) ? p.dv : p.dk;
-      if (krow < p.S) store_row64(dst + (long long)(row_base + krow) * p.stride_dqkv + colq, v, g == 0 ? 1.f : p.scale);
+      if (krow < p.S) store_row32(dst + (long long)(row_base + krow) * p.stride_dqkv + colq + hf * 32, v, g == 0 ? 1.f : p.scale);
     }
   }
   bb::tc_fence_before_sync();

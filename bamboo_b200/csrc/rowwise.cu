@@ -199,11 +199,16 @@ layernorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat
 // out[j] += sum_p partials[p * stride + j].  A 32-column x 8-way block: eight threads share
 // a column, each sums every eighth partial, shared memory combines them in a fixed order
 // (deterministic).
+// blockIdx.y selects one of two (partials, out) pairs, `pair_offset` floats apart in `partials`
+// (LayerNorm: dgamma and dbeta in one launch).
 __global__ void __launch_bounds__(256)
-reduce_partials_kernel(const float* __restrict__ partials, float* __restrict__ out, int nparts, int n, long long stride) {
+reduce_partials_kernel(const float* __restrict__ partials, float* __restrict__ out0, float* __restrict__ out1,
+                       long long pair_offset, int nparts, int n, long long stride) {
   __shared__ float red[8][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int j = blockIdx.x * 32 + tx;
+  float* out = blockIdx.y ? out1 : out0;
+  partials += blockIdx.y * pair_offset;
   float s = 0.f;
   if (j < n)
     for (int p = ty; p < nparts; p += 8) s += partials[(size_t)p * stride + j];
@@ -373,8 +378,7 @@ extern "C" int bb_layernorm_bwd(const void* dy, const void* x, const void* gamma
   const int grid = ln_bwd_grid(rows, h);
   float* ws = (float*)workspace;
   if (int rc = ln_bwd_main(dy, x, gamma, mean, rstd, dres, dx, ws, rows, h, grid, warps, s)) return rc;
-  reduce_partials_kernel<<<(h + 31) / 32, 256, 0, s>>>(ws, dgamma, grid, h, 2LL * h);
-  reduce_partials_kernel<<<(h + 31) / 32, 256, 0, s>>>(ws + h, dbeta, grid, h, 2LL * h);
+  reduce_partials_kernel<<<dim3((h + 31) / 32, 2), 256, 0, s>>>(ws, dgamma, dbeta, (long long)h, grid, h, 2LL * h);
   BB_CUDA_CHECK(cudaGetLastError());
   return BB_OK;
 }
@@ -428,8 +432,7 @@ extern "C" int bb_layernorm_bwd_static(const void* dy, const void* x, const void
   // every partial row that the reduction reads is rewritten by this launch, so the scratch
   // needs no clearing although it still holds the previous call's sums
   if (int rc = ln_bwd_main(dy, x, gamma, mean, rstd, dres, dx, ws, rows, h, grid, warps, s)) return rc;
-  reduce_partials_kernel<<<(h + 31) / 32, 256, 0, s>>>(ws, dgamma, grid, h, 2LL * h);
-  reduce_partials_kernel<<<(h + 31) / 32, 256, 0, s>>>(ws + h, dbeta, grid, h, 2LL * h);
+  reduce_partials_kernel<<<dim3((h + 31) / 32, 2), 256, 0, s>>>(ws, dgamma, dbeta, (long long)h, grid, h, 2LL * h);
   BB_CUDA_CHECK(cudaGetLastError());
   return BB_OK;
 }
@@ -461,7 +464,7 @@ extern "C" int bb_colsum_accum(const void* dy, long long ld, float* out, void* w
   const int rps = (rows + splits - 1) / splits;
   dim3 grid((n + 255) / 256, splits);
   colsum_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)dy, (float*)workspace, rows, n, ld, rps);
-  reduce_partials_kernel<<<(n + 31) / 32, 256, 0, s>>>((const float*)workspace, out, splits, n, (long long)n);
+  reduce_partials_kernel<<<dim3((n + 31) / 32, 1), 256, 0, s>>>((const float*)workspace, out, nullptr, 0LL, splits, n, (long long)n);
   BB_CUDA_CHECK(cudaGetLastError());
   return BB_OK;
 }

@@ -259,6 +259,28 @@ def test_attention_rows_sum_to_one_at_full_size(L):
     assert torch.isfinite(lse).all()
 
 
+def test_attention_backward_checksums_at_full_size(L):
+    """GPT-2-medium attention shape, properties that hold at any size: every probability row sums
+    to one, so the V-gradient summed over keys equals dO summed over queries; and the score
+    gradient of a row sums to zero, so with all keys equal the Q-gradient vanishes."""
+    B, H, S, D = 8, 16, 1024, 64
+    torch.manual_seed(12)
+    qkv = (torch.randn(B * S, 3 * H * D, device="cuda") * 0.5).bfloat16()
+    qkv[:, H * D:2 * H * D] = qkv[0, H * D:2 * H * D]               # the same key vector at every position
+    out = torch.empty(B * S, H * D, device="cuda", dtype=torch.bfloat16)
+    lse = torch.empty(B, H, S, device="cuda")
+    L.attention_fwd(qkv, out, lse, B, H, S, D, True)
+    do = torch.randn_like(out)
+    dqkv = torch.empty_like(qkv)
+    L.attention_bwd(qkv, out, do, lse, dqkv, B, H, S, D, True)
+    dq, dv = dqkv[:, :H * D].float(), dqkv[:, 2 * H * D:].float()
+    want = do.float().view(B, S, H * D).sum(1)
+    got = dv.view(B, S, H * D).sum(1)
+    assert (got - want).abs().max().item() <= 2e-2 * want.abs().max().item() + 0.5   # bf16 rounding of 1024 addends
+    assert dq.abs().max().item() <= 2e-2 * do.float().abs().max().item()
+    assert L.read_status() == 0
+
+
 def test_status_word_is_clean(L):
     torch.cuda.synchronize()
     assert L.read_status() == 0
