@@ -485,14 +485,14 @@ namespace {
 // for head dimension 64; the tcgen05 forward still hands off serially per key block (379 us
 // against 120 us) and stays opt-in.  BB_ATTENTION_IMPL=tc / mma in the environment forces one
 // implementation for both directions.
-bool use_tc_path(const void* q, const void* k, const void* v, int H, int D, long long stride_qkv, bool backward) {
-  static int mode = -1;   // 0 = default split, 1 = all tcgen05, 2 = all warp-level
+bool use_tc_path(const void* q, const void* k, const void* v, int H, int D, long long stride_qkv) {
+  static int mode = -1;   // 0 = tcgen05 kernels where they apply (default), 2 = warp-level kernels only
   if (mode < 0) {
     const char* e = getenv("BB_ATTENTION_IMPL");
-    mode = (e && e[0] == 't') ? 1 : (e && e[0] == 'm') ? 2 : 0;
+    mode = (e && e[0] == 'm') ? 2 : 0;
   }
   if (D != 64 || mode == 2) return false;
-  if (mode == 0 && !backward) return false;
+  // the tcgen05 kernels address q, k and v through one tensor map over the packed projection
   const long long hb = (long long)H * D * 2;
   return (const char*)k - (const char*)q == hb && (const char*)v - (const char*)q == 2 * hb && stride_qkv >= 3LL * H * D &&
          (long long)H * D * 3 < (1LL << 31);
@@ -509,7 +509,7 @@ extern "C" int bb_attention_fwd(const void* q, const void* k, const void* v, voi
   AttnParams p = {};
   p.q = (const __nv_bfloat16*)q; p.k = (const __nv_bfloat16*)k; p.v = (const __nv_bfloat16*)v; p.out = (__nv_bfloat16*)out;
   p.lse = lse; p.stride_qkv = stride_qkv; p.stride_o = stride_o; p.B = B; p.H = H; p.S = S; p.causal = causal; p.scale = scale;
-  if (use_tc_path(q, k, v, H, D, stride_qkv, false))
+  if (use_tc_path(q, k, v, H, D, stride_qkv))
     return bb_attention_tc_fwd(q, out, lse, B, H, S, stride_qkv, stride_o, causal, scale, (cudaStream_t)stream);
   if (D == 64) return launch_fwd<64>(p, (cudaStream_t)stream);
   if (D == 128) return launch_fwd<128>(p, (cudaStream_t)stream);
@@ -542,7 +542,7 @@ extern "C" int bb_attention_bwd(const void* q, const void* k, const void* v, con
   p.lse = const_cast<float*>(lse); p.delta = (float*)workspace;
   p.stride_qkv = stride_qkv; p.stride_o = stride_o; p.stride_dqkv = stride_dqkv;
   p.B = B; p.H = H; p.S = S; p.causal = causal; p.scale = scale;
-  if (use_tc_path(q, k, v, H, D, stride_qkv, true))
+  if (use_tc_path(q, k, v, H, D, stride_qkv))
     return bb_attention_tc_bwd(q, out, d_out, lse, dq, dk, dv, (float*)workspace, B, H, S, stride_qkv, stride_o, stride_dqkv,
                                causal, scale, (cudaStream_t)stream);
   if (D == 64) return launch_bwd<64>(p, (cudaStream_t)stream);

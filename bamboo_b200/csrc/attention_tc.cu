@@ -7,10 +7,12 @@
 // nothing is transposed.  Probabilities are recomputed from the saved log-sum-exp in the
 // backward pass; scores never reach HBM.
 //
-// CTA = 192 threads: warp 0 issues TMA, warp 1 issues MMAs, warps 2-5 (one TMEM lane quarter
-// each, thread == tile row) do the softmax / elementwise work and the final stores.
-// Three kernels: forward (CTA owns 128 query rows), dQ (CTA owns 128 query rows), dK/dV (CTA
-// owns 128 key rows); the backward split keeps every sum in a fixed order (no atomics).
+// In every kernel warp 0 issues TMA, warp 1 issues MMAs and the remaining warps (one TMEM lane
+// quarter each) do the softmax / element-wise work and the final stores.  Three kernels:
+//   forward : CTA owns 256 query rows as two tiles in ping-pong (one compute group per tile);
+//   dQ      : CTA owns 128 query rows, streams 64-row key/value sub-tiles;
+//   dK, dV  : CTA owns 128 key rows, streams 64-row query / dO sub-tiles;
+// the backward split keeps every sum in a fixed order (no atomics).
 #include "tma_host.cuh"
 #include <math.h>
 
@@ -19,8 +21,6 @@ namespace {
 constexpr int TQ = 128;        // rows per tile (queries or keys)
 constexpr int HD = 64;         // head dimension
 constexpr int TILE_BYTES = TQ * HD * 2;          // 16 KiB: [128 x 64] bf16, 128-byte rows
-constexpr int SQ_BYTES = 2 * TILE_BYTES;         // 32 KiB: [128 x 128] bf16 as two 64-column atoms
-constexpr int NTHREADS = 192;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct TcParams {
@@ -41,46 +41,19 @@ __device__ __forceinline__ uint32_t idesc(int n, int a_mn, int b_mn) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) |
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TQ >> 4) << 24);
 }
+// Matrix descriptors.  The MMA-issuing warp shares its scheduler with compute warps, so the
+// instructions spent per MMA count: a tile's descriptor is built once (`desc_*0`) and every later
+// k-step only adds a constant to its address field (16-byte units; no carry into the next field
+// for any shared-memory address).
 // [rows x 64] tile, reduction over the 64 columns: k-step = 16 columns = 32 bytes
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile, int kstep) {
-  return bb::make_smem_desc_sw128(tile + kstep * 32, 16, 1024);
-}
+__device__ __forceinline__ uint64_t desc_k0(uint32_t tile) { return bb::make_smem_desc_sw128(tile, 16, 1024); }
+__device__ __forceinline__ uint64_t desc_kmajor(uint64_t d0, int kstep) { return d0 + (uint64_t)(kstep * (32 >> 4)); }
 // [rows x 64] tile, reduction over its rows (N or M = the 64 columns): k-step = 16 rows = 2 KiB
-__device__ __forceinline__ uint64_t desc_mnmajor64(uint32_t tile, int kstep) {
-  return bb::make_smem_desc_sw128(tile + kstep * 2048, 8192, 1024);
-}
-// [128 x 128] two-atom buffer, reduction over its 128 columns: k-step k lives in atom k/4
-__device__ __forceinline__ uint64_t desc_sq_kmajor(uint32_t buf, int kstep) {
-  return bb::make_smem_desc_sw128(buf + (kstep >> 2) * TILE_BYTES + (kstep & 3) * 32, 16, 1024);
-}
-// [128 x 128] two-atom buffer, reduction over its rows (M = the 128 columns, atoms 16 KiB apart)
-__device__ __forceinline__ uint64_t desc_sq_mnmajor(uint32_t buf, int kstep) {
-  return bb::make_smem_desc_sw128(buf + kstep * 2048, TILE_BYTES, 1024);
-}
-
-// 32 values of one row into a two-atom [128 x 128] bf16 buffer at columns c0 .. c0+31
-__device__ __forceinline__ void sq_store32(uint8_t* buf, int row, int c0, const float* v) {
-  uint8_t* base = buf + (c0 >> 6) * TILE_BYTES + row * 128;
-  const int chunk0 = (c0 & 63) >> 3;
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    uint4 q;
-    q.x = bb::pack_bf16x2(v[8 * c + 0], v[8 * c + 1]); q.y = bb::pack_bf16x2(v[8 * c + 2], v[8 * c + 3]);
-    q.z = bb::pack_bf16x2(v[8 * c + 4], v[8 * c + 5]); q.w = bb::pack_bf16x2(v[8 * c + 6], v[8 * c + 7]);
-    *reinterpret_cast<uint4*>(base + (((chunk0 + c) ^ (row & 7)) << 4)) = q;
-  }
-}
-
+__device__ __forceinline__ uint64_t desc_mn0(uint32_t tile) { return bb::make_smem_desc_sw128(tile, 8192, 1024); }
+__device__ __forceinline__ uint64_t desc_mnmajor64(uint64_t d0, int kstep) { return d0 + (uint64_t)(kstep * (2048 >> 4)); }
 __device__ __forceinline__ void pack32(const float* v, uint32_t* out16) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) out16[i] = bb::pack_bf16x2(v[2 * i], v[2 * i + 1]);
-}
-// one row of a [128 x 64] bf16 atom (128 bytes) from 32 packed registers
-__device__ __forceinline__ void atom_store_row(uint8_t* atom, int row, const uint32_t* pk) {
-  uint8_t* base = atom + row * 128;
-#pragma unroll
-  for (int c = 0; c < 8; ++c)
-    *reinterpret_cast<uint4*>(base + ((c ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
 }
 // half a row (64 bytes: chunks 4*half .. 4*half+3) of a [128 x 64] bf16 atom from 16 packed registers
 __device__ __forceinline__ void atom_store_half_row(uint8_t* atom, int row, int half, const uint32_t* pk) {
@@ -140,477 +113,6 @@ struct Ctl {
   int abort_flag;
 };
 
-// Compute warps wait together: the 128 threads either all proceed or all leave.
-__device__ __forceinline__ bool wait_all(uint64_t* bar, uint32_t parity, Ctl* ctl, int* status) {
-  const bool ok = bb::mbar_wait_spin(bar, parity, &ctl->abort_flag, status);
-  return bb::named_bar_all(2, 128, ok);
-}
-
-// ------------------------------------------------------------------ dQ
-// CTA owns query rows q0..q0+127 of one (batch, head); streams key/value tiles.
-//   S = Q K^T, dP = dO V^T  ->  dS = P o (dP - delta)  ->  dQ += dS K
-// smem: Q, dO (once) | K, V (2 stages) | dS [128 q x 128 kv] ; TMEM: S 128 | dP 128 | dQ 64
-__global__ void __launch_bounds__(NTHREADS, 1)
-attn_tc_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do, const TcParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;
-  uint8_t* sDO = sQ + TILE_BYTES;
-  uint8_t* sK = sDO + TILE_BYTES;              // 2 stages
-  uint8_t* sV = sK + 2 * TILE_BYTES;           // 2 stages
-  uint8_t* sDS = sV + 2 * TILE_BYTES;          // 32 KiB
-  Ctl* ctl = reinterpret_cast<Ctl*>(sDS + SQ_BYTES);
-  uint64_t* q_full = &ctl->bars[0];
-  uint64_t* kv_full = &ctl->bars[1];           // [2]
-  uint64_t* kv_empty = &ctl->bars[3];          // [2]
-  uint64_t* s_full = &ctl->bars[5];
-  uint64_t* s_empty = &ctl->bars[6];
-  uint64_t* ds_full = &ctl->bars[7];
-  uint64_t* ds_empty = &ctl->bars[8];
-  uint64_t* acc_full = &ctl->bars[9];
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
-  const int q0 = qb * TQ;
-  const int row_base = batch * p.S;            // token row of this batch in the [T, *] matrices
-  const int colq = head * HD, colk = p.hidden + head * HD, colv = 2 * p.hidden + head * HD;
-  int nkv = (p.S + TQ - 1) / TQ;
-  if (p.causal) nkv = min(nkv, qb + 1);
-
-  if (threadIdx.x == 0) {
-    ctl->abort_flag = 0;
-    bb::mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) { bb::mbar_init(&kv_full[i], 1); bb::mbar_init(&kv_empty[i], 1); }
-    bb::mbar_init(s_full, 1); bb::mbar_init(s_empty, 4);
-    bb::mbar_init(ds_full, 4); bb::mbar_init(ds_empty, 1);
-    bb::mbar_init(acc_full, 1);
-    bb::fence_barrier_init();
-    bb::tma_prefetch_desc(&tm_qkv); bb::tma_prefetch_desc(&tm_do);
-  }
-  if (warp == 1) { bb::tmem_alloc(&ctl->tmem_slot, 512); bb::tmem_relinquish(); }
-  bb::tc_fence_before_sync();
-  __syncthreads();
-  bb::tc_fence_after_sync();
-  const uint32_t tmem = ctl->tmem_slot;
-  const uint32_t tS = tmem, tDP = tmem + 128, tDQ = tmem + 256;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      bb::mbar_arrive_expect_tx(q_full, 2 * TILE_BYTES);
-      bb::tma_load_2d(sQ, &tm_qkv, q_full, colq, row_base + q0);
-      bb::tma_load_2d(sDO, &tm_do, q_full, colq, row_base + q0);
-      for (int j = 0; j < nkv; ++j) {
-        const int s = j & 1;
-        if (!bb::mbar_wait_spin(&kv_empty[s], ((j >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
-        bb::mbar_arrive_expect_tx(&kv_full[s], 2 * TILE_BYTES);
-        bb::tma_load_2d(sK + s * TILE_BYTES, &tm_qkv, &kv_full[s], colk, row_base + j * TQ);
-        bb::tma_load_2d(sV + s * TILE_BYTES, &tm_qkv, &kv_full[s], colv, row_base + j * TQ);
-      }
-    }
-  } else if (warp == 1) {
-    const uint32_t aQ = bb::smem_u32(sQ), aDO = bb::smem_u32(sDO), aDS = bb::smem_u32(sDS);
-    const uint32_t i_s = idesc(128, 0, 0), i_dq = idesc(64, 0, 1);
-    bool alive = bb::mbar_wait_spin(q_full, 0, &ctl->abort_flag, p.status);
-    for (int j = 0; j < nkv && alive; ++j) {
-      const int s = j & 1;
-      const uint32_t aK = bb::smem_u32(sK + s * TILE_BYTES), aV = bb::smem_u32(sV + s * TILE_BYTES);
-      if (!bb::mbar_wait_spin(&kv_full[s], (j >> 1) & 1, &ctl->abort_flag, p.status)) break;
-      if (!bb::mbar_wait_spin(s_empty, (j & 1) ^ 1, &ctl->abort_flag, p.status)) break;
-      bb::tc_fence_after_sync();
-      if (lane == 0) {
-#pragma unroll
-        for (int k = 0; k < 4; ++k) bb::umma_f16(tS, desc_kmajor(aQ, k), desc_kmajor(aK, k), i_s, k > 0);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) bb::umma_f16(tDP, desc_kmajor(aDO, k), desc_kmajor(aV, k), i_s, k > 0);
-        bb::umma_commit(s_full);
-      }
-      __syncwarp();
-      if (!bb::mbar_wait_spin(ds_full, j & 1, &ctl->abort_flag, p.status)) break;
-      bb::tc_fence_after_sync();
-      if (lane == 0) {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) bb::umma_f16(tDQ, desc_sq_kmajor(aDS, k), desc_mnmajor64(aK, k), i_dq, (j > 0 || k > 0));
-        bb::umma_commit(ds_empty);
-        bb::umma_commit(&kv_empty[s]);
-        if (j == nkv - 1) bb::umma_commit(acc_full);
-      }
-      __syncwarp();
-    }
-  } else {
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;                   // query row inside the tile
-    const int qrow = q0 + row;
-    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const float* lse_g = p.lse + ((long long)batch * p.H + head) * p.S;
-    const float* delta_g = p.delta + ((long long)batch * p.H + head) * p.S;
-    const float lse = (qrow < p.S) ? lse_g[qrow] * LOG2E : 0.f;
-    const float dl = (qrow < p.S) ? delta_g[qrow] : 0.f;
-    const float sl = p.scale * LOG2E;
-    bool alive = true;
-    for (int j = 0; j < nkv && alive; ++j) {
-      if (!wait_all(s_full, j & 1, ctl, p.status)) { alive = false; break; }
-      if (!wait_all(ds_empty, (j & 1) ^ 1, ctl, p.status)) { alive = false; break; }
-      bb::tc_fence_after_sync();
-      const int c0 = j * TQ;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float sv[32], dp[32];
-        ld32(tS + lane_addr + c * 32, sv);
-        ld32(tDP + lane_addr + c * 32, dp);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int col = c0 + c * 32 + i;
-          float pv = exp2f(sv[i] * sl - lse);
-          if (col >= p.S || qrow >= p.S || (p.causal && col > qrow)) pv = 0.f;
-          dp[i] = pv * (dp[i] - dl);
-        }
-        sq_store32(sDS, row, c * 32, dp);
-      }
-      bb::tc_fence_before_sync();
-      bb::fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) { bb::mbar_arrive(s_empty); bb::mbar_arrive(ds_full); }
-    }
-    if (alive && wait_all(acc_full, 0, ctl, p.status)) {
-      bb::tc_fence_after_sync();
-      float v[64];
-      ld32(tDQ + lane_addr, v);
-      ld32(tDQ + lane_addr + 32, v + 32);
-      if (qrow < p.S) store_row64(p.dq + (long long)(row_base + qrow) * p.stride_dqkv + colq, v, p.scale);
-    }
-  }
-  bb::tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 1) bb::tmem_dealloc(tmem, 512);
-}
-
-// ------------------------------------------------------------------ dK, dV
-// CTA owns key rows k0..k0+127 of one (batch, head); streams query / dO tiles.
-//   S^T = K Q^T, dP^T = V dO^T  ->  P^T, dS^T = P^T o (dP^T - delta)  ->  dV += P^T dO, dK += dS^T Q
-// smem: K, V (once) | Q, dO (2 stages) | P^T, dS^T [128 kv x 128 q] ; TMEM: S^T 128 | dP^T 128 | dV 64 | dK 64
-__global__ void __launch_bounds__(NTHREADS, 1)
-attn_tc_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do, const TcParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sK = smem;
-  uint8_t* sV = sK + TILE_BYTES;
-  uint8_t* sQ = sV + TILE_BYTES;               // 2 stages
-  uint8_t* sDO = sQ + 2 * TILE_BYTES;          // 2 stages
-  uint8_t* sP = sDO + 2 * TILE_BYTES;          // 32 KiB
-  uint8_t* sDS = sP + SQ_BYTES;                // 32 KiB
-  float* s_lse = reinterpret_cast<float*>(sDS + SQ_BYTES);   // [128]
-  float* s_delta = s_lse + TQ;                               // [128]
-  Ctl* ctl = reinterpret_cast<Ctl*>(s_delta + TQ);
-  uint64_t* kv_full = &ctl->bars[0];
-  uint64_t* q_full = &ctl->bars[1];            // [2]
-  uint64_t* q_empty = &ctl->bars[3];           // [2]
-  uint64_t* s_full = &ctl->bars[5];
-  uint64_t* s_empty = &ctl->bars[6];
-  uint64_t* p_full = &ctl->bars[7];
-  uint64_t* p_empty = &ctl->bars[8];
-  uint64_t* acc_full = &ctl->bars[9];
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kb = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
-  const int k0 = kb * TQ;
-  const int row_base = batch * p.S;
-  const int colq = head * HD, colk = p.hidden + head * HD, colv = 2 * p.hidden + head * HD;
-  const int nq = (p.S + TQ - 1) / TQ;
-  const int qstart = p.causal ? kb : 0;
-  const int nblk = nq - qstart;
-
-  if (threadIdx.x == 0) {
-    ctl->abort_flag = 0;
-    bb::mbar_init(kv_full, 1);
-    for (int i = 0; i < 2; ++i) { bb::mbar_init(&q_full[i], 1); bb::mbar_init(&q_empty[i], 1); }
-    bb::mbar_init(s_full, 1); bb::mbar_init(s_empty, 4);
-    bb::mbar_init(p_full, 4); bb::mbar_init(p_empty, 1);
-    bb::mbar_init(acc_full, 1);
-    bb::fence_barrier_init();
-    bb::tma_prefetch_desc(&tm_qkv); bb::tma_prefetch_desc(&tm_do);
-  }
-  if (warp == 1) { bb::tmem_alloc(&ctl->tmem_slot, 512); bb::tmem_relinquish(); }
-  bb::tc_fence_before_sync();
-  __syncthreads();
-  bb::tc_fence_after_sync();
-  const uint32_t tmem = ctl->tmem_slot;
-  const uint32_t tS = tmem, tDP = tmem + 128, tDV = tmem + 256, tDK = tmem + 320;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      bb::mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
-      bb::tma_load_2d(sK, &tm_qkv, kv_full, colk, row_base + k0);
-      bb::tma_load_2d(sV, &tm_qkv, kv_full, colv, row_base + k0);
-      for (int i = 0; i < nblk; ++i) {
-        const int s = i & 1;
-        if (!bb::mbar_wait_spin(&q_empty[s], ((i >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
-        bb::mbar_arrive_expect_tx(&q_full[s], 2 * TILE_BYTES);
-        bb::tma_load_2d(sQ + s * TILE_BYTES, &tm_qkv, &q_full[s], colq, row_base + (qstart + i) * TQ);
-        bb::tma_load_2d(sDO + s * TILE_BYTES, &tm_do, &q_full[s], colq, row_base + (qstart + i) * TQ);
-      }
-    }
-  } else if (warp == 1) {
-    const uint32_t aK = bb::smem_u32(sK), aV = bb::smem_u32(sV), aP = bb::smem_u32(sP), aDS = bb::smem_u32(sDS);
-    const uint32_t i_s = idesc(128, 0, 0), i_acc = idesc(64, 0, 1);
-    bool alive = bb::mbar_wait_spin(kv_full, 0, &ctl->abort_flag, p.status);
-    for (int i = 0; i < nblk && alive; ++i) {
-      const int s = i & 1;
-      const uint32_t aQ = bb::smem_u32(sQ + s * TILE_BYTES), aDO = bb::smem_u32(sDO + s * TILE_BYTES);
-      if (!bb::mbar_wait_spin(&q_full[s], (i >> 1) & 1, &ctl->abort_flag, p.status)) break;
-      if (!bb::mbar_wait_spin(s_empty, (i & 1) ^ 1, &ctl->abort_flag, p.status)) break;
-      bb::tc_fence_after_sync();
-      if (lane == 0) {
-#pragma unroll
-        for (int k = 0; k < 4; ++k) bb::umma_f16(tS, desc_kmajor(aK, k), desc_kmajor(aQ, k), i_s, k > 0);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) bb::umma_f16(tDP, desc_kmajor(aV, k), desc_kmajor(aDO, k), i_s, k > 0);
-        bb::umma_commit(s_full);
-      }
-      __syncwarp();
-      if (!bb::mbar_wait_spin(p_full, i & 1, &ctl->abort_flag, p.status)) break;
-      bb::tc_fence_after_sync();
-      if (lane == 0) {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) bb::umma_f16(tDV, desc_sq_kmajor(aP, k), desc_mnmajor64(aDO, k), i_acc, (i > 0 || k > 0));
-#pragma unroll
-        for (int k = 0; k < 8; ++k) bb::umma_f16(tDK, desc_sq_kmajor(aDS, k), desc_mnmajor64(aQ, k), i_acc, (i > 0 || k > 0));
-        bb::umma_commit(p_empty);
-        bb::umma_commit(&q_empty[s]);
-        if (i == nblk - 1) bb::umma_commit(acc_full);
-      }
-      __syncwarp();
-    }
-  } else {
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;                   // key row inside the tile
-    const int krow = k0 + row;
-    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const float* lse_g = p.lse + ((long long)batch * p.H + head) * p.S;
-    const float* delta_g = p.delta + ((long long)batch * p.H + head) * p.S;
-    const float sl = p.scale * LOG2E;
-    bool alive = true;
-    for (int i = 0; i < nblk && alive; ++i) {
-      const int qc0 = (qstart + i) * TQ;
-      // per-column statistics of this query block (the previous block's readers are past
-      // their last use: they all went through the waits below)
-      bb::named_bar_sync(1, 128);
-      {
-        const int q = qc0 + row;
-        s_lse[row] = (q < p.S) ? lse_g[q] * LOG2E : 0.f;
-        s_delta[row] = (q < p.S) ? delta_g[q] : 0.f;
-      }
-      bb::named_bar_sync(1, 128);
-      if (!wait_all(s_full, i & 1, ctl, p.status)) { alive = false; break; }
-      if (!wait_all(p_empty, (i & 1) ^ 1, ctl, p.status)) { alive = false; break; }
-      bb::tc_fence_after_sync();
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float sv[32], dp[32];
-        ld32(tS + lane_addr + c * 32, sv);
-        ld32(tDP + lane_addr + c * 32, dp);
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int qi = c * 32 + e;
-          const int q = qc0 + qi;
-          float pv = exp2f(sv[e] * sl - s_lse[qi]);
-          if (q >= p.S || krow >= p.S || (p.causal && krow > q)) pv = 0.f;
-          sv[e] = pv;
-          dp[e] = pv * (dp[e] - s_delta[qi]);
-        }
-        sq_store32(sP, row, c * 32, sv);
-        sq_store32(sDS, row, c * 32, dp);
-      }
-      bb::tc_fence_before_sync();
-      bb::fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) { bb::mbar_arrive(s_empty); bb::mbar_arrive(p_full); }
-    }
-    if (alive && nblk > 0 && wait_all(acc_full, 0, ctl, p.status)) {
-      bb::tc_fence_after_sync();
-      float v[64];
-      ld32(tDV + lane_addr, v);
-      ld32(tDV + lane_addr + 32, v + 32);
-      if (krow < p.S) store_row64(p.dv + (long long)(row_base + krow) * p.stride_dqkv + colq, v, 1.f);
-      ld32(tDK + lane_addr, v);
-      ld32(tDK + lane_addr + 32, v + 32);
-      if (krow < p.S) store_row64(p.dk + (long long)(row_base + krow) * p.stride_dqkv + colq, v, p.scale);
-    }
-  }
-  bb::tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 1) bb::tmem_dealloc(tmem, 512);
-}
-
-constexpr int DKV_SMEM = 6 * TILE_BYTES + 2 * SQ_BYTES + 2 * TQ * (int)sizeof(float) + (int)sizeof(Ctl) + 1024;
-// ------------------------------------------------------------------ forward
-// CTA owns query rows q0..q0+127 of one (batch, head); streams key/value tiles.
-//   S = Q K^T -> online softmax -> P (bf16, shared memory) -> PV = P V (fresh TMEM tile per block),
-//   O = O * alpha + PV kept in registers (thread == query row), so tensor memory is never rescaled.
-// smem: Q | K, V (2 stages) | P [128 q x 128 kv] ; TMEM: S 128 | PV 64
-__global__ void __launch_bounds__(NTHREADS, 1)
-attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const TcParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;
-  uint8_t* sK = sQ + TILE_BYTES;               // 2 stages
-  uint8_t* sV = sK + 2 * TILE_BYTES;           // 2 stages
-  uint8_t* sP = sV + 2 * TILE_BYTES;           // 32 KiB
-  Ctl* ctl = reinterpret_cast<Ctl*>(sP + SQ_BYTES);
-  uint64_t* q_full = &ctl->bars[0];
-  uint64_t* kv_full = &ctl->bars[1];           // [2]
-  uint64_t* kv_empty = &ctl->bars[3];          // [2]
-  uint64_t* s_full = &ctl->bars[5];
-  uint64_t* s_empty = &ctl->bars[6];
-  uint64_t* p_full = &ctl->bars[7];
-  uint64_t* pv_full = &ctl->bars[8];
-  uint64_t* pv_empty = &ctl->bars[9];
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
-  const int q0 = qb * TQ;
-  const int row_base = batch * p.S;
-  const int colq = head * HD, colk = p.hidden + head * HD, colv = 2 * p.hidden + head * HD;
-  int nkv = (p.S + TQ - 1) / TQ;
-  if (p.causal) nkv = min(nkv, qb + 1);
-
-  if (threadIdx.x == 0) {
-    ctl->abort_flag = 0;
-    bb::mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) { bb::mbar_init(&kv_full[i], 1); bb::mbar_init(&kv_empty[i], 1); }
-    bb::mbar_init(s_full, 1); bb::mbar_init(s_empty, 4);
-    bb::mbar_init(p_full, 4); bb::mbar_init(pv_full, 1); bb::mbar_init(pv_empty, 4);
-    bb::fence_barrier_init();
-    bb::tma_prefetch_desc(&tm_qkv);
-  }
-  if (warp == 1) { bb::tmem_alloc(&ctl->tmem_slot, 256); bb::tmem_relinquish(); }
-  bb::tc_fence_before_sync();
-  __syncthreads();
-  bb::tc_fence_after_sync();
-  const uint32_t tmem = ctl->tmem_slot;
-  const uint32_t tS = tmem, tPV = tmem + 128;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      bb::mbar_arrive_expect_tx(q_full, TILE_BYTES);
-      bb::tma_load_2d(sQ, &tm_qkv, q_full, colq, row_base + q0);
-      for (int j = 0; j < nkv; ++j) {
-        const int s = j & 1;
-        if (!bb::mbar_wait_spin(&kv_empty[s], ((j >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
-        bb::mbar_arrive_expect_tx(&kv_full[s], 2 * TILE_BYTES);
-        bb::tma_load_2d(sK + s * TILE_BYTES, &tm_qkv, &kv_full[s], colk, row_base + j * TQ);
-        bb::tma_load_2d(sV + s * TILE_BYTES, &tm_qkv, &kv_full[s], colv, row_base + j * TQ);
-      }
-    }
-  } else if (warp == 1) {
-    const uint32_t aQ = bb::smem_u32(sQ), aP = bb::smem_u32(sP);
-    const uint32_t i_s = idesc(128, 0, 0), i_pv = idesc(64, 0, 1);
-    bool alive = bb::mbar_wait_spin(q_full, 0, &ctl->abort_flag, p.status);
-    for (int j = 0; j < nkv && alive; ++j) {
-      const int s = j & 1;
-      const uint32_t aK = bb::smem_u32(sK + s * TILE_BYTES), aV = bb::smem_u32(sV + s * TILE_BYTES);
-      if (!bb::mbar_wait_spin(&kv_full[s], (j >> 1) & 1, &ctl->abort_flag, p.status)) break;
-      if (!bb::mbar_wait_spin(s_empty, (j & 1) ^ 1, &ctl->abort_flag, p.status)) break;
-      bb::tc_fence_after_sync();
-      if (lane == 0) {
-#pragma unroll
-        for (int k = 0; k < 4; ++k) bb::umma_f16(tS, desc_kmajor(aQ, k), desc_kmajor(aK, k), i_s, k > 0);
-        bb::umma_commit(s_full);
-      }
-      __syncwarp();
-      if (!bb::mbar_wait_spin(p_full, j & 1, &ctl->abort_flag, p.status)) break;
-      if (!bb::mbar_wait_spin(pv_empty, (j & 1) ^ 1, &ctl->abort_flag, p.status)) break;
-      bb::tc_fence_after_sync();
-      if (lane == 0) {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) bb::umma_f16(tPV, desc_sq_kmajor(aP, k), desc_mnmajor64(aV, k), i_pv, k > 0);
-        bb::umma_commit(pv_full);
-        bb::umma_commit(&kv_empty[s]);
-      }
-      __syncwarp();
-    }
-  } else {
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;
-    const int qrow = q0 + row;
-    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const float sl = p.scale * LOG2E;
-    float o[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) o[i] = 0.f;
-    float m_i = -INFINITY, l_i = 0.f;
-    bool alive = true;
-    for (int j = 0; j < nkv && alive; ++j) {
-      if (!wait_all(s_full, j & 1, ctl, p.status)) { alive = false; break; }
-      bb::tc_fence_after_sync();
-      const int c0 = j * TQ;
-      const bool need_mask = (c0 + TQ > p.S) || (p.causal && j == qb);
-      // pass 1: row maximum of the (masked) scores
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float sv[32];
-        ld32(tS + lane_addr + c * 32, sv);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int col = c0 + c * 32 + i;
-          const bool dead = need_mask && (col >= p.S || (p.causal && col > qrow));
-          mx = fmaxf(mx, dead ? -INFINITY : sv[i] * sl);
-        }
-      }
-      const float m_new = fmaxf(m_i, mx);
-      const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = exp2f(m_i - m_safe);
-      m_i = m_new;
-      // pass 2: probabilities -> shared memory (the previous P.V has been consumed: the wait on
-      // pv_full below, one block earlier, is behind us)
-      float rs = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float sv[32];
-        ld32(tS + lane_addr + c * 32, sv);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int col = c0 + c * 32 + i;
-          const bool dead = need_mask && (col >= p.S || (p.causal && col > qrow));
-          const float pv = dead ? 0.f : exp2f(sv[i] * sl - m_safe);
-          sv[i] = pv;
-          rs += pv;
-        }
-        sq_store32(sP, row, c * 32, sv);
-      }
-      l_i = l_i * alpha + rs;
-      bb::tc_fence_before_sync();
-      bb::fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) { bb::mbar_arrive(s_empty); bb::mbar_arrive(p_full); }
-      // O = O * alpha + P V
-      if (!wait_all(pv_full, j & 1, ctl, p.status)) { alive = false; break; }
-      bb::tc_fence_after_sync();
-      {
-        float pv[32];
-        ld32(tPV + lane_addr, pv);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = o[i] * alpha + pv[i];
-        ld32(tPV + lane_addr + 32, pv);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[32 + i] = o[32 + i] * alpha + pv[i];
-      }
-      bb::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) bb::mbar_arrive(pv_empty);
-    }
-    if (alive && qrow < p.S) {
-      const float inv = l_i > 0.f ? 1.f / l_i : 0.f;
-      store_row64(p.out + (long long)(row_base + qrow) * p.stride_o + colq, o, inv);
-      p.lse[((long long)batch * p.H + head) * p.S + qrow] = (l_i > 0.f) ? (m_i + log2f(l_i)) / LOG2E : -INFINITY;
-    }
-  }
-  bb::tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 1) bb::tmem_dealloc(tmem, 256);
-}
-
-constexpr int FWD_SMEM = 5 * TILE_BYTES + SQ_BYTES + (int)sizeof(Ctl) + 1024;
 
 // delta[b, h, s] = sum_d dO * O : one warp per (token, head)
 __global__ void __launch_bounds__(256)
@@ -706,7 +208,9 @@ attn_tc_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       }
     }
   } else if (warp == 1) {
-    const uint32_t aQ = bb::smem_u32(sQ), aDO = bb::smem_u32(sDO);
+    const uint64_t dQ0 = desc_k0(bb::smem_u32(sQ)), dDO0 = desc_k0(bb::smem_u32(sDO));
+    const uint64_t dK0 = desc_k0(bb::smem_u32(sK)), dV0 = desc_k0(bb::smem_u32(sV));     // stage 0; stage s: + s * SUB_BYTES / 16
+    const uint64_t dKm0 = desc_mn0(bb::smem_u32(sK)), dDS0 = desc_k0(bb::smem_u32(sDS));
     const uint32_t i_s = idesc(64, 0, 0), i_dq = idesc(64, 0, 1);
     bool alive = bb::mbar_wait_spin(q_full, 0, &ctl->abort_flag, p.status);
     // software pipeline: the scores run two sub-blocks ahead of the dQ updates
@@ -717,11 +221,11 @@ attn_tc_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (!bb::mbar_wait_spin(&s_empty[b], ((j / NSB) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
         bb::tc_fence_after_sync();
         if (lane == 0) {
-          const uint32_t aK = bb::smem_u32(sK + s * SUB_BYTES), aV = bb::smem_u32(sV + s * SUB_BYTES);
+          const uint64_t dK = dK0 + (uint64_t)(s * (SUB_BYTES >> 4)), dV = dV0 + (uint64_t)(s * (SUB_BYTES >> 4));
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            bb::umma_f16(tmem + 64 * b, desc_kmajor(aQ, k), desc_kmajor(aK, k), i_s, k > 0);
-            bb::umma_f16(tmem + 192 + 64 * b, desc_kmajor(aDO, k), desc_kmajor(aV, k), i_s, k > 0);
+            bb::umma_f16(tmem + 64 * b, desc_kmajor(dQ0, k), desc_kmajor(dK, k), i_s, k > 0);
+            bb::umma_f16(tmem + 192 + 64 * b, desc_kmajor(dDO0, k), desc_kmajor(dV, k), i_s, k > 0);
           }
           bb::umma_commit(&s_full[b]);
         }
@@ -732,9 +236,9 @@ attn_tc_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (!bb::mbar_wait_spin(&ds_full[b2], (jj >> 1) & 1, &ctl->abort_flag, p.status)) break;
         bb::tc_fence_after_sync();
         if (lane == 0) {
-          const uint32_t aK2 = bb::smem_u32(sK + s2 * SUB_BYTES), aDS = bb::smem_u32(sDS + b2 * TILE_BYTES);
+          const uint64_t dK2 = dKm0 + (uint64_t)(s2 * (SUB_BYTES >> 4)), dDS = dDS0 + (uint64_t)(b2 * (TILE_BYTES >> 4));
 #pragma unroll
-          for (int k = 0; k < 4; ++k) bb::umma_f16(tDQ, desc_kmajor(aDS, k), desc_mnmajor64(aK2, k), i_dq, (jj > 0 || k > 0));
+          for (int k = 0; k < 4; ++k) bb::umma_f16(tDQ, desc_kmajor(dDS, k), desc_mnmajor64(dK2, k), i_dq, (jj > 0 || k > 0));
           bb::umma_commit(&ds_empty[b2]);
           bb::umma_commit(&kv_empty[s2]);
           if (jj == nblk - 1) bb::umma_commit(acc_full);
@@ -878,7 +382,10 @@ attn_tc_dkv2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
       }
     }
   } else if (warp == 1) {
-    const uint32_t aK = bb::smem_u32(sK), aV = bb::smem_u32(sV);
+    const uint64_t dK0 = desc_k0(bb::smem_u32(sK)), dV0 = desc_k0(bb::smem_u32(sV));
+    const uint64_t dQ0 = desc_k0(bb::smem_u32(sQ)), dDO0 = desc_k0(bb::smem_u32(sDO));   // stage 0; stage s: + s * SUB_BYTES / 16
+    const uint64_t dQm0 = desc_mn0(bb::smem_u32(sQ)), dDOm0 = desc_mn0(bb::smem_u32(sDO));
+    const uint64_t dP0 = desc_k0(bb::smem_u32(sP)), dDS0 = desc_k0(bb::smem_u32(sDS));
     const uint32_t i_s = idesc(64, 0, 0), i_acc = idesc(64, 0, 1);
     bool alive = bb::mbar_wait_spin(kv_full, 0, &ctl->abort_flag, p.status);
     // the score products run two sub-blocks ahead of the dV / dK updates
@@ -889,11 +396,11 @@ attn_tc_dkv2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
         if (!bb::mbar_wait_spin(&s_empty[b], ((i / NSB) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
         bb::tc_fence_after_sync();
         if (lane == 0) {
-          const uint32_t aQ = bb::smem_u32(sQ + s * SUB_BYTES), aDO = bb::smem_u32(sDO + s * SUB_BYTES);
+          const uint64_t dQ = dQ0 + (uint64_t)(s * (SUB_BYTES >> 4)), dDO = dDO0 + (uint64_t)(s * (SUB_BYTES >> 4));
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            bb::umma_f16(tmem + 64 * b, desc_kmajor(aK, k), desc_kmajor(aQ, k), i_s, k > 0);
-            bb::umma_f16(tmem + 192 + 64 * b, desc_kmajor(aV, k), desc_kmajor(aDO, k), i_s, k > 0);
+            bb::umma_f16(tmem + 64 * b, desc_kmajor(dK0, k), desc_kmajor(dQ, k), i_s, k > 0);
+            bb::umma_f16(tmem + 192 + 64 * b, desc_kmajor(dV0, k), desc_kmajor(dDO, k), i_s, k > 0);
           }
           bb::umma_commit(&s_full[b]);
         }
@@ -904,12 +411,12 @@ attn_tc_dkv2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
         if (!bb::mbar_wait_spin(&p_full[b2], (ii >> 1) & 1, &ctl->abort_flag, p.status)) break;
         bb::tc_fence_after_sync();
         if (lane == 0) {
-          const uint32_t aQ2 = bb::smem_u32(sQ + s2 * SUB_BYTES), aDO2 = bb::smem_u32(sDO + s2 * SUB_BYTES);
-          const uint32_t aP = bb::smem_u32(sP + b2 * TILE_BYTES), aDS = bb::smem_u32(sDS + b2 * TILE_BYTES);
+          const uint64_t dQ2 = dQm0 + (uint64_t)(s2 * (SUB_BYTES >> 4)), dDO2 = dDOm0 + (uint64_t)(s2 * (SUB_BYTES >> 4));
+          const uint64_t dP = dP0 + (uint64_t)(b2 * (TILE_BYTES >> 4)), dDS = dDS0 + (uint64_t)(b2 * (TILE_BYTES >> 4));
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            bb::umma_f16(tDV, desc_kmajor(aP, k), desc_mnmajor64(aDO2, k), i_acc, (ii > 0 || k > 0));
-            bb::umma_f16(tDK, desc_kmajor(aDS, k), desc_mnmajor64(aQ2, k), i_acc, (ii > 0 || k > 0));
+            bb::umma_f16(tDV, desc_kmajor(dP, k), desc_mnmajor64(dDO2, k), i_acc, (ii > 0 || k > 0));
+            bb::umma_f16(tDK, desc_kmajor(dDS, k), desc_mnmajor64(dQ2, k), i_acc, (ii > 0 || k > 0));
           }
           bb::umma_commit(&p_empty[b2]);
           bb::umma_commit(&q_empty[s2]);
@@ -1012,7 +519,232 @@ attn_tc_dkv2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
 
 constexpr int DKV2_SMEM = 2 * TILE_BYTES + 2 * NST * SUB_BYTES + 4 * TILE_BYTES + 4 * SUB * (int)sizeof(float) + (int)sizeof(Ctl) + 1024;
 
-constexpr int DQ_SMEM = 6 * TILE_BYTES + SQ_BYTES + (int)sizeof(Ctl) + 1024;
+// ------------------------------------------------------------------ forward (two query tiles in ping-pong)
+// A CTA owns 256 query rows of one (batch, head) as two 128-row tiles; compute group g (4 warps,
+// one query row per thread) runs the online softmax of tile g.  Keys/values stream in 64-row
+// sub-tiles that serve both query tiles.  Per sub-block jj and group g:
+//   S_g(jj) = Q_g K_jj^T  ->  P_g = exp2(S_g * c - m_g)  ->  PV_g(jj) = P_g V_jj
+// Scores are double-buffered in tensor memory and issued two sub-blocks ahead, so a group never
+// waits for the tensor core between sub-blocks; P goes through shared memory (bf16, two buffers
+// per group); every P V product lands in its own TMEM buffer (two per group, alternating) and is
+// added to the output row held in registers, so the running-maximum rescale never touches
+// tensor memory.
+// smem: Q_0, Q_1 [128 x 64] | K, V sub-tiles [64 x 64] x NKV stages | P_g,b [128 x 64] x 4
+// TMEM: S_g,b at 128 g + 64 b | PV_g,b at 256 + 128 g + 64 b
+constexpr int NKV = 6;
+constexpr int FWD2_THREADS = 320;
+constexpr int FWD2_SMEM = 2 * TILE_BYTES + 2 * NKV * SUB_BYTES + 4 * TILE_BYTES + (int)sizeof(Ctl) + 1024;
+
+// one row (64 values) of a [128 x 64] bf16 atom
+__device__ __forceinline__ void atom_store_row64(uint8_t* atom, int row, const float* a /*32*/, const float* b /*32*/) {
+  uint8_t* base = atom + row * 128;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const float* v = (c < 4) ? a + 8 * c : b + 8 * (c - 4);
+    uint4 q;
+    q.x = bb::pack_bf16x2(v[0], v[1]); q.y = bb::pack_bf16x2(v[2], v[3]);
+    q.z = bb::pack_bf16x2(v[4], v[5]); q.w = bb::pack_bf16x2(v[6], v[7]);
+    *reinterpret_cast<uint4*>(base + ((c ^ (row & 7)) << 4)) = q;
+  }
+}
+
+__global__ void __launch_bounds__(FWD2_THREADS, 1)
+attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv, const TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                          // 2 tiles
+  uint8_t* sK = sQ + 2 * TILE_BYTES;           // NKV sub-tiles
+  uint8_t* sV = sK + NKV * SUB_BYTES;          // NKV sub-tiles
+  uint8_t* sP = sV + NKV * SUB_BYTES;          // [group][buffer] x 16 KiB
+  Ctl* ctl = reinterpret_cast<Ctl*>(sP + 4 * TILE_BYTES);
+  uint64_t* q_full = &ctl->bars[0];
+  uint64_t* kv_full = &ctl->bars[1];           // [NKV]
+  uint64_t* kv_empty = &ctl->bars[1 + NKV];    // [NKV]
+  uint64_t* s_full = &ctl->bars[1 + 2 * NKV];  // [group][buffer] scores ready
+  uint64_t* p_full = s_full + 4;               // [group] probabilities in shared memory, scores read
+  uint64_t* pv_full = p_full + 2;              // [group] P V product ready
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cb = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, batch = blockIdx.z;   // long CTAs first
+  const int row_base = batch * p.S;
+  const int colq = head * HD, colk = p.hidden + head * HD, colv = 2 * p.hidden + head * HD;
+  const int nsub = (p.S + SUB - 1) / SUB;
+  // last key sub-block of each query tile (-1: the tile lies past the end of the sequence)
+  const int qa = cb * 2 * TQ, qb = qa + TQ;
+  const int last0 = (qa >= p.S) ? -1 : (p.causal ? min(nsub - 1, (qa + TQ - 1) / SUB) : nsub - 1);
+  const int last1 = (qb >= p.S) ? -1 : (p.causal ? min(nsub - 1, (qb + TQ - 1) / SUB) : nsub - 1);
+  const int jmax = max(last0, last1);
+#define BB_LAST(g) ((g) ? last1 : last0)
+
+  if (threadIdx.x == 0) {
+    ctl->abort_flag = 0;
+    bb::mbar_init(q_full, 1);
+    for (int i = 0; i < NKV; ++i) { bb::mbar_init(&kv_full[i], 1); bb::mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < 4; ++i) bb::mbar_init(&s_full[i], 1);
+    for (int g = 0; g < 2; ++g) { bb::mbar_init(&p_full[g], 4); bb::mbar_init(&pv_full[g], 1); }
+    bb::fence_barrier_init();
+    bb::tma_prefetch_desc(&tm_q); bb::tma_prefetch_desc(&tm_kv);
+  }
+  if (warp == 1) { bb::tmem_alloc(&ctl->tmem_slot, 512); bb::tmem_relinquish(); }
+  bb::tc_fence_before_sync();
+  __syncthreads();
+  bb::tc_fence_after_sync();
+  const uint32_t tmem = ctl->tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bb::mbar_arrive_expect_tx(q_full, 2 * TILE_BYTES);
+      bb::tma_load_2d(sQ, &tm_q, q_full, colq, row_base + qa);
+      bb::tma_load_2d(sQ + TILE_BYTES, &tm_q, q_full, colq, row_base + qb);
+      for (int jj = 0; jj <= jmax; ++jj) {
+        const int s = jj % NKV;
+        if (!bb::mbar_wait_spin(&kv_empty[s], ((jj / NKV) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        bb::mbar_arrive_expect_tx(&kv_full[s], 2 * SUB_BYTES);
+        bb::tma_load_2d(sK + s * SUB_BYTES, &tm_kv, &kv_full[s], colk, row_base + jj * SUB);
+        bb::tma_load_2d(sV + s * SUB_BYTES, &tm_kv, &kv_full[s], colv, row_base + jj * SUB);
+      }
+    }
+  } else if (warp == 1) {
+    const uint64_t dQ0 = desc_k0(bb::smem_u32(sQ)), dP0 = desc_k0(bb::smem_u32(sP));
+    const uint64_t dK0 = desc_k0(bb::smem_u32(sK)), dVm0 = desc_mn0(bb::smem_u32(sV));   // stage 0; stage s: + s * SUB_BYTES / 16
+    const uint32_t i_s = idesc(64, 0, 0), i_pv = idesc(64, 0, 1);
+    bool alive = bb::mbar_wait_spin(q_full, 0, &ctl->abort_flag, p.status);
+    // scores of sub-block jj for group g into score buffer jj & 1
+    auto issue_scores = [&](int g, int jj) {
+      const uint64_t dK = dK0 + (uint64_t)((jj % NKV) * (SUB_BYTES >> 4)), dQ = dQ0 + (uint64_t)(g * (TILE_BYTES >> 4));
+      const uint32_t tS = tmem + 128 * g + 64 * (jj & 1);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) bb::umma_f16(tS, desc_kmajor(dQ, k), desc_kmajor(dK, k), i_s, k > 0);
+      bb::umma_commit(&s_full[2 * g + (jj & 1)]);
+    };
+    // prologue: the first two score products of each group
+    for (int jj = 0; jj < 2 && jj <= jmax && alive; ++jj) {
+      if (!bb::mbar_wait_spin(&kv_full[jj % NKV], 0, &ctl->abort_flag, p.status)) { alive = false; break; }
+      bb::tc_fence_after_sync();
+      if (lane == 0) {
+#pragma unroll
+        for (int g = 0; g < 2; ++g) if (jj <= BB_LAST(g)) issue_scores(g, jj);
+      }
+      __syncwarp();
+    }
+    for (int jj = 0; jj <= jmax && alive; ++jj) {
+      const int s = jj % NKV;
+      const uint64_t dV = dVm0 + (uint64_t)(s * (SUB_BYTES >> 4));
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        if (jj > BB_LAST(g)) continue;
+        // P_g(jj) is in shared memory, and group g is done reading S_g(jj): its buffer is free
+        if (!bb::mbar_wait_spin(&p_full[g], jj & 1, &ctl->abort_flag, p.status)) { alive = false; break; }
+        const bool more = (jj + 2 <= BB_LAST(g));
+        if (more && !bb::mbar_wait_spin(&kv_full[(jj + 2) % NKV], ((jj + 2) / NKV) & 1, &ctl->abort_flag, p.status)) { alive = false; break; }
+        bb::tc_fence_after_sync();
+        if (lane == 0) {
+          if (more) issue_scores(g, jj + 2);               // first: the group's next-but-one scores
+          const uint32_t tPV = tmem + 256 + 128 * g + 64 * (jj & 1);
+          const uint64_t dPg = dP0 + (uint64_t)((2 * g + (jj & 1)) * (TILE_BYTES >> 4));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) bb::umma_f16(tPV, desc_kmajor(dPg, k), desc_mnmajor64(dV, k), i_pv, k > 0);
+          bb::umma_commit(&pv_full[g]);
+        }
+        __syncwarp();
+      }
+      if (alive && lane == 0) bb::umma_commit(&kv_empty[s]);      // K_jj, V_jj: every product that reads them is issued
+      __syncwarp();
+    }
+  } else {
+    const int g = (warp - 2) >> 2;
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int q0 = g ? qb : qa;
+    const int qrow = q0 + row;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tS = tmem + 128 * g + lane_addr;
+    const uint32_t tPV = tmem + 256 + 128 * g + lane_addr;
+    const float sl = p.scale * LOG2E;
+    const int lastj = BB_LAST(g);
+    float o[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) o[i] = 0.f;
+    float m_i = -INFINITY, l_i = 0.f;
+    bool alive = true;
+    for (int jj = 0; jj <= lastj; ++jj) {
+      const int b = jj & 1;
+      const bool got = bb::mbar_wait_spin(&s_full[2 * g + b], (jj >> 1) & 1, &ctl->abort_flag, p.status);
+      if (!__all_sync(0xffffffffu, got)) { alive = false; break; }
+      bb::tc_fence_after_sync();
+      const int c0 = jj * SUB;
+      // only sub-blocks that touch the causal diagonal or the end of the sequence need masks
+      const bool need_mask = (c0 + SUB > p.S) || (p.causal && c0 + SUB - 1 > q0);
+      float sa[32], sb[32];                                  // the row's 64 scores stay in registers
+      ld32x2(tS + 64 * b, tS + 64 * b + 32, sa, sb);
+      float mx = -INFINITY;
+      if (!need_mask) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(sa[i], sb[i]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int ca = c0 + i, cc = ca + 32;
+          if (ca >= p.S || (p.causal && ca > qrow)) sa[i] = -INFINITY;
+          if (cc >= p.S || (p.causal && cc > qrow)) sb[i] = -INFINITY;
+          mx = fmaxf(mx, fmaxf(sa[i], sb[i]));
+        }
+      }
+      mx *= sl;                                              // scale > 0: the maximum commutes with it
+      const float m_new = fmaxf(m_i, mx);
+      const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = ex2(m_i - m_safe);
+      m_i = m_new;
+      const float nm = -m_safe;
+      float rs = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {                         // exp2(-inf) = 0 covers the masked entries
+        sa[i] = ex2(fmaf(sa[i], sl, nm)); sb[i] = ex2(fmaf(sb[i], sl, nm));
+        rs += sa[i] + sb[i];
+      }
+      l_i = l_i * alpha + rs;
+      // the product that read this P buffer two sub-blocks ago has retired (and so has the last one)
+      if (jj > 0) {
+        const bool ok = bb::mbar_wait_spin(&pv_full[g], (jj - 1) & 1, &ctl->abort_flag, p.status);
+        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+      }
+      atom_store_row64(sP + (2 * g + b) * TILE_BYTES, row, sa, sb);
+      bb::tc_fence_before_sync();
+      bb::fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) bb::mbar_arrive(&p_full[g]);
+      // O = (O + P V of the previous sub-block) * alpha, while the tensor core works on this one
+      if (jj > 0) {
+        bb::tc_fence_after_sync();
+        const uint32_t t = tPV + 64 * ((jj - 1) & 1);
+        ld32x2(t, t + 32, sa, sb);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { o[i] = (o[i] + sa[i]) * alpha; o[32 + i] = (o[32 + i] + sb[i]) * alpha; }
+      }
+    }
+    if (lastj >= 0) {
+      const bool fin = alive && bb::mbar_wait_spin(&pv_full[g], lastj & 1, &ctl->abort_flag, p.status);
+      if (__all_sync(0xffffffffu, fin)) {
+        bb::tc_fence_after_sync();
+        float pa[32], pb[32];
+        const uint32_t t = tPV + 64 * (lastj & 1);
+        ld32x2(t, t + 32, pa, pb);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { o[i] += pa[i]; o[32 + i] += pb[i]; }
+        if (qrow < p.S) {
+          const float inv = l_i > 0.f ? 1.f / l_i : 0.f;
+          store_row64(p.out + (long long)(row_base + qrow) * p.stride_o + colq, o, inv);
+          p.lse[((long long)batch * p.H + head) * p.S + qrow] = (l_i > 0.f) ? (m_i + log2f(l_i)) / LOG2E : -INFINITY;
+        }
+      }
+    }
+  }
+  bb::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) bb::tmem_dealloc(tmem, 512);
+}
+#undef BB_LAST
+
 
 template <typename K> int set_smem(K kernel, int bytes) {
   BB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
@@ -1025,17 +757,19 @@ template <typename K> int set_smem(K kernel, int bytes) {
 int bb_attention_tc_fwd(const void* qkv_q, void* out, float* lse, int B, int H, int S, long long stride_qkv, long long stride_o,
                         int causal, float scale, cudaStream_t stream) {
   if (int rc = bbhost::bind_context()) return rc;
-  CUtensorMap tm_qkv;
+  CUtensorMap tm_q, tm_kv;
   const long long T = (long long)B * S;
-  // the packed projection [T, 3*H*64]: q, k, v blocks of H*64 columns each
-  if (int rc = bbhost::encode_2d(&tm_qkv, qkv_q, T, 3LL * H * HD, stride_qkv, HD, TQ)) return rc;
+  // the packed projection [T, 3*H*64]: q, k, v blocks of H*64 columns each; 128-row boxes for
+  // the query tiles, 64-row boxes for the streamed key/value sub-tiles
+  if (int rc = bbhost::encode_2d(&tm_q, qkv_q, T, 3LL * H * HD, stride_qkv, HD, TQ)) return rc;
+  if (int rc = bbhost::encode_2d(&tm_kv, qkv_q, T, 3LL * H * HD, stride_qkv, HD, SUB)) return rc;
   TcParams p = {};
   p.out = (__nv_bfloat16*)out; p.lse = lse; p.stride_o = stride_o; p.B = B; p.H = H; p.S = S; p.hidden = H * HD;
   p.causal = causal; p.scale = scale; p.status = bb_device_status_word();
   static bool attr = false;
-  if (!attr) { if (int rc = set_smem(attn_tc_fwd_kernel, FWD_SMEM)) return rc; attr = true; }
-  dim3 grid((S + TQ - 1) / TQ, H, B);
-  attn_tc_fwd_kernel<<<grid, NTHREADS, FWD_SMEM, stream>>>(tm_qkv, p);
+  if (!attr) { if (int rc = set_smem(attn_tc_fwd2_kernel, FWD2_SMEM)) return rc; attr = true; }
+  dim3 grid((S + 2 * TQ - 1) / (2 * TQ), H, B);
+  attn_tc_fwd2_kernel<<<grid, FWD2_THREADS, FWD2_SMEM, stream>>>(tm_q, tm_kv, p);
   BB_CUDA_CHECK(cudaGetLastError());
   return BB_OK;
 }

@@ -304,12 +304,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         if (!bb::mbar_wait(&full_bar[s], phase, abort_flag, p.status)) { alive = false; break; }
         bb::tc_fence_after_sync();
         if (lane == 0) {
-          const uint32_t a_addr = bb::smem_u32(sA + s * A_STAGE_BYTES);
-          const uint32_t b_addr = bb::smem_u32(sB + s * C::B_STAGE_BYTES);
+          // one descriptor per stage; a k-step only adds to its address field (16-byte units)
+          const uint64_t ad0 = bb::make_smem_desc_sw128(bb::smem_u32(sA + s * A_STAGE_BYTES), a_lbo, 1024u);
+          const uint64_t bd0 = bb::make_smem_desc_sw128(bb::smem_u32(sB + s * C::B_STAGE_BYTES), b_lbo, 1024u);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            uint64_t ad = bb::make_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, 1024u);
-            uint64_t bd = bb::make_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, 1024u);
+            const uint64_t ad = ad0 + (uint64_t)(k * (a_kstep >> 4));
+            const uint64_t bd = bd0 + (uint64_t)(k * (b_kstep >> 4));
             if (PAIR) bb::umma_f16_pair(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
             else bb::umma_f16(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }

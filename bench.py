@@ -212,11 +212,14 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    host_issue_ms = [0.0]
+
     def timed(steps_data, read_loss):
         barrier()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         last = None
+        t_host = time.perf_counter()
         for batches in steps_data:
             loss = engine.train_batch(data_iter=iter(batches))
             if read_loss and torch.is_tensor(loss):
@@ -224,6 +227,7 @@ def main():
             elif torch.is_tensor(loss):
                 last = loss
         end.record()
+        host_issue_ms[0] = (time.perf_counter() - t_host) * 1e3     # host time to issue the steps (no final sync)
         barrier()
         ms = torch.tensor([start.elapsed_time(end)], device=dev)
         if world > 1:
@@ -238,6 +242,7 @@ def main():
     sampler.start()
     n0 = lib.LAUNCHES
     ms_dev, loss_dev = timed(resident, read_loss=False)
+    issue_ms = host_issue_ms[0] / args.steps
     launches = lib.LAUNCHES - n0
     ms_e2e, loss_e2e = timed(host[-args.steps:], read_loss=True)
     clocks = sampler.stop()
@@ -292,7 +297,7 @@ def main():
                    "l2": "working set per step is far larger than L2 (no flush needed)"},
         "e2e": {"value": e2e, "unit": METRIC, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                 "ms_per_step": ms_e2e / args.steps},
-        "gpu_launches": launches, "clocks": clocks, "device_status": status,
+        "gpu_launches": launches, "host_issue_ms_per_step": issue_ms, "clocks": clocks, "device_status": status,
         "loss": float(loss_e2e) if loss_e2e is not None else None,
         "model_tflops_per_gpu": step_flops * args.steps / (ms_dev * 1e-3) / 1e12 / world,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
