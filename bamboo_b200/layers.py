@@ -63,22 +63,44 @@ def wgrad_sync(device):
         torch.cuda.current_stream(device).wait_stream(st)
 
 
-def _linear_backward(dy2d, x2d, weight, bias, dx_out=None, dx_epilogue=L.EPI_STORE, aux=None, need_dx=True):
-    """dx = dy @ W (optionally through a fused epilogue); dW += dy^T x ; db += colsum(dy)."""
-    T, n_out = dy2d.shape
-    n_in = weight.shape[1]
-    main = torch.cuda.current_stream(dy2d.device)
-    side = _wgrad_stream(dy2d.device) if WGRAD_SIDE_STREAM else main
-    if side is not main:
-        side.wait_stream(main)                   # dy (and x) are ready on the main stream
-    with torch.cuda.stream(side):
-        L.gemm(dy2d, x2d, _main_grad(weight), a_mn=True, b_mn=True, epilogue=L.EPI_ACCUM_F32, M=n_out, N=n_in, K=T)
-        if bias is not None:
-            L.colsum_accum(dy2d, _main_grad(bias), tag="wgrad")
-    if side is not main:
+def _wgrad(dy2d, x2d, weight, bias, stream=None):
+    """dW += dy^T x ; db += colsum(dy), into the fp32 gradient arena."""
+    L.gemm(dy2d, x2d, _main_grad(weight), a_mn=True, b_mn=True, epilogue=L.EPI_ACCUM_F32,
+           M=dy2d.shape[1], N=weight.shape[1], K=dy2d.shape[0], stream=stream)
+    if bias is not None:
+        L.colsum_accum(dy2d, _main_grad(bias), tag="wgrad", stream=stream)
+
+
+def flush_wgrads(pending):
+    """Launch the deferred weight-gradient work `[(dy, x, weight, bias), ...]`: on the side stream
+    (one fork per call, all operands already produced on the current stream), or in place when
+    the side stream is switched off."""
+    if not pending:
+        return
+    if not WGRAD_SIDE_STREAM:
+        for item in pending:
+            _wgrad(*item)
+        return
+    dev = pending[0][0].device
+    side = _wgrad_stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    raw = side.cuda_stream
+    for dy2d, x2d, weight, bias in pending:
+        _wgrad(dy2d, x2d, weight, bias, stream=raw)
         # the caching allocator must not hand these buffers out again before the side stream is done
         dy2d.record_stream(side)
         x2d.record_stream(side)
+
+
+def _linear_backward(dy2d, x2d, weight, bias, dx_out=None, dx_epilogue=L.EPI_STORE, aux=None, need_dx=True, defer=None):
+    """dx = dy @ W (optionally through a fused epilogue); the weight and bias gradients are
+    launched right away, or appended to `defer` for one `flush_wgrads` call per layer."""
+    T, n_out = dy2d.shape
+    n_in = weight.shape[1]
+    if defer is None:
+        flush_wgrads([(dy2d, x2d, weight, bias)])
+    else:
+        defer.append((dy2d, x2d, weight, bias))
     dx = None
     if need_dx:
         dx = dx_out if dx_out is not None else torch.empty(T, n_in, dtype=torch.bfloat16, device=dy2d.device)
@@ -137,15 +159,19 @@ class _BlockFn(torch.autograd.Function):
             d2 = d2.contiguous()
         T = d2.shape[0]
         # MLP: d(pre) = (d2 @ W2) * gelu'(pre) fused in the dgrad epilogue
-        dpre = _linear_backward(d2, act, blk.fc2_w, blk.fc2_b, dx_epilogue=L.EPI_MUL_DGELU, aux=pre)
-        dh2 = _linear_backward(dpre, h2, blk.fc1_w, blk.fc1_b)
+        wg = []          # the block's four weight gradients go to the side stream in one batch
+        dpre = _linear_backward(d2, act, blk.fc2_w, blk.fc2_b, dx_epilogue=L.EPI_MUL_DGELU, aux=pre, defer=wg)
+        dh2 = _linear_backward(dpre, h2, blk.fc1_w, blk.fc1_b, defer=wg)
+        flush_wgrads(wg)
+        wg = []
         dx1 = torch.empty(T, h, dtype=bf, device=dev)
         L.layernorm_bwd(dh2, x1, blk.ln2_w, mean2, rstd2, d2, dx1, _main_grad(blk.ln2_w), _main_grad(blk.ln2_b))
         # attention
-        datt = _linear_backward(dx1, att, blk.proj_w, blk.proj_b)
+        datt = _linear_backward(dx1, att, blk.proj_w, blk.proj_b, defer=wg)
         dqkv = torch.empty_like(qkv)
         L.attention_bwd(qkv, att, datt, lse, dqkv, B, H, S, D, blk.causal)
-        dh1 = _linear_backward(dqkv, h1, blk.qkv_w, blk.qkv_b)
+        dh1 = _linear_backward(dqkv, h1, blk.qkv_w, blk.qkv_b, defer=wg)
+        flush_wgrads(wg)
         dx = torch.empty(T, h, dtype=bf, device=dev)
         L.layernorm_bwd(dh1, x2, blk.ln1_w, mean1, rstd1, dx1, dx, _main_grad(blk.ln1_w), _main_grad(blk.ln1_b))
         return (dx.view(ctx.shape), None) + (None,) * 12

@@ -80,9 +80,14 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else None
 
 
-def _stream():
+def _stream(raw=None):
+    """cudaStream_t of the current stream of the current device (or the given raw handle).  The
+    raw getter is a single C call; `torch.cuda.current_stream()` builds a Stream object through
+    several Python layers and showed up as a third of the host time per step."""
+    if raw is not None:
+        return ctypes.c_void_p(raw)
     import torch
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice()))
 
 
 # Process-wide default for GemmDesc.cta_pair (0 = library heuristic, 1 = pairs, -1 = single CTAs);
@@ -91,7 +96,7 @@ GEMM_CTA_PAIR = int(os.environ.get("BB_GEMM_CTA_PAIR", "0"))
 
 
 def gemm(a, b, out, *, a_mn=False, b_mn=False, epilogue=EPI_STORE, bias=None, out2=None, aux=None,
-         M=None, N=None, K=None, tile_n=0, max_ctas=0, split_k=0, cta_pair=0):
+         M=None, N=None, K=None, tile_n=0, max_ctas=0, split_k=0, cta_pair=0, stream=None):
     """out[M,N] = op(a)[M,K] @ op(b)[N,K]^T with a fused epilogue; see bb_gemm_bf16.
 
     ``a`` is [M,K] (or [K,M] when ``a_mn``), ``b`` is [N,K] (or [K,N] when ``b_mn``); 2-D,
@@ -106,18 +111,19 @@ def gemm(a, b, out, *, a_mn=False, b_mn=False, epilogue=EPI_STORE, bias=None, ou
     for t in (a, b, out, bias, out2, aux):
         if t is not None and (not t.is_cuda or t.stride(-1) != 1):
             raise BambooNativeError("gemm operands must be CUDA tensors with unit inner stride")
-    d = GemmDesc(M=M, N=N, K=K, A=_ptr(a), lda=a.stride(0), a_mn_major=int(a_mn),
-                 B=_ptr(b), ldb=b.stride(0), b_mn_major=int(b_mn), D=_ptr(out), ldd=out.stride(0),
-                 epilogue=epilogue, bias=_ptr(bias), D2=_ptr(out2), aux=_ptr(aux),
+    d = GemmDesc(M=M, N=N, K=K, A=a.data_ptr(), lda=a.stride(0), a_mn_major=int(a_mn),
+                 B=b.data_ptr(), ldb=b.stride(0), b_mn_major=int(b_mn), D=out.data_ptr(), ldd=out.stride(0),
+                 epilogue=epilogue, bias=None if bias is None else bias.data_ptr(),
+                 D2=None if out2 is None else out2.data_ptr(), aux=None if aux is None else aux.data_ptr(),
                  ld_aux=aux.stride(0) if aux is not None else 0, tile_n=tile_n, max_ctas=max_ctas, split_k=split_k,
                  cta_pair=cta_pair or GEMM_CTA_PAIR)
     global LAUNCHES
     LAUNCHES += 1
     if gemm_hook is not None:
         gemm_hook((M, N, K, int(a_mn), int(b_mn), epilogue), 2.0 * M * N * K,
-                  lambda: check(load().bb_gemm_bf16(ctypes.byref(d), _stream()), "bb_gemm_bf16"))
+                  lambda: check(load().bb_gemm_bf16(ctypes.byref(d), _stream(stream)), "bb_gemm_bf16"))
         return out
-    check(load().bb_gemm_bf16(ctypes.byref(d), _stream()), "bb_gemm_bf16")
+    check(load().bb_gemm_bf16(ctypes.byref(d), _stream(stream)), "bb_gemm_bf16")
     return out
 
 
@@ -176,7 +182,7 @@ def layernorm_bwd_static(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta):
     return dx
 
 
-def colsum_accum(dy, out, tag="rowwise"):
+def colsum_accum(dy, out, tag="rowwise", stream=None):
     """out(fp32)[n] += dy(bf16)[rows, n].sum(0); ``tag`` names the scratch buffer (calls that may
     overlap on the GPU, e.g. on different streams, need different ones)"""
     global LAUNCHES
@@ -187,7 +193,7 @@ def colsum_accum(dy, out, tag="rowwise"):
     need = lib.bb_colsum_workspace_bytes(_I(rows), _I(n))
     ws = workspace(need, tag)
     check(lib.bb_colsum_accum(_ptr(dy), _LL(dy.stride(0)), _ptr(out), _ptr(ws), _LL(ws.numel()), _I(rows), _I(n),
-                              _stream()), "bb_colsum_accum")
+                              _stream(stream)), "bb_colsum_accum")
     return out
 
 

@@ -117,7 +117,7 @@ class MailboxTransport:
 
     # ------------------------------------------------------------------ data path
     def _stream(self):
-        return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        return L._stream()
 
     def _put(self, ch, slot, src_ptr, nbytes, seq):
         L.LAUNCHES += 1
