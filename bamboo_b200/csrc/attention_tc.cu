@@ -114,19 +114,47 @@ struct Ctl {
 };
 
 
-// delta[b, h, s] = sum_d dO * O : one warp per (token, head)
+// delta[b, h, s] = sum_d dO * O.  Eight lanes per (token, head): each loads 16 bytes of O and dO
+// (a warp reads four consecutive heads of a token: 512 contiguous bytes per operand), two
+// independent units per thread for memory-level parallelism.
 __global__ void __launch_bounds__(256)
 attn_tc_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, const TcParams p) {
-  const int lane = threadIdx.x & 31;
-  const long long total = (long long)p.B * p.S * p.H;
-  for (long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); w < total; w += (long long)gridDim.x * 8) {
-    const long long tok = w / p.H; const int head = (int)(w % p.H);
-    const uint32_t a = *reinterpret_cast<const uint32_t*>(o + tok * p.stride_o + head * HD + lane * 2);
-    const uint32_t b = *reinterpret_cast<const uint32_t*>(d_o + tok * p.stride_o + head * HD + lane * 2);
-    float s = bb::bf16_lo(a) * bb::bf16_lo(b) + bb::bf16_hi(a) * bb::bf16_hi(b);
+  const int per_tok = p.H * 8;                                 // 16-byte chunks per token row
+  const long long total = (long long)p.B * p.S * per_tok;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  // the trip count is uniform within a warp (the shuffles below need every lane)
+  for (long long w = (long long)blockIdx.x * blockDim.x + (threadIdx.x & ~31); w < total; w += 2 * stride) {
+    const long long c = w + (threadIdx.x & 31);
+    float s[2];
+    long long cc[2] = {c, c + stride};
+    uint4 a[2], b[2];
 #pragma unroll
-    for (int k = 16; k > 0; k >>= 1) s += __shfl_xor_sync(0xffffffffu, s, k);
-    if (lane == 0) p.delta[((tok / p.S) * p.H + head) * p.S + (tok % p.S)] = s;
+    for (int u = 0; u < 2; ++u) {
+      a[u] = make_uint4(0, 0, 0, 0); b[u] = a[u];
+      if (cc[u] < total) {
+        const long long tok = cc[u] / per_tok; const int within = (int)(cc[u] % per_tok);
+        a[u] = __ldg(reinterpret_cast<const uint4*>(o + tok * p.stride_o + within * 8));
+        b[u] = __ldg(reinterpret_cast<const uint4*>(d_o + tok * p.stride_o + within * 8));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const uint32_t x[4] = {a[u].x, a[u].y, a[u].z, a[u].w}, y[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
+      float t = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) t += bb::bf16_lo(x[i]) * bb::bf16_lo(y[i]) + bb::bf16_hi(x[i]) * bb::bf16_hi(y[i]);
+      t += __shfl_xor_sync(0xffffffffu, t, 1);
+      t += __shfl_xor_sync(0xffffffffu, t, 2);
+      t += __shfl_xor_sync(0xffffffffu, t, 4);
+      s[u] = t;
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (cc[u] < total && (threadIdx.x & 7) == 0) {
+        const long long tok = cc[u] / per_tok; const int head = (int)(cc[u] % per_tok) >> 3;
+        p.delta[((tok / p.S) * p.H + head) * p.S + (tok % p.S)] = s[u];
+      }
+    }
   }
 }
 
@@ -795,8 +823,8 @@ int bb_attention_tc_bwd(const void* qkv_q, const void* out, const void* d_out, c
     if (int rc = set_smem(attn_tc_dkv2_kernel, DKV2_SMEM)) return rc;
     attr = true;
   }
-  const long long units = T * H;
-  long long dgrid = (units + 7) / 8, cap = (long long)bb_num_sms() * 8;
+  const long long chunks = T * H * 8;
+  long long dgrid = (chunks + 511) / 512, cap = (long long)bb_num_sms() * 8;
   attn_tc_delta_kernel<<<(int)(dgrid < cap ? dgrid : cap), 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out, p);
   dim3 grid((S + TQ - 1) / TQ, H, B);
   attn_tc_dkv2_kernel<<<grid, NT2, DKV2_SMEM, stream>>>(tm_qkv, tm_qkv64, tm_do64, p);
