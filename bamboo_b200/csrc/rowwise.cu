@@ -252,6 +252,22 @@ colsum_kernel(const __nv_bfloat16* __restrict__ dy, float* __restrict__ partials
   }
 }
 
+// ------------------------------------------------------------------ GeLU backward (stand-alone)
+// dx = dy * gelu'(pre), tanh form; 8 bf16 per thread.  The transformer blocks get this fused into
+// the input-gradient GEMM's epilogue; it stands alone where the activation is followed by a
+// LayerNorm instead of a GEMM (masked-LM head transform).
+__global__ void __launch_bounds__(256)
+gelu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ pre, __nv_bfloat16* __restrict__ dx, long long n8) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float d[8], x[8], o[8];
+    unpack8(__ldg(reinterpret_cast<const uint4*>(dy) + i), d);
+    unpack8(__ldg(reinterpret_cast<const uint4*>(pre) + i), x);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = d[k] * bb::gelu_tanh_grad(x[k]);
+    reinterpret_cast<uint4*>(dx)[i] = pack8(o);
+  }
+}
+
 // ------------------------------------------------------------------ embedding
 // out[t,:] = wte[tok[t],:] + wpe[t % seq,:]
 __global__ void __launch_bounds__(WARPS * 32)
@@ -443,6 +459,19 @@ int colsum_splits(int rows) {
   return s < 1 ? 1 : (s > 64 ? 64 : s);
 }
 }  // namespace
+
+extern "C" int bb_gelu_bwd(const void* dy, const void* pre, void* dx, long long n, void* stream) {
+  if (!dy || !pre || !dx || n <= 0 || (n & 7) || ((uintptr_t)dy & 15) || ((uintptr_t)pre & 15) || ((uintptr_t)dx & 15)) {
+    bb_set_last_error_msg("bb_gelu_bwd: null/unaligned pointer or n not a multiple of 8");
+    return BB_ERR_INVALID_ARG;
+  }
+  const long long n8 = n >> 3;
+  long long grid = (n8 + 255) / 256, cap = (long long)bb_num_sms() * 8;
+  gelu_bwd_kernel<<<(int)(grid < cap ? grid : cap), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)pre, (__nv_bfloat16*)dx, n8);
+  BB_CUDA_CHECK(cudaGetLastError());
+  return BB_OK;
+}
 
 extern "C" long long bb_colsum_workspace_bytes(int rows, int n) {
   if (rows <= 0 || n <= 0) return 0;

@@ -256,6 +256,45 @@ class _LinearFn(torch.autograd.Function):
         return dx.view(ctx.shape), None, None, None
 
 
+class _MLMTransformFn(torch.autograd.Function):
+    """y = LayerNorm(gelu(x W^T + b)): the masked-LM head transform.  Forward: one GEMM with the
+    bias+GeLU epilogue (keeps the pre-activation) and a LayerNorm; backward: LayerNorm backward,
+    stand-alone GeLU backward, then the usual input / weight gradients."""
+
+    @staticmethod
+    def forward(ctx, x, mod, w, b, ln_w, ln_b):
+        _require_cuda(x, "MLMTransform")
+        h = x.shape[-1]
+        x2 = x.reshape(-1, h)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        T, dev = x2.shape[0], x.device
+        pre = torch.empty(T, h, dtype=torch.bfloat16, device=dev)
+        act = torch.empty(T, h, dtype=torch.bfloat16, device=dev)
+        L.gemm(x2, w, act, epilogue=L.EPI_BIAS_GELU, bias=b, out2=pre)
+        mean = torch.empty(T, dtype=torch.float32, device=dev)
+        rstd = torch.empty(T, dtype=torch.float32, device=dev)
+        y = torch.empty(T, h, dtype=torch.bfloat16, device=dev)
+        L.layernorm_fwd(act, ln_w, ln_b, y, mean, rstd, mod.eps)
+        ctx.mod, ctx.shape = mod, x.shape
+        ctx.save_for_backward(x2, pre, act, mean, rstd)
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, pre, act, mean, rstd = ctx.saved_tensors
+        mod = ctx.mod
+        d2 = dy.reshape(-1, x2.shape[1])
+        if not d2.is_contiguous():
+            d2 = d2.contiguous()
+        dact = torch.empty_like(act)
+        L.layernorm_bwd(d2, act, mod.ln_weight, mean, rstd, None, dact, _main_grad(mod.ln_weight), _main_grad(mod.ln_bias))
+        dpre = torch.empty_like(pre)
+        L.gelu_bwd(dact, pre, dpre)
+        dx = _linear_backward(dpre, x2, mod.weight, mod.bias)
+        return dx.view(ctx.shape), None, None, None, None, None
+
+
 class _CrossEntropyFn(torch.autograd.Function):
     """Mean token cross entropy; the gradient overwrites the logits buffer in place."""
 
@@ -348,6 +387,22 @@ class Linear(nn.Module):
 
     def forward(self, x):
         return _LinearFn.apply(x, self, self.weight, self.bias)
+
+
+class MLMTransform(nn.Module):
+    """Masked-LM head transform: dense (hidden -> hidden) + tanh-GeLU + LayerNorm; the vocabulary
+    decoder is the ``Linear`` that follows it in the layer list."""
+
+    def __init__(self, hidden, eps=1e-5, seed=0):
+        super().__init__()
+        g = torch.Generator().manual_seed(seed)
+        self.eps = eps
+        self.weight = nn.Parameter(_normal((hidden, hidden), g))
+        self.bias = nn.Parameter(torch.zeros(hidden))
+        self.ln_weight = nn.Parameter(torch.ones(hidden)); self.ln_bias = nn.Parameter(torch.zeros(hidden))
+
+    def forward(self, x):
+        return _MLMTransformFn.apply(x, self, self.weight, self.bias, self.ln_weight, self.ln_bias)
 
 
 class CrossEntropyLoss:

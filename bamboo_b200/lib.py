@@ -197,6 +197,14 @@ def colsum_accum(dy, out, tag="rowwise", stream=None):
     return out
 
 
+def gelu_bwd(dy, pre, dx):
+    """dx = dy * gelu'(pre), elementwise over contiguous bf16 tensors"""
+    global LAUNCHES
+    LAUNCHES += 1
+    check(load().bb_gelu_bwd(_ptr(dy), _ptr(pre), _ptr(dx), _LL(dy.numel()), _stream()), "bb_gelu_bwd")
+    return dx
+
+
 def embedding_fwd(tokens, wte, wpe, out, seq):
     global LAUNCHES
     LAUNCHES += 1

@@ -32,7 +32,9 @@ def parse():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="bamboo_b200", choices=["bamboo_b200", "reference"])
     ap.add_argument("--rc", default="auto", choices=["auto", "off", "lazy", "eager"])
-    ap.add_argument("--model", default="gpt2-medium", choices=["gpt2-medium", "toy"])
+    ap.add_argument("--model", default="gpt2-medium", choices=["gpt2-medium", "bert-large", "toy"],
+                    help="gpt2-medium is the headline configuration (micro-batch 8 x 16, seq 1024); bert-large is the "
+                         "masked-LM configuration (micro-batch 16 x 32, seq 512, bidirectional attention)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--failover", action="store_true",
                     help="after the timed region: the last stage announces its preemption and leaves; reports the "
@@ -44,7 +46,7 @@ def parse():
 
 def model_config(name):
     from bamboo_b200 import models
-    return models.GPT2_MEDIUM if name == "gpt2-medium" else models.GPT_TOY
+    return {"gpt2-medium": models.GPT2_MEDIUM, "bert-large": models.BERT_LARGE}.get(name, models.GPT_TOY)
 
 
 class ClockSampler:
@@ -91,16 +93,21 @@ class ClockSampler:
 
 
 def synthetic_tokens(cfg, steps, seed, pin):
-    """Uniform token ids; labels = tokens shifted by one (last position ignored)."""
+    """Uniform token ids; labels = tokens shifted by one (last position ignored), or for the
+    masked-LM model the BERT masking recipe (15 % of the positions, 80/10/10)."""
     import torch
+    from bamboo_b200 import models
     g = torch.Generator().manual_seed(seed)
     out = []
     for _ in range(steps):
         step = []
         for _ in range(MICRO_BATCHES):
             tok = torch.randint(0, cfg.vocab, (MICRO_BATCH, cfg.seq), generator=g)
-            lab = torch.full_like(tok, -100)
-            lab[:, :-1] = tok[:, 1:]
+            if cfg.mlm:
+                tok, lab = models.mlm_mask(tok, g, cfg.vocab)
+            else:
+                lab = torch.full_like(tok, -100)
+                lab[:, :-1] = tok[:, 1:]
             if pin:
                 tok, lab = tok.pin_memory(), lab.pin_memory()
             step.append((tok, lab))
@@ -114,13 +121,17 @@ def cpu_baseline(cfg, seconds_budget=25.0):
     from oracle import gpt_ref
     cores = len(os.sched_getaffinity(0))
     torch.set_num_threads(cores)
-    rc = gpt_ref.RefConfig(cfg.layers, cfg.hidden, cfg.heads, cfg.ffn, cfg.seq, cfg.vocab, cfg.causal)
+    rc = gpt_ref.RefConfig(cfg.layers, cfg.hidden, cfg.heads, cfg.ffn, cfg.seq, cfg.vocab, cfg.causal, cfg.mlm)
     ref = gpt_ref.RefTrainer(rc, seed=0, lr=1e-4, micro_batches=1)
     g = torch.Generator().manual_seed(1)
     seqs, t_fb = 0, 0.0
     while t_fb < seconds_budget * 0.6 and seqs < 4:
         tok = torch.randint(0, cfg.vocab, (1, cfg.seq), generator=g)
-        lab = torch.full_like(tok, -100); lab[:, :-1] = tok[:, 1:]
+        if cfg.mlm:
+            from bamboo_b200 import models
+            tok, lab = models.mlm_mask(tok, g, cfg.vocab)
+        else:
+            lab = torch.full_like(tok, -100); lab[:, :-1] = tok[:, 1:]
         t0 = time.perf_counter()
         loss = gpt_ref.forward_loss(rc, ref.P, tok, lab)
         loss.backward()
@@ -162,8 +173,10 @@ def run_reference(args):
 
 
 def main():
-    global MICRO_BATCHES
+    global MICRO_BATCH, MICRO_BATCHES
     args = parse()
+    if args.model == "bert-large":
+        MICRO_BATCH, MICRO_BATCHES = 16, 32
     if args.micro_batches:
         MICRO_BATCHES = args.micro_batches
     if args.impl == "reference":
@@ -192,7 +205,7 @@ def main():
     from bamboo_b200.partition import partition_balanced
     h = cfg.hidden
     head_cost = 2.0 * h * cfg.vocab / (24.0 * h * h + 4.0 * cfg.seq * h)
-    costs = [0.0] + [1.0] * cfg.layers + [0.0, head_cost]
+    costs = [0.0] + [1.0] * cfg.layers + [0.0] + ([2.0 * h * h / (24.0 * h * h + 4.0 * cfg.seq * h)] if cfg.mlm else []) + [head_cost]
     parts = partition_balanced([int(c * 1000) for c in costs], world)
     for st in range(world - 1, 0, -1):          # no stage may be empty: steal the predecessor's last layer
         if parts[st] >= parts[st + 1]:
@@ -227,7 +240,9 @@ def main():
             elif torch.is_tensor(loss):
                 last = loss
         end.record()
-        host_issue_ms[0] = (time.perf_counter() - t_host) * 1e3     # host time to issue the steps (no final sync)
+        # host time to issue the steps, no final sync (an upper bound on the launch cost: a host
+        # that runs far ahead blocks on the driver's bounded launch queue and then tracks the GPU)
+        host_issue_ms[0] = (time.perf_counter() - t_host) * 1e3
         barrier()
         ms = torch.tensor([start.elapsed_time(end)], device=dev)
         if world > 1:

@@ -151,6 +151,13 @@ int bb_cross_entropy_bwd(const void* logits, long long ld, const long long* targ
                          const float* loss_out, const float* grad_scale_dev, float grad_scale, void* dlogits,
                          long long ldd, int rows, int vocab, int cols, long long ignore_index, void* stream);
 
+/* dx = dy * gelu'(pre) (tanh form), n bf16 elements, n a multiple of 8.  The activation gradient
+ * where no GEMM follows to fuse it into: the masked-LM head transform (dense + GeLU +
+ * LayerNorm) of the BERT-large configuration.  The reference runs this as ATen's GeLU backward
+ * inside loss.backward() (DS/runtime/engine.py:1478); its own BERT example
+ * (DeepSpeedExamples/pipeline_parallelism/bert.py:126-147) stops before the language-model head. */
+int bb_gelu_bwd(const void* dy, const void* pre, void* dx, long long n, void* stream);
+
 /* ---- optimizer -------------------------------------------------------------------- */
 /* One Adam / AdamW step over a flat parameter arena: fp32 master weights, gradient and
  * moments; refreshes the bf16 working copy (may be NULL) and optionally clears the

@@ -43,6 +43,7 @@ class RefConfig:
     seq: int
     vocab: int
     causal: bool = True
+    mlm: bool = False       # BERT-style head: dense + GeLU + LayerNorm before the vocabulary decoder
 
 
 def _normal(shape, gen):
@@ -66,7 +67,13 @@ def init_params(cfg: RefConfig, seed: int = 0):
         P[p + "fc1_w"], P[p + "fc1_b"] = _normal((cfg.ffn, h), g), torch.zeros(cfg.ffn)
         P[p + "fc2_w"], P[p + "fc2_b"] = _normal((h, cfg.ffn), g), torch.zeros(h)
     P["lnf_w"], P["lnf_b"] = torch.ones(h), torch.zeros(h)
-    g = torch.Generator().manual_seed(seed * 1000 + cfg.layers + 2)
+    nxt = seed * 1000 + cfg.layers + 2
+    if cfg.mlm:
+        g = torch.Generator().manual_seed(nxt)
+        P["mlm_w"], P["mlm_b"] = _normal((h, h), g), torch.zeros(h)
+        P["mlm_ln_w"], P["mlm_ln_b"] = torch.ones(h), torch.zeros(h)
+        nxt += 1
+    g = torch.Generator().manual_seed(nxt)
     P["head_w"] = _normal((cfg.vocab, h), g)
     return P
 
@@ -93,6 +100,9 @@ def forward_loss(cfg: RefConfig, P, tokens, labels, ignore_index=-100):
     for i in range(cfg.layers):
         x = block_forward(cfg, P, f"b{i}.", x)
     x = F.layer_norm(x, (cfg.hidden,), P["lnf_w"], P["lnf_b"], 1e-5)
+    if cfg.mlm:
+        x = F.gelu(F.linear(x, P["mlm_w"], P["mlm_b"]), approximate="tanh")
+        x = F.layer_norm(x, (cfg.hidden,), P["mlm_ln_w"], P["mlm_ln_b"], 1e-5)
     logits = F.linear(x, P["head_w"])
     return F.cross_entropy(logits.view(-1, cfg.vocab), labels.reshape(-1), ignore_index=ignore_index)
 
@@ -151,5 +161,35 @@ def synthetic_batches(cfg: RefConfig, micro_batch, micro_batches, steps, seed=1)
             lab = torch.full_like(tok, -100)
             lab[:, :-1] = tok[:, 1:]
             step.append((tok, lab))
+        out.append(step)
+    return out
+
+
+def synthetic_mlm_batches(cfg: RefConfig, micro_batch, micro_batches, steps, seed=1, mask_id=103):
+    """Masked-LM micro-batches: uniform token ids from Generator(seed); per sequence 15 % of the
+    positions are chosen (the first round(0.15 S) of a random permutation); labels hold the
+    original token there and -100 elsewhere; chosen inputs become ``mask_id`` with probability
+    0.8, a random token with 0.1 and stay with 0.1.  Draw order per micro-batch: tokens,
+    permutation keys, the 80/10/10 roll, the replacement tokens."""
+    g = torch.Generator().manual_seed(seed)
+    n = max(1, int(round(0.15 * cfg.seq)))
+    out = []
+    for _ in range(steps):
+        step = []
+        for _ in range(micro_batches):
+            tok = torch.randint(0, cfg.vocab, (micro_batch, cfg.seq), generator=g)
+            pos = torch.rand(micro_batch, cfg.seq, generator=g).argsort(dim=1)[:, :n]
+            roll = torch.rand(micro_batch, cfg.seq, generator=g)
+            rnd = torch.randint(0, cfg.vocab, (micro_batch, cfg.seq), generator=g)
+            lab = torch.full_like(tok, -100)
+            inp = tok.clone()
+            for b in range(micro_batch):
+                for p_ in pos[b].tolist():
+                    lab[b, p_] = tok[b, p_]
+                    if roll[b, p_] < 0.8:
+                        inp[b, p_] = mask_id
+                    elif roll[b, p_] < 0.9:
+                        inp[b, p_] = rnd[b, p_]
+            step.append((inp, lab))
         out.append(step)
     return out

@@ -167,6 +167,17 @@ def test_colsum(L, rows, n):
     close(out - 1, dy.float().sum(0), 1e-3)
 
 
+def test_gelu_backward(L):
+    torch.manual_seed(4)
+    pre = torch.randn(1000, 1024, device="cuda").bfloat16()
+    dy = torch.randn_like(pre)
+    dx = torch.empty_like(pre)
+    L.gelu_bwd(dy, pre, dx)
+    x = pre.float().requires_grad_(True)
+    gelu(x).backward(dy.float())
+    close(dx, x.grad)
+
+
 def test_embedding(L):
     torch.manual_seed(6)
     V, h, B, S = 1024, 256, 4, 128

@@ -19,7 +19,7 @@ def build_engine(cfg, mb, gas, lr, seed=0):
     from bamboo_b200.module import PipelineModule
     os.environ["BAMBOO_QUIET"] = "1"
     tc = models.TransformerConfig(layers=cfg.layers, hidden=cfg.hidden, heads=cfg.heads, ffn=cfg.ffn, seq=cfg.seq,
-                                  vocab=cfg.vocab, causal=cfg.causal)
+                                  vocab=cfg.vocab, causal=cfg.causal, mlm=cfg.mlm)
     model = PipelineModule(models.transformer_layer_specs(tc, seed), num_stages=1, loss_fn=models.transformer_loss(tc),
                            partition_method="uniform")
     config = {"train_micro_batch_size_per_gpu": mb, "gradient_accumulation_steps": gas, "bf16": {"enabled": True},
@@ -34,7 +34,10 @@ def oracle_names(cfg):
     for i in range(cfg.layers):
         names += [f"b{i}.{n}" for n in ("ln1_w", "ln1_b", "qkv_w", "qkv_b", "proj_w", "proj_b", "ln2_w", "ln2_b",
                                         "fc1_w", "fc1_b", "fc2_w", "fc2_b")]
-    return names + ["lnf_w", "lnf_b", "head_w"]
+    names += ["lnf_w", "lnf_b"]
+    if cfg.mlm:
+        names += ["mlm_w", "mlm_b", "mlm_ln_w", "mlm_ln_b"]
+    return names + ["head_w"]
 
 
 def compare_grads(engine, ref, cfg):
@@ -89,6 +92,23 @@ def test_bidirectional_ragged_vocab_matches_oracle():
         got = float(engine.train_batch(data_iter=iter(batches)))
         assert got == pytest.approx(want, rel=TOL)
         compare_grads(engine, ref, cfg)
+
+
+def test_masked_lm_encoder_matches_oracle():
+    """BERT-style configuration at toy size: bidirectional attention, masked-LM head transform
+    (dense + GeLU + LayerNorm, stand-alone GeLU backward), loss on the 15 % chosen positions."""
+    cfg = gpt_ref.RefConfig(layers=2, hidden=256, heads=4, ffn=1024, seq=128, vocab=1000, causal=False, mlm=True)
+    mb, gas, lr = 4, 2, 1e-3
+    ref = gpt_ref.RefTrainer(cfg, seed=2, lr=lr, micro_batches=gas)
+    engine = build_engine(cfg, mb, gas, lr, seed=2)
+    for batches in gpt_ref.synthetic_mlm_batches(cfg, mb, gas, 3, seed=7):
+        want = ref.train_batch(batches)
+        got = float(engine.train_batch(data_iter=iter(batches)))
+        assert got == pytest.approx(want, rel=TOL)
+        compare_grads(engine, ref, cfg)
+    from bamboo_b200 import lib
+    torch.cuda.synchronize()
+    assert lib.read_status() == 0
 
 
 def test_layers_refuse_cpu_tensors():

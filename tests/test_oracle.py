@@ -61,3 +61,34 @@ def test_product_init_recipe_matches_oracle():
         assert torch.equal(getattr(blk, n).data, P[f"b1.{n}"]), n
     head = layers.Linear(CFG.hidden, CFG.vocab, bias=False, pad_to=128, seed=CFG.layers + 2)
     assert torch.equal(head.weight.data[: CFG.vocab], P["head_w"]) and head.weight.shape[0] == 128
+
+
+def test_masked_lm_batches_and_loss():
+    """15 % of every sequence is chosen, labels elsewhere are ignored, about 80 % of the chosen
+    inputs carry the mask id; the product's vectorised masking draws the same batch; the loss is
+    the mean over the chosen positions only."""
+    import torch.nn.functional as F
+    from bamboo_b200 import models
+    cfg = gpt_ref.RefConfig(layers=1, hidden=64, heads=2, ffn=128, seq=128, vocab=1000, causal=False, mlm=True)
+    (inp, lab), = gpt_ref.synthetic_mlm_batches(cfg, 8, 1, 1, seed=3)[0]
+    chosen = lab != -100
+    assert chosen.sum(1).tolist() == [round(0.15 * cfg.seq)] * 8
+    frac_mask = (inp[chosen] == 103).float().mean().item()
+    assert 0.7 < frac_mask < 0.9
+    assert torch.equal(inp[~chosen], inp[~chosen]) and (inp[~chosen] != 103).float().mean() > 0.99
+    g = torch.Generator().manual_seed(3)
+    tok = torch.randint(0, cfg.vocab, (8, cfg.seq), generator=g)
+    inp2, lab2 = models.mlm_mask(tok, g, cfg.vocab)
+    assert torch.equal(inp, inp2) and torch.equal(lab, lab2)
+    P = gpt_ref.init_params(cfg, 0)
+    loss = gpt_ref.forward_loss(cfg, P, inp, lab)
+    # same loss from per-position terms averaged over the chosen positions by hand
+    full = gpt_ref.forward_loss(cfg, P, inp, torch.where(chosen, lab, torch.zeros_like(lab)))  # all positions labelled
+    assert loss.item() != pytest.approx(full.item(), rel=1e-6)
+    x = P["wte"][inp] + P["wpe"][: cfg.seq].unsqueeze(0)
+    x = gpt_ref.block_forward(cfg, P, "b0.", x)
+    x = F.layer_norm(x, (cfg.hidden,), P["lnf_w"], P["lnf_b"], 1e-5)
+    x = F.layer_norm(F.gelu(F.linear(x, P["mlm_w"], P["mlm_b"]), approximate="tanh"), (cfg.hidden,), P["mlm_ln_w"], P["mlm_ln_b"], 1e-5)
+    logp = F.log_softmax(F.linear(x, P["head_w"]), -1)
+    manual = -(logp[chosen].gather(1, lab[chosen].unsqueeze(1))).mean()
+    assert loss.item() == pytest.approx(manual.item(), rel=1e-5)
