@@ -49,6 +49,35 @@ def model_config(name):
     return {"gpt2-medium": models.GPT2_MEDIUM, "bert-large": models.BERT_LARGE}.get(name, models.GPT_TOY)
 
 
+def contiguous_partition(costs, parts):
+    """Boundaries of `parts` non-empty contiguous groups of `costs` with the smallest maximum
+    group sum and, among those, the smallest sum of squares (dynamic programme over prefixes).
+    The package's `partition_balanced` follows the reference's bottleneck search, which may leave
+    the last stages empty when one heavy layer (the vocabulary head) ends the list."""
+    n = len(costs)
+    pre = [0.0]
+    for c in costs:
+        pre.append(pre[-1] + c)
+    INF = (float("inf"), float("inf"))
+    best = [[INF] * (n + 1) for _ in range(parts + 1)]
+    arg = [[0] * (n + 1) for _ in range(parts + 1)]
+    best[0][0] = (0.0, 0.0)
+    for k in range(1, parts + 1):
+        for j in range(k, n + 1):
+            for i in range(k - 1, j):
+                if best[k - 1][i] == INF:
+                    continue
+                load = pre[j] - pre[i]
+                cand = (max(best[k - 1][i][0], load), best[k - 1][i][1] + load * load)
+                if cand < best[k][j]:
+                    best[k][j], arg[k][j] = cand, i
+    bounds, j = [n], n
+    for k in range(parts, 0, -1):
+        j = arg[k][j]
+        bounds.append(j)
+    return bounds[::-1]
+
+
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
 
@@ -200,16 +229,15 @@ def main():
     rc = args.rc if args.rc != "auto" else ("eager" if world > 1 else "off")
     if world == 1:
         rc = "off"
-    # stage boundaries balanced by forward FLOPs per token (the embedding costs nothing, the
-    # vocabulary head about as much as 2hV / (24h^2 + 4sh) blocks)
-    from bamboo_b200.partition import partition_balanced
+    # stage boundaries balanced by time per micro-batch: a block counts 1, the embedding 0, the
+    # vocabulary head its FLOP ratio 2hV / (24h^2 + 4sh) scaled by 0.65, because its three large
+    # GEMMs run at ~1.2 PFLOP/s while a block (attention and row-wise kernels included) averages
+    # ~0.75 (measured on one GPU: 1.07 ms per block, 2.5 ms for the head, per micro-batch)
     h = cfg.hidden
-    head_cost = 2.0 * h * cfg.vocab / (24.0 * h * h + 4.0 * cfg.seq * h)
-    costs = [0.0] + [1.0] * cfg.layers + [0.0] + ([2.0 * h * h / (24.0 * h * h + 4.0 * cfg.seq * h)] if cfg.mlm else []) + [head_cost]
-    parts = partition_balanced([int(c * 1000) for c in costs], world)
-    for st in range(world - 1, 0, -1):          # no stage may be empty: steal the predecessor's last layer
-        if parts[st] >= parts[st + 1]:
-            parts[st] = parts[st + 1] - 1
+    blk = 24.0 * h * h + 4.0 * cfg.seq * h
+    head_cost = 0.65 * 2.0 * h * cfg.vocab / blk
+    costs = [0.0] + [1.0] * cfg.layers + [0.0] + ([0.65 * 2.0 * h * h / blk] if cfg.mlm else []) + [head_cost]
+    parts = contiguous_partition(costs, world)
     model = PipelineModule(models.transformer_layer_specs(cfg, 0), num_stages=world, loss_fn=models.transformer_loss(cfg),
                            partition_method="custom", custom_partitions=parts)
     engine, *_ = api.initialize(model=model, config={

@@ -20,9 +20,9 @@ def _oracle_losses():
     return [ref.train_batch(step) for step in data], ref
 
 
-def _train(rank, world, store, stages, rc, eager, victim_step):
-    """Body of one rank.  ``victim_step``: the last stage's rank announces its preemption so
-    that it is gone from step ``victim_step`` on (None = no failure)."""
+def _train(rank, world, store, stages, rc, eager, victim_step, victim_stage=None):
+    """Body of one rank.  ``victim_step``: the rank of ``victim_stage`` (default: the last stage)
+    announces its preemption so that it is gone from step ``victim_step`` on (None = no failure)."""
     import cpu_layers
     from bamboo_b200 import api
     from bamboo_b200.module import PipelineModule
@@ -35,7 +35,7 @@ def _train(rank, world, store, stages, rc, eager, victim_step):
     data = gpt_ref.synthetic_batches(CFG, MB, GAS, STEPS, seed=1)
     losses = []
     for step, batches in enumerate(data):
-        if victim_step is not None and step == victim_step - 1 and rank == stages - 1:
+        if victim_step is not None and step == victim_step - 1 and rank == (stages - 1 if victim_stage is None else victim_stage):
             engine.announce_preemption()
         loss = engine.train_batch(data_iter=iter(batches))
         losses.append(float(loss))
@@ -81,6 +81,33 @@ def test_failover_continues_the_same_trajectory(eager):
     assert out["losses"][3:] == pytest.approx(want[3:], rel=1e-5)
     total = sum(float(p.detach().double().sum()) for p in ref.P.values())
     assert sum(out["checksum"].values()) == pytest.approx(total, rel=1e-6)
+
+
+@pytest.mark.parametrize("eager,victim", [(False, None), (True, None), (True, 3), (False, 1)])
+def test_four_stage_pipeline(eager, victim):
+    """Four stages on four CPU ranks with redundant computation; optionally one stage (the last
+    one, or one in the middle whose neighbours on both sides must re-route) is preempted after
+    step 2.  The survivors' losses are those of an undisturbed single-process run."""
+    from dist_utils import run_ranks
+    want, ref = _oracle_losses()
+    res = run_ranks(_train, 4, 4, 1, eager, None if victim is None else 2, victim, timeout=300)
+    last = 3 if victim != 3 else 2                    # the rank that ends up owning the last stage
+    for r in range(4):
+        if r == victim:
+            assert res[r] == ("exit", 13)
+        else:
+            assert res[r][0] == "ok", res[r]
+    losses = res[last][1]["losses"]
+    if victim == 3:
+        assert losses[:2] == [0, 0] and losses[2:] == pytest.approx(want[2:], rel=1e-5)
+        assert res[2][1]["stage_ids"] == [2, 3]
+    else:
+        assert losses == pytest.approx(want, rel=1e-5)
+    if victim == 1:
+        assert res[0][1]["stage_ids"] == [0, 1]
+    total = sum(float(p.detach().double().sum()) for p in ref.P.values())
+    got = sum(sum(res[r][1]["checksum"].values()) for r in range(4) if r != victim)
+    assert got == pytest.approx(total, rel=1e-6)
 
 
 # ---------------------------------------------------------------------------------------------
