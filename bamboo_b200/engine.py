@@ -228,6 +228,7 @@ class PipelineEngine:
         # low-priority stream for redundant computation
         self.rc_stream = None
         self._rc_event = None
+        self._lp_refreshed = None
         if self.native and self.eager_recovery:
             lo, hi = torch.cuda.Stream.priority_range() if hasattr(torch.cuda.Stream, "priority_range") else (0, -1)
             prio = 0 if self._config.rc_stream_priority_low else -1
@@ -419,6 +420,10 @@ class PipelineEngine:
         if nxt not in self.param_buffers or nxt not in self.state_buffers:
             raise RuntimeError("Doesn't have param or state to recover")
         t0 = time.time()
+        if self.rc_stream is not None:
+            # redundant forwards and the shadow's working-copy refresh are ordered on the RC stream
+            torch.cuda.current_stream().wait_stream(self.rc_stream)
+            self._rc_event = None
         next_rank = self.grid.stage_to_global(nxt)
         next_coord = self.grid.topology().get_coord(next_rank)
         self.grid.topology().modify_mapping(rank=self.global_rank, **next_coord._asdict())
@@ -601,6 +606,22 @@ class PipelineEngine:
             return (self.total_loss / self.micro_batches).clone().detach()
         return 0
 
+    # ------------------------------------------------------------------ checkpoints
+    def save_checkpoint(self, save_dir, tag=None, client_state={}, save_latest=True):
+        """Per-layer model files plus one state file per stage (every rank calls it); same
+        signature and on-disk layout as ``DeepSpeedEngine.save_checkpoint``
+        (``deepspeed/runtime/engine.py:2197-2253``)."""
+        from . import checkpoint
+        return checkpoint.save_checkpoint(self, save_dir, tag, client_state, save_latest)
+
+    def load_checkpoint(self, load_dir, tag=None, load_module_strict=True, load_optimizer_states=True,
+                        load_lr_scheduler_states=True):
+        """Returns ``(path, client_state)`` like ``DeepSpeedEngine.load_checkpoint``
+        (``deepspeed/runtime/engine.py:1925-1990``); the stage partition may differ from the
+        one that wrote the checkpoint."""
+        from . import checkpoint
+        return checkpoint.load_checkpoint(self, load_dir, tag, load_optimizer_states, load_lr_scheduler_states)
+
     def eval_batch(self, *a, **k):
         raise PipelineError("eval_batch is outside the training-step path of this implementation")
 
@@ -649,6 +670,14 @@ class PipelineEngine:
             # redundant computation: off the critical path, on the low-priority stream
             ready = torch.cuda.current_stream().record_event()
             self.rc_stream.wait_event(ready)
+            # the redundant forward may run many micro-batches later than it was issued: its
+            # inputs must not go back to the main stream's allocator before it has read them
+            for t in (inputs if isinstance(inputs, tuple) else (inputs,)):
+                if torch.is_tensor(t) and t.is_cuda:
+                    t.record_stream(self.rc_stream)
+            label = self.pipe_buffers["label"][buffer_id] if stage_id == self.num_stages - 1 else None
+            if torch.is_tensor(label) and label.is_cuda:
+                label.record_stream(self.rc_stream)
             with torch.cuda.stream(self.rc_stream):
                 self._forward_stage(inputs, buffer_id, stage_id, retain=self._config.rc_retain_graph)
                 self._rc_event = self.rc_stream.record_event()
@@ -796,10 +825,6 @@ class PipelineEngine:
         return
 
     def _exec_optimizer_step(self, lr_kwargs=None):
-        if self._rc_event is not None:
-            # shadow forwards read the shadow weights the state transfer is about to overwrite
-            torch.cuda.current_stream().wait_event(self._rc_event)
-            self._rc_event = None
         self._join_wgrad_stream()
         scales = getattr(self, "_reduce_scale", {})
         if getattr(self, "capture_grads", False):
@@ -829,6 +854,10 @@ class PipelineEngine:
                 recv_from, tensors_in = self._shadow_source_rank[sid], self.param_buffers[sid].state_tensors()
         if send_to is None and recv_from is None:
             return
+        if self.rc_stream is not None and self._lp_refreshed is not None:
+            # the previous refresh (on the RC stream) reads the master copy this transfer overwrites
+            torch.cuda.current_stream().wait_event(self._lp_refreshed)
+            self._lp_refreshed = None
         try:
             self.transport.exchange_state(send_to, tensors_out, recv_from, tensors_in, self.global_steps)
         except PeerTimeout:
@@ -836,7 +865,17 @@ class PipelineEngine:
         if recv_from is not None:
             for sid in self.r_stage_ids:
                 if sid in self.param_buffers:
-                    self.param_buffers[sid].refresh_lp()
+                    if self.rc_stream is not None:
+                        # Redundant forwards of this step may still be queued on the low-priority
+                        # stream and read the shadow's bf16 working copy; the fp32 state that just
+                        # arrived is not read by them.  So the working copy is refreshed ON that
+                        # stream, behind them, and the main stream never waits for redundant work.
+                        self.rc_stream.wait_event(torch.cuda.current_stream().record_event())
+                        with torch.cuda.stream(self.rc_stream):
+                            self.param_buffers[sid].refresh_lp()
+                            self._lp_refreshed = self.rc_stream.record_event()
+                    else:
+                        self.param_buffers[sid].refresh_lp()
                     self.param_buffers[sid].step_count = self.arenas[self.stage_id].step_count
 
     def _alive(self, rank):
