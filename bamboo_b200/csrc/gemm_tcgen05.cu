@@ -47,6 +47,7 @@ struct GemmParams {
   int a_mn, b_mn;
   int epi;
   int ksplit, kb_per_split;   // split-K work units (fp32 add-reduction epilogue only)
+  int n_fast;                 // tile order: consecutive work units walk along N (else along M)
   void* D; void* D2; const void* bias; const void* aux;
   long long ldd, ld_aux;
   int* status;
@@ -225,8 +226,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       bool alive = true;
       for (int tile = worker; tile < num_tiles && alive; tile += num_workers) {
         const int mn = tile % num_mn, ks = tile / num_mn;
-        const int m0 = (mn % num_m) * C::TILE_M + (int)rank * BM;          // this CTA's A rows
-        const int n0 = (mn / num_m) * BN + (int)rank * C::B_ROWS;          // this CTA's share of B (pairs: half)
+        const int mi = p.n_fast ? mn / num_n : mn % num_m, ni = p.n_fast ? mn % num_n : mn / num_m;
+        const int m0 = mi * C::TILE_M + (int)rank * BM;                    // this CTA's A rows
+        const int n0 = ni * BN + (int)rank * C::B_ROWS;                    // this CTA's share of B (pairs: half)
         const int kb0 = ks * p.kb_per_split, kb1 = min(total_kb, kb0 + p.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!bb::mbar_wait(&empty_bar[s], phase ^ 1, abort_flag, p.status)) { alive = false; break; }
@@ -345,7 +347,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     bool alive = true;
     for (int tile = worker; tile < num_tiles && alive; tile += num_workers) {
       const int mn = tile % num_mn;
-      const int m0 = (mn % num_m) * C::TILE_M + (int)rank * BM, n0 = (mn / num_m) * BN;
+      const int mi = p.n_fast ? mn / num_n : mn % num_m, ni = p.n_fast ? mn % num_n : mn / num_m;
+      const int m0 = mi * C::TILE_M + (int)rank * BM, n0 = ni * BN;
       const int r0 = m0 + quarter * 32;            // first output row of this warp
       const bool got = bb::mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status);
       if (!__all_sync(0xffffffffu, got)) { alive = false; break; }
@@ -461,6 +464,9 @@ int launch(const bb_gemm_desc* g, cudaStream_t stream) {
   p.M = g->M; p.N = g->N; p.K = g->K; p.a_mn = g->a_mn_major; p.b_mn = g->b_mn_major; p.epi = g->epilogue;
   p.D = g->D; p.D2 = g->D2; p.bias = g->bias; p.aux = g->aux; p.ldd = g->ldd; p.ld_aux = g->ld_aux ? g->ld_aux : g->ldd;
   p.status = bb_device_status_word();
+  // The CTAs that run at the same time share one operand and stream the other: walk along the
+  // dimension of the SMALLER operand, so that the larger one passes through L2 once.
+  p.n_fast = (long long)g->M > (long long)g->N ? 1 : 0;
   const int total_kb = (g->K + BK - 1) / BK;
   const int mn_tiles = ((g->M + C::TILE_M - 1) / C::TILE_M) * ((g->N + BN - 1) / BN);
   const int workers_max = PAIR ? bb_num_sms() / 2 : bb_num_sms();

@@ -111,6 +111,21 @@ def test_gemm_is_linear_and_deterministic_at_full_size(L):
     assert torch.equal(o1[:256], (A1[:256].float() @ B.float().t()))
 
 
+def test_gemm_cta_pairs_at_full_size(L):
+    """Input-gradient shape of the MLP (long reduction, B stored [K, N]): the heuristic picks CTA
+    pairs; small integers make the result exact, and single CTAs must give the same bits."""
+    torch.manual_seed(13)
+    M, N, K = 8192, 1024, 4096
+    A = torch.randint(-3, 4, (M, K), device="cuda").bfloat16()
+    B = torch.randint(-3, 4, (K, N), device="cuda").bfloat16()      # stored [K, N]
+    pair = torch.empty(M, N, device="cuda")
+    single = torch.empty(M, N, device="cuda")
+    L.gemm(A, B, pair, b_mn=True, epilogue=L.EPI_STORE_F32, M=M, N=N, K=K)
+    L.gemm(A, B, single, b_mn=True, epilogue=L.EPI_STORE_F32, M=M, N=N, K=K, cta_pair=-1)
+    assert torch.equal(pair, single)
+    assert torch.equal(pair[:512], A[:512].float() @ B.float())
+
+
 @pytest.mark.parametrize("cta_pair", [-1, 1])
 @pytest.mark.parametrize("split", [0, 1, 3, 8])
 def test_gemm_split_k_accumulation(L, split, cta_pair):
