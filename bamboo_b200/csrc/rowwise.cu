@@ -5,6 +5,7 @@
 // multiple of the SM count and stride over rows.
 #include "common.cuh"
 #include <stdio.h>
+#include <stdlib.h>
 
 namespace {
 
@@ -196,6 +197,103 @@ layernorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat
   }
 }
 
+// Column-owner variant (hidden sizes that are a multiple of 256, up to 8192): a thread owns 8
+// columns of one of `slots` row slots; its dgamma/dbeta partial sums are 16 registers, so several
+// CTAs fit on an SM and every thread keeps 2 x LNB_R 16-byte loads in flight (the warp-per-row
+// kernels hold a whole row's partial sums per warp, run one CTA per SM and are latency-bound at
+// about a third of the HBM rate).  The two row sums of LNB_R rows per slot are combined across
+// the slot's warps through double-buffered shared memory: one block barrier per 8 rows.
+constexpr int LNB_R = 4;
+template <int MAXT>
+__global__ void __launch_bounds__(MAXT, MAXT <= 256 ? 2 : 1)
+layernorm_bwd_cols_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                          const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
+                          const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
+                          __nv_bfloat16* __restrict__ dx, float* __restrict__ partials, int rows, int h, int slots) {
+  extern __shared__ float sm[];
+  const int tpr = h >> 3;                          // threads per row
+  const int wps = tpr >> 5;                        // warps per slot
+  const int slot = threadIdx.x / tpr, tc = threadIdx.x - slot * tpr;   // my slot, my 8-column group
+  const int lane = threadIdx.x & 31, wis = tc >> 5;
+  float* red = sm;                                 // [2][slots][wps][2 * LNB_R]
+  float* fin = sm + 2 * slots * wps * 2 * LNB_R;   // [slots][2][h] final combination
+  float g[8], ag[8], ab[8];
+  unpack8(__ldg(reinterpret_cast<const uint4*>(gamma) + tc), g);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { ag[i] = 0.f; ab[i] = 0.f; }
+  const float inv_h = 1.f / h;
+  int buf = 0;
+  for (int base = blockIdx.x * slots * LNB_R; base < rows; base += gridDim.x * slots * LNB_R) {
+    const int r0 = base + slot * LNB_R;
+    uint4 qd[LNB_R], qx[LNB_R];
+    float mean[LNB_R], rstd[LNB_R];
+#pragma unroll
+    for (int r = 0; r < LNB_R; ++r) {
+      const int row = r0 + r;
+      if (row < rows) {
+        qd[r] = reinterpret_cast<const uint4*>(dy + (size_t)row * h)[tc];
+        qx[r] = reinterpret_cast<const uint4*>(x + (size_t)row * h)[tc];
+        mean[r] = mean_in[row]; rstd[r] = rstd_in[row];
+      } else {
+        qd[r] = make_uint4(0, 0, 0, 0); qx[r] = qd[r]; mean[r] = 0.f; rstd[r] = 0.f;
+      }
+    }
+    float s[2 * LNB_R];
+#pragma unroll
+    for (int r = 0; r < LNB_R; ++r) {
+      float d[8], f[8];
+      unpack8(qd[r], d); unpack8(qx[r], f);
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { const float t = d[i] * g[i]; s1 += t; s2 += t * (f[i] - mean[r]) * rstd[r]; }
+      s[2 * r] = s1; s[2 * r + 1] = s2;
+    }
+#pragma unroll
+    for (int k = 0; k < 2 * LNB_R; ++k) s[k] = warp_sum(s[k]);
+    float* my = red + ((buf * slots + slot) * wps + wis) * 2 * LNB_R;
+    if (lane == 0) {
+#pragma unroll
+      for (int k = 0; k < 2 * LNB_R; ++k) my[k] = s[k];
+    }
+    __syncthreads();
+    const float* all = red + (buf * slots + slot) * wps * 2 * LNB_R;
+#pragma unroll
+    for (int k = 0; k < 2 * LNB_R; ++k) {
+      float t = 0.f;
+      for (int w = 0; w < wps; ++w) t += all[w * 2 * LNB_R + k];    // fixed order
+      s[k] = t * inv_h;
+    }
+    buf ^= 1;
+#pragma unroll
+    for (int r = 0; r < LNB_R; ++r) {
+      const int row = r0 + r;
+      if (row >= rows) continue;
+      float d[8], f[8], o[8], rr[8];
+      unpack8(qd[r], d); unpack8(qx[r], f);
+      if (dres) unpack8(reinterpret_cast<const uint4*>(dres + (size_t)row * h)[tc], rr);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float xh = (f[i] - mean[r]) * rstd[r];
+        o[i] = rstd[r] * (d[i] * g[i] - s[2 * r] - xh * s[2 * r + 1]) + (dres ? rr[i] : 0.f);
+        ag[i] += d[i] * xh;
+        ab[i] += d[i];
+      }
+      reinterpret_cast<uint4*>(dx + (size_t)row * h)[tc] = pack8(o);
+    }
+  }
+  // combine the slots' column sums (fixed order) and write this CTA's partial row
+  float* mine = fin + (size_t)slot * 2 * h;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { mine[tc * 8 + i] = ag[i]; mine[h + tc * 8 + i] = ab[i]; }
+  __syncthreads();
+  float* out = partials + (size_t)blockIdx.x * 2 * h;
+  for (int j = threadIdx.x; j < 2 * h; j += blockDim.x) {
+    float t = 0.f;
+    for (int q = 0; q < slots; ++q) t += fin[(size_t)q * 2 * h + j];
+    out[j] = t;
+  }
+}
+
 // out[j] += sum_p partials[p * stride + j].  A 32-column x 8-way block: eight threads share
 // a column, each sums every eighth partial, shared memory combines them in a fixed order
 // (deterministic).
@@ -339,7 +437,19 @@ int ln_bwd_warps(int h) {
   int w = (int)((200 * 1024) / ((size_t)2 * h * sizeof(float)));
   return w > WARPS ? WARPS : w;
 }
+// column-owner kernel: hidden size a multiple of 256 and at most 8192 (1024 threads per row slot)
+bool ln_bwd_cols_ok(int h) {
+  static int off = -1;
+  if (off < 0) { const char* e = getenv("BB_LN_BWD_ROWS"); off = (e && e[0] == '1') ? 1 : 0; }   // 1: warp-per-row kernels
+  return !off && h % 256 == 0 && h <= 8192;
+}
+int ln_bwd_cols_slots(int h) { const int tpr = h / 8; return tpr >= 256 ? 1 : 256 / tpr; }
 int ln_bwd_grid(int rows, int h) {
+  if (ln_bwd_cols_ok(h)) {
+    const int per = ln_bwd_cols_slots(h) * LNB_R;
+    long long want = ((long long)rows + per - 1) / per, cap = 2LL * bb_num_sms();
+    return (int)(want < cap ? (want > 0 ? want : 1) : cap);
+  }
   const int w = ln_bwd_warps(h);
   long long want = ((long long)rows + w - 1) / w;
   long long cap = (long long)bb_num_sms() * (w * 2 * h * 4 > 100 * 1024 ? 1 : 2);
@@ -351,6 +461,26 @@ namespace {
 // launches the backward main kernel (register variant when the hidden size allows it)
 int ln_bwd_main(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, const void* dres,
                 void* dx, float* ws, int rows, int h, int grid, int warps, cudaStream_t s) {
+  if (ln_bwd_cols_ok(h)) {
+    const int slots = ln_bwd_cols_slots(h), tpr = h / 8;
+    const size_t sm_bytes = ((size_t)2 * slots * (tpr / 32) * 2 * LNB_R + (size_t)slots * 2 * h) * sizeof(float);
+    static bool attr_cols = false;
+    if (!attr_cols) {
+      BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_cols_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
+      BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_cols_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
+      BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_cols_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
+      attr_cols = true;
+    }
+    const int threads = slots * tpr;
+#define BB_LNC_ARGS (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, mean, rstd, \
+                    (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, ws, rows, h, slots
+    if (threads <= 256) layernorm_bwd_cols_kernel<256><<<grid, threads, sm_bytes, s>>>(BB_LNC_ARGS);
+    else if (threads <= 512) layernorm_bwd_cols_kernel<512><<<grid, threads, sm_bytes, s>>>(BB_LNC_ARGS);
+    else layernorm_bwd_cols_kernel<1024><<<grid, threads, sm_bytes, s>>>(BB_LNC_ARGS);
+#undef BB_LNC_ARGS
+    BB_CUDA_CHECK(cudaGetLastError());
+    return BB_OK;
+  }
   const size_t smem = (size_t)warps * 2 * h * sizeof(float);
   static bool attr = false;
   if (!attr) {

@@ -280,6 +280,11 @@ def main():
     host = synthetic_tokens(cfg, max(args.warmup, 1) + args.steps, seed=1, pin=True)
     resident = [[(t.to(dev), l.to(dev)) for t, l in step] for step in host[-args.steps:]]
     timed(host[:max(args.warmup, 1)], read_loss=True)                      # warm-up (untimed)
+    if world > 1:
+        # multi-stage runs: the caching allocator keeps growing its pools for a few more steps
+        # (buffers that crossed to the redundant-computation or weight-gradient stream return
+        # late), and every growth is a device-wide cudaMalloc; settle it before the timed region
+        timed(host[:max(args.warmup, 1)], read_loss=True)
 
     sampler = ClockSampler(local_rank)
     sampler.start()
