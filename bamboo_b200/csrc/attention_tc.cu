@@ -177,9 +177,9 @@ constexpr int NSB = 3;                           // score buffers in tensor memo
 // ------------------------------------------------------------------ dQ (pipelined)
 // smem: Q, dO [128 x 64] | K, V sub-tiles [64 x 64] x 3 stages | dS [128 q x 64 kv] x 2
 // TMEM: S 2 x 64 | dP 2 x 64 | dQ 64
-__global__ void __launch_bounds__(NT2, 1)
-attn_tc_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
-                   const __grid_constant__ CUtensorMap tm_do, const TcParams p) {
+__device__ __forceinline__ void
+attn_tc_dq2_body(const CUtensorMap& tm_q, const CUtensorMap& tm_kv, const CUtensorMap& tm_do, const TcParams& p,
+                 const int bx, const int nbx) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
@@ -198,7 +198,7 @@ attn_tc_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint64_t* acc_full = ds_empty + 2;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+  const int qb = nbx - 1 - bx, head = blockIdx.y, batch = blockIdx.z;
   const int q0 = qb * TQ;
   const int row_base = batch * p.S;
   const int colq = head * HD, colk = p.hidden + head * HD, colv = 2 * p.hidden + head * HD;
@@ -347,9 +347,8 @@ constexpr int DQ2_SMEM = 2 * TILE_BYTES + 2 * NST * SUB_BYTES + 2 * TILE_BYTES +
 // smem: K, V [128 x 64] | Q, dO sub-tiles [64 x 64] x 3 stages | P^T, dS^T [128 kv x 64 q] x 2 each
 //       | per-group lse / delta of the sub-block's 64 query columns
 // TMEM: S^T 2 x 64 | dP^T 2 x 64 | dV 64 | dK 64
-__global__ void __launch_bounds__(NT2, 1)
-attn_tc_dkv2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_constant__ CUtensorMap tm64,
-                    const __grid_constant__ CUtensorMap tm_do64, const TcParams p) {
+__device__ __forceinline__ void
+attn_tc_dkv2_body(const CUtensorMap& tm128, const CUtensorMap& tm64, const CUtensorMap& tm_do64, const TcParams& p, const int bx) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
@@ -371,7 +370,7 @@ attn_tc_dkv2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
   uint64_t* acc_full = p_empty + 2;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kb = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+  const int kb = bx, head = blockIdx.y, batch = blockIdx.z;
   const int k0 = kb * TQ;
   const int row_base = batch * p.S;
   const int colq = head * HD, colk = p.hidden + head * HD, colv = 2 * p.hidden + head * HD;
@@ -546,6 +545,18 @@ attn_tc_dkv2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
 }
 
 constexpr int DKV2_SMEM = 2 * TILE_BYTES + 2 * NST * SUB_BYTES + 4 * TILE_BYTES + 4 * SUB * (int)sizeof(float) + (int)sizeof(Ctl) + 1024;
+
+// Both backward roles in one launch: of the 2 * nbx CTAs of a (batch, head), the first nbx own a
+// key tile (dK, dV) and the rest a query tile (dQ).  The two roles are independent, so the tail
+// of one fills with CTAs of the other instead of leaving SMs idle between two launches.
+constexpr int BWD2_SMEM = DKV2_SMEM > DQ2_SMEM ? DKV2_SMEM : DQ2_SMEM;
+__global__ void __launch_bounds__(NT2, 1)
+attn_tc_bwd2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_constant__ CUtensorMap tm64,
+                    const __grid_constant__ CUtensorMap tm_do128, const __grid_constant__ CUtensorMap tm_do64, const TcParams p) {
+  const int nbx = gridDim.x >> 1;
+  if ((int)blockIdx.x < nbx) attn_tc_dkv2_body(tm128, tm64, tm_do64, p, blockIdx.x);
+  else attn_tc_dq2_body(tm128, tm64, tm_do128, p, blockIdx.x - nbx, nbx);
+}
 
 // ------------------------------------------------------------------ forward (two query tiles in ping-pong)
 // A CTA owns 256 query rows of one (batch, head) as two 128-row tiles; compute group g (4 warps,
@@ -819,16 +830,14 @@ int bb_attention_tc_bwd(const void* qkv_q, const void* out, const void* d_out, c
   if (int rc = bbhost::encode_2d(&tm_do64, d_out, T, (long long)H * HD, stride_o, HD, SUB)) return rc;
   static bool attr = false;
   if (!attr) {
-    if (int rc = set_smem(attn_tc_dq2_kernel, DQ2_SMEM)) return rc;
-    if (int rc = set_smem(attn_tc_dkv2_kernel, DKV2_SMEM)) return rc;
+    if (int rc = set_smem(attn_tc_bwd2_kernel, BWD2_SMEM)) return rc;
     attr = true;
   }
   const long long chunks = T * H * 8;
   long long dgrid = (chunks + 511) / 512, cap = (long long)bb_num_sms() * 8;
   attn_tc_delta_kernel<<<(int)(dgrid < cap ? dgrid : cap), 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out, p);
-  dim3 grid((S + TQ - 1) / TQ, H, B);
-  attn_tc_dkv2_kernel<<<grid, NT2, DKV2_SMEM, stream>>>(tm_qkv, tm_qkv64, tm_do64, p);
-  attn_tc_dq2_kernel<<<grid, NT2, DQ2_SMEM, stream>>>(tm_qkv, tm_qkv64, tm_do, p);
+  dim3 grid(2 * ((S + TQ - 1) / TQ), H, B);
+  attn_tc_bwd2_kernel<<<grid, NT2, BWD2_SMEM, stream>>>(tm_qkv, tm_qkv64, tm_do, tm_do64, p);
   BB_CUDA_CHECK(cudaGetLastError());
   return BB_OK;
 }
