@@ -502,6 +502,10 @@ int launch(const bb_gemm_desc* g, cudaStream_t stream) {
   if (g->max_ctas > 0 && g->max_ctas / (PAIR ? 2 : 1) < workers) workers = g->max_ctas / (PAIR ? 2 : 1);
   if (workers < 1) workers = 1;
   if (tiles < workers) workers = tiles;
+  // max_ctas < 0: one work unit per CTA (or pair).  Meant for work on a low-priority stream: a
+  // persistent CTA that found a free SM keeps it for its whole tile loop, and a persistent kernel
+  // of the main stream launched meanwhile waits for that SM with a fixed share of the tiles.
+  if (g->max_ctas < 0) workers = tiles;
   if constexpr (PAIR) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * workers); cfg.blockDim = dim3(NUM_THREADS);

@@ -678,8 +678,13 @@ class PipelineEngine:
             label = self.pipe_buffers["label"][buffer_id] if stage_id == self.num_stages - 1 else None
             if torch.is_tensor(label) and label.is_cuda:
                 label.record_stream(self.rc_stream)
+            from . import lib as _lib
             with torch.cuda.stream(self.rc_stream):
-                self._forward_stage(inputs, buffer_id, stage_id, retain=self._config.rc_retain_graph)
+                _lib.GEMM_MAX_CTAS = -1 if self._config.rc_short_ctas else 0    # short CTAs: see bb_gemm_desc.max_ctas
+                try:
+                    self._forward_stage(inputs, buffer_id, stage_id, retain=self._config.rc_retain_graph)
+                finally:
+                    _lib.GEMM_MAX_CTAS = 0
                 self._rc_event = self.rc_stream.record_event()
         else:
             self._forward_stage(inputs, buffer_id, stage_id, retain=(not shadow) or self._config.rc_retain_graph)

@@ -95,6 +95,11 @@ def _stream(raw=None):
 GEMM_CTA_PAIR = int(os.environ.get("BB_GEMM_CTA_PAIR", "0"))
 
 
+# Default for GemmDesc.max_ctas; the engine sets it to -1 (one tile per CTA) while it issues
+# redundant computation on the low-priority stream and back to 0 afterwards.
+GEMM_MAX_CTAS = 0
+
+
 def gemm(a, b, out, *, a_mn=False, b_mn=False, epilogue=EPI_STORE, bias=None, out2=None, aux=None,
          M=None, N=None, K=None, tile_n=0, max_ctas=0, split_k=0, cta_pair=0, stream=None):
     """out[M,N] = op(a)[M,K] @ op(b)[N,K]^T with a fused epilogue; see bb_gemm_bf16.
@@ -115,7 +120,7 @@ def gemm(a, b, out, *, a_mn=False, b_mn=False, epilogue=EPI_STORE, bias=None, ou
                  B=b.data_ptr(), ldb=b.stride(0), b_mn_major=int(b_mn), D=out.data_ptr(), ldd=out.stride(0),
                  epilogue=epilogue, bias=None if bias is None else bias.data_ptr(),
                  D2=None if out2 is None else out2.data_ptr(), aux=None if aux is None else aux.data_ptr(),
-                 ld_aux=aux.stride(0) if aux is not None else 0, tile_n=tile_n, max_ctas=max_ctas, split_k=split_k,
+                 ld_aux=aux.stride(0) if aux is not None else 0, tile_n=tile_n, max_ctas=max_ctas or GEMM_MAX_CTAS, split_k=split_k,
                  cta_pair=cta_pair or GEMM_CTA_PAIR)
     global LAUNCHES
     LAUNCHES += 1

@@ -243,7 +243,7 @@ def main():
     engine, *_ = api.initialize(model=model, config={
         "train_micro_batch_size_per_gpu": MICRO_BATCH, "gradient_accumulation_steps": MICRO_BATCHES,
         "bf16": {"enabled": True}, "optimizer": {"type": "Adam", "params": {"lr": 1e-4}},
-        "bamboo_b200": {"rc_retain_graph": False}},
+        "bamboo_b200": {"rc_retain_graph": False, "rc_short_ctas": os.environ.get("BB_RC_SHORT_CTAS", "0") == "1"}},
         redundancy_level=0 if rc == "off" else 1, eager_recovery=(rc == "eager"))
     dev = torch.device("cuda", local_rank)
     tokens_per_step = MICRO_BATCH * MICRO_BATCHES * cfg.seq

@@ -58,7 +58,8 @@ typedef struct bb_gemm_desc {
   void* D2;                         /* second output of BB_EPI_BIAS_GELU, same ldd      */
   const void* aux; long long ld_aux;/* bf16 [M,N] operand of DGELU / RESIDUAL           */
   int tile_n;                       /* 0 = choose, else 128 or 256                      */
-  int max_ctas;                     /* 0 = one per SM; else cap (leaves SMs to a concurrent stream) */
+  int max_ctas;                     /* 0 = one persistent CTA per SM; > 0 = cap (leaves SMs to a concurrent stream);
+                                       < 0 = one tile per CTA (short CTAs for a low-priority stream) */
   int split_k;                      /* BB_EPI_ACCUM_F32 only: 0 = choose, else number of K splits */
   int cta_pair;                     /* 0 = choose, 1 = CTA pairs (cta_group::2, 256 x 256 tiles), -1 = single CTAs */
 } bb_gemm_desc;
