@@ -25,7 +25,8 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;        // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int NUM_THREADS = 320;   // TMA warp, MMA warp, two epilogue groups of four warps
+// threads: TMA warp, MMA warp and EW epilogue warps per TMEM lane quarter (EW = 2: 320, EW = 4: 576)
+constexpr int num_threads(int ew) { return 64 + 128 * ew; }
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
 // Epilogue staging: one 4 KiB slab (32 rows x 128 bytes = 64 bf16 or 32 fp32 columns) per
 // epilogue warp; shared memory is better spent on main-loop stages.
@@ -151,6 +152,65 @@ __device__ __forceinline__ void slab_flush_f32(const uint8_t* slab, float* dst, 
   }
 }
 
+// ---- narrow variant (four epilogue warps per lane quarter): 32 rows x 64 bytes = 32 bf16
+// columns per pass, 2 KiB per warp.  Chunk c of row r sits at c ^ ((r >> 1) & 3): eight
+// consecutive rows cover all 32 banks once, on the row side (lane == row) and on the coalesced
+// side (lane -> row 8*i + lane/4, chunk lane%4, i = 0..3).
+__device__ __forceinline__ uint32_t slab64_off(int row, int chunk) { return row * 64 + ((chunk ^ ((row >> 1) & 3)) << 4); }
+
+__device__ __forceinline__ void slab64_store_row(uint8_t* slab, int row, const float* v /*32*/) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint4 q;
+    q.x = bb::pack_bf16x2(v[8 * c + 0], v[8 * c + 1]); q.y = bb::pack_bf16x2(v[8 * c + 2], v[8 * c + 3]);
+    q.z = bb::pack_bf16x2(v[8 * c + 4], v[8 * c + 5]); q.w = bb::pack_bf16x2(v[8 * c + 6], v[8 * c + 7]);
+    *reinterpret_cast<uint4*>(slab + slab64_off(row, c)) = q;
+  }
+}
+// rows r0.., columns nb..nb+31 of a bf16 matrix -> slab (zero outside the matrix), coalesced
+__device__ __forceinline__ void slab64_fetch(uint8_t* slab, const __nv_bfloat16* src, long long ld, int r0, int nb, int M, int N, int lane) {
+  const int c = nb + (lane & 3) * 8;
+  uint4 q[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = r0 + 8 * i + (lane >> 2);
+    q[i] = make_uint4(0, 0, 0, 0);
+    if (r < M) {
+      const __nv_bfloat16* g = src + (long long)r * ld + c;
+      if (c + 8 <= N) {
+        q[i] = __ldg(reinterpret_cast<const uint4*>(g));
+      } else {
+        unsigned short e[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) e[k] = (c + k < N) ? __bfloat16_as_ushort(g[k]) : (unsigned short)0;
+        q[i].x = e[0] | ((uint32_t)e[1] << 16); q[i].y = e[2] | ((uint32_t)e[3] << 16);
+        q[i].z = e[4] | ((uint32_t)e[5] << 16); q[i].w = e[6] | ((uint32_t)e[7] << 16);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(slab + slab64_off(8 * i + (lane >> 2), lane & 3)) = q[i];
+}
+__device__ __forceinline__ void slab64_flush(const uint8_t* slab, __nv_bfloat16* dst, long long ld, int r0, int nb, int M, int N, int lane) {
+  const int c = nb + (lane & 3) * 8;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int rl = 8 * i + (lane >> 2);
+    const int r = r0 + rl;
+    const uint4 q = *reinterpret_cast<const uint4*>(slab + slab64_off(rl, lane & 3));
+    if (r < M) {
+      __nv_bfloat16* g = dst + (long long)r * ld + c;
+      if (c + 8 <= N) {
+        *reinterpret_cast<uint4*>(g) = q;
+      } else {
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) if (c + k < N) g[k] = __ushort_as_bfloat16((unsigned short)(w[k >> 1] >> (16 * (k & 1))));
+      }
+    }
+  }
+}
+
 // bias[n0 .. n0+W) added to v; columns past N read as zero
 template <int W>
 __device__ __forceinline__ void add_bias(const GemmParams& p, int n0, float* v) {
@@ -169,8 +229,8 @@ __device__ __forceinline__ void add_bias(const GemmParams& p, int n0, float* v) 
   }
 }
 
-template <int BN, bool PAIR>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+template <int BN, bool PAIR, int EW>
+__global__ void __launch_bounds__(num_threads(EW), 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          const GemmParams p) {
   using C = Cfg<BN, PAIR>;
@@ -204,7 +264,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     *abort_flag = 0;
     for (int s = 0; s < C::STAGES; ++s) { bb::mbar_init(&full_bar[s], 1); bb::mbar_init(&empty_bar[s], 1); }
     // accumulator hand-back: one arrival per epilogue warp (of both CTAs for a pair, on rank 0's barrier)
-    for (int a = 0; a < 2; ++a) { bb::mbar_init(&tmem_full[a], 1); bb::mbar_init(&tmem_empty[a], PAIR ? 16 : 8); }
+    for (int a = 0; a < 2; ++a) { bb::mbar_init(&tmem_full[a], 1); bb::mbar_init(&tmem_empty[a], (PAIR ? 2 : 1) * 4 * EW); }
     bb::fence_barrier_init();
     bb::tma_prefetch_desc(&tmA);
     bb::tma_prefetch_desc(&tmB);
@@ -336,15 +396,82 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     // fused math -> the warp's private 4 KiB staging slab in shared memory -> coalesced 16-byte
     // global stores (fp32 add-reduction: vector red) by the same warp.  Nothing here waits on
     // another warp or on the TMA queue, which the producer keeps full of operand loads.
-    const int eg = (warp - 2) >> 2;                // which of the quarter's two warps
+    const int eg = (warp - 2) >> 2;                // which of the quarter's EW warps
     const int quarter = warp & 3;
     const int epi = p.epi;
     const bool f32 = (epi == BB_EPI_ACCUM_F32 || epi == BB_EPI_STORE_F32);
     const bool dual = (epi == BB_EPI_BIAS_GELU);
     const bool has_aux = (epi == BB_EPI_MUL_DGELU || epi == BB_EPI_BIAS_RESIDUAL);
-    uint8_t* slab = panels + (warp - 2) * SLAB_BYTES;
     int acc = 0; uint32_t acc_phase = 0;
     bool alive = true;
+    if constexpr (EW == 4) {
+      // Narrow variant for the epilogues with the most arithmetic per element (GeLU and its
+      // derivative) on short reductions, where eight warps cannot finish a tile's epilogue
+      // within the next tile's main loop: sixteen warps, 32 bf16 columns per pass (bf16 outputs only).
+      uint8_t* slab = panels + (warp - 2) * (SLAB_BYTES / 2);
+      for (int tile = worker; tile < num_tiles && alive; tile += num_workers) {
+        const int mn = tile % num_mn;
+        const int mi = p.n_fast ? mn / num_n : mn % num_m, ni = p.n_fast ? mn % num_n : mn / num_m;
+        const int m0 = mi * C::TILE_M + (int)rank * BM, n0 = ni * BN;
+        const int r0 = m0 + quarter * 32;
+        const bool got = bb::mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status);
+        if (!__all_sync(0xffffffffu, got)) { alive = false; break; }
+        bb::tc_fence_after_sync();
+        const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+        constexpr int npanels = BN / 32;
+#pragma unroll 1
+        for (int pn = eg; pn < npanels; pn += 4) {
+          const int nb = n0 + pn * 32;
+          const bool inside = (nb < p.N) && (r0 < p.M);
+          if (has_aux && inside) slab64_fetch(slab, reinterpret_cast<const __nv_bfloat16*>(p.aux), p.ld_aux, r0, nb, p.M, p.N, lane);
+          float v[32];
+          {
+            uint32_t r[32];
+            bb::tmem_ld_32x32b_x32(t_row + pn * 32, r);
+            bb::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          }
+          if (pn + 4 >= npanels) {
+            bb::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+              if (PAIR) bb::mbar_arrive_cluster(bb::mapa_shared(bb::smem_u32(&tmem_empty[acc]), 0));
+              else bb::mbar_arrive(&tmem_empty[acc]);
+            }
+          }
+          if (!inside) continue;
+          if (epi == BB_EPI_BIAS || dual || epi == BB_EPI_BIAS_RESIDUAL) add_bias<32>(p, nb, v);
+          if (dual) {
+            slab64_store_row(slab, lane, v);           // pre-activation first
+            __syncwarp();
+            slab64_flush(slab, reinterpret_cast<__nv_bfloat16*>(p.D2), p.ldd, r0, nb, p.M, p.N, lane);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = bb::gelu_tanh(__bfloat162float(__float2bfloat16(v[i])));
+            __syncwarp();
+          } else if (has_aux) {
+            __syncwarp();
+            float x[32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) unpack8(*reinterpret_cast<const uint4*>(slab + slab64_off(lane, c)), x + 8 * c);
+            if (epi == BB_EPI_MUL_DGELU) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] *= bb::gelu_tanh_grad(x[i]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] += x[i];
+            }
+            __syncwarp();
+          }
+          slab64_store_row(slab, lane, v);
+          __syncwarp();
+          slab64_flush(slab, reinterpret_cast<__nv_bfloat16*>(p.D), p.ldd, r0, nb, p.M, p.N, lane);
+          __syncwarp();
+        }
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    } else {
+    uint8_t* slab = panels + (warp - 2) * SLAB_BYTES;
     for (int tile = worker; tile < num_tiles && alive; tile += num_workers) {
       const int mn = tile % num_mn;
       const int mi = p.n_fast ? mn / num_n : mn % num_m, ni = p.n_fast ? mn % num_n : mn / num_m;
@@ -433,6 +560,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       }
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
+    }   // EW == 2
   }
 
   bb::tc_fence_before_sync();
@@ -449,7 +577,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 // ---------------------------------------------------------------- host side
 using bbhost::encode_2d;
 
-template <int BN, bool PAIR>
+template <int BN, bool PAIR, int EW>
 int launch(const bb_gemm_desc* g, cudaStream_t stream) {
   using C = Cfg<BN, PAIR>;
   CUtensorMap tmA, tmB;
@@ -494,7 +622,7 @@ int launch(const bb_gemm_desc* g, cudaStream_t stream) {
   p.ksplit = (total_kb + p.kb_per_split - 1) / p.kb_per_split;   // no empty splits
   static bool attr_set = false;
   if (!attr_set) {
-    BB_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    BB_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, PAIR, EW>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     attr_set = true;
   }
   const int tiles = mn_tiles * p.ksplit;
@@ -508,15 +636,15 @@ int launch(const bb_gemm_desc* g, cudaStream_t stream) {
   if (g->max_ctas < 0) workers = tiles;
   if constexpr (PAIR) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * workers); cfg.blockDim = dim3(NUM_THREADS);
+    cfg.gridDim = dim3(2 * workers); cfg.blockDim = dim3(num_threads(EW));
     cfg.dynamicSmemBytes = C::SMEM_BYTES; cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    BB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<BN, true>, tmA, tmB, p));
+    BB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<BN, true, EW>, tmA, tmB, p));
   } else {
-    gemm_bf16_tcgen05_kernel<BN, false><<<workers, NUM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, p);
+    gemm_bf16_tcgen05_kernel<BN, false, EW><<<workers, num_threads(EW), C::SMEM_BYTES, stream>>>(tmA, tmB, p);
   }
   BB_CUDA_CHECK(cudaGetLastError());
   return BB_OK;
@@ -543,6 +671,10 @@ extern "C" int bb_gemm_bf16(const bb_gemm_desc* g, void* stream) {
     bb_set_last_error_msg("bb_gemm_bf16: pointers must be 16-byte aligned and leading dimensions multiples of 8 elements");
     return BB_ERR_INVALID_ARG;
   }
+  if ((g->epi_warps != 0 && g->epi_warps != 2 && g->epi_warps != 4) || (g->epi_warps == 4 && f32)) {
+    bb_set_last_error_msg("bb_gemm_bf16: epi_warps must be 0, 2 or 4 (4 only with bf16 outputs)");
+    return BB_ERR_INVALID_ARG;
+  }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   // cuTensorMapEncodeTiled is a driver call and needs a context bound to the calling thread;
   // a thread that has only ever set its device (autograd worker threads) has none yet.
@@ -554,7 +686,9 @@ extern "C" int bb_gemm_bf16(const bb_gemm_desc* g, void* stream) {
   const bool pair = g->cta_pair > 0 ||
                     (g->cta_pair == 0 && g->tile_n == 0 && g->M > BM && g->N > 128 &&
                      (g->K >= 2048 || tiles_single >= 16LL * bb_num_sms()));
-  if (pair) return launch<256, true>(g, s);
+  // sixteen epilogue warps for the GeLU epilogues on short reductions (see the narrow variant)
+  const bool wide_epi = g->epi_warps == 4 || (g->epi_warps == 0 && (e == BB_EPI_BIAS_GELU || e == BB_EPI_MUL_DGELU) && g->K <= 2048);
+  if (pair) return wide_epi ? launch<256, true, 4>(g, s) : launch<256, true, 2>(g, s);
   int bn = g->tile_n;
   if (bn == 0) {
     // 256-wide tiles halve the A re-reads; use them when they still fill the machine
@@ -562,8 +696,8 @@ extern "C" int bb_gemm_bf16(const bb_gemm_desc* g, void* stream) {
     // the add-reduction epilogue can split K to fill the machine, so it always takes wide tiles
     bn = (g->N > 128 && (tiles256 >= bb_num_sms() || e == BB_EPI_ACCUM_F32)) ? 256 : 128;
   }
-  if (bn == 256) return launch<256, false>(g, s);
-  if (bn == 128) return launch<128, false>(g, s);
+  if (bn == 256) return wide_epi ? launch<256, false, 4>(g, s) : launch<256, false, 2>(g, s);
+  if (bn == 128) return wide_epi ? launch<128, false, 4>(g, s) : launch<128, false, 2>(g, s);
   bb_set_last_error_msg("bb_gemm_bf16: tile_n must be 0, 128 or 256");
   return BB_ERR_INVALID_ARG;
 }

@@ -32,6 +32,7 @@ class GemmDesc(ctypes.Structure):
         ("max_ctas", ctypes.c_int),
         ("split_k", ctypes.c_int),
         ("cta_pair", ctypes.c_int),
+        ("epi_warps", ctypes.c_int),
     ]
 
 
@@ -93,6 +94,7 @@ def _stream(raw=None):
 # Process-wide default for GemmDesc.cta_pair (0 = library heuristic, 1 = pairs, -1 = single CTAs);
 # BB_GEMM_CTA_PAIR in the environment sets it, for A/B measurements of the two kernels.
 GEMM_CTA_PAIR = int(os.environ.get("BB_GEMM_CTA_PAIR", "0"))
+GEMM_EPI_WARPS = int(os.environ.get("BB_GEMM_EPI_WARPS", "0"))      # same for GemmDesc.epi_warps (0, 2 or 4)
 
 
 # Default for GemmDesc.max_ctas; the engine sets it to -1 (one tile per CTA) while it issues
@@ -101,7 +103,7 @@ GEMM_MAX_CTAS = 0
 
 
 def gemm(a, b, out, *, a_mn=False, b_mn=False, epilogue=EPI_STORE, bias=None, out2=None, aux=None,
-         M=None, N=None, K=None, tile_n=0, max_ctas=0, split_k=0, cta_pair=0, stream=None):
+         M=None, N=None, K=None, tile_n=0, max_ctas=0, split_k=0, cta_pair=0, epi_warps=0, stream=None):
     """out[M,N] = op(a)[M,K] @ op(b)[N,K]^T with a fused epilogue; see bb_gemm_bf16.
 
     ``a`` is [M,K] (or [K,M] when ``a_mn``), ``b`` is [N,K] (or [K,N] when ``b_mn``); 2-D,
@@ -121,7 +123,7 @@ def gemm(a, b, out, *, a_mn=False, b_mn=False, epilogue=EPI_STORE, bias=None, ou
                  epilogue=epilogue, bias=None if bias is None else bias.data_ptr(),
                  D2=None if out2 is None else out2.data_ptr(), aux=None if aux is None else aux.data_ptr(),
                  ld_aux=aux.stride(0) if aux is not None else 0, tile_n=tile_n, max_ctas=max_ctas or GEMM_MAX_CTAS, split_k=split_k,
-                 cta_pair=cta_pair or GEMM_CTA_PAIR)
+                 cta_pair=cta_pair or GEMM_CTA_PAIR, epi_warps=epi_warps or GEMM_EPI_WARPS)
     global LAUNCHES
     LAUNCHES += 1
     if gemm_hook is not None:

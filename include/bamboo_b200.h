@@ -62,6 +62,7 @@ typedef struct bb_gemm_desc {
                                        < 0 = one tile per CTA (short CTAs for a low-priority stream) */
   int split_k;                      /* BB_EPI_ACCUM_F32 only: 0 = choose, else number of K splits */
   int cta_pair;                     /* 0 = choose, 1 = CTA pairs (cta_group::2, 256 x 256 tiles), -1 = single CTAs */
+  int epi_warps;                    /* epilogue warps per TMEM lane quarter: 0 = choose, 2, or 4 (bf16 outputs only) */
 } bb_gemm_desc;
 
 /* D[M,N] = op(A)[M,K] * op(B)[N,K]^T, bf16 operands, fp32 accumulation in tensor memory

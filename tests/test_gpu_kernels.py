@@ -60,14 +60,20 @@ def test_gemm_ragged_shapes(L, shape, cta_pair):
     aux = torch.randn(M, ldd, device="cuda").bfloat16()[:, :N]
     L.gemm(A, B, out[:, :N], epilogue=L.EPI_BIAS_RESIDUAL, bias=bias, aux=aux, cta_pair=cta_pair)
     close(out[:, :N], A.float() @ B.float().t() + bias.float() + aux.float())
+    out.fill_(7)
+    L.gemm(A, B, out[:, :N], epilogue=L.EPI_BIAS_RESIDUAL, bias=bias, aux=aux, cta_pair=cta_pair, epi_warps=4)
+    close(out[:, :N], A.float() @ B.float().t() + bias.float() + aux.float())
+    assert torch.all(out[:, N:] == 7)
     acc = torch.full((M, ldd), 7.0, device="cuda")
     L.gemm(A, B, acc[:, :N], epilogue=L.EPI_ACCUM_F32, cta_pair=cta_pair)
     close(acc[:, :N], A.float() @ B.float().t() + 7, 1e-3)
     assert torch.all(acc[:, N:] == 7)
 
 
+@pytest.mark.parametrize("epi_warps", [2, 4])
 @pytest.mark.parametrize("cta_pair", [-1, 1])
-def test_gemm_epilogues(L, cta_pair):
+def test_gemm_epilogues(L, cta_pair, epi_warps):
+    """Every fused epilogue, with 8 and with 16 epilogue warps (the latter bf16 outputs only)."""
     torch.manual_seed(2)
     M, N, K = 384, 768, 320
     A = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
@@ -77,14 +83,14 @@ def test_gemm_epilogues(L, cta_pair):
     ref = A.float() @ B.float().t()
     out = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
     out2 = torch.zeros_like(out)
-    L.gemm(A, B, out, epilogue=L.EPI_BIAS_GELU, bias=bias, out2=out2, cta_pair=cta_pair)
+    L.gemm(A, B, out, epilogue=L.EPI_BIAS_GELU, bias=bias, out2=out2, cta_pair=cta_pair, epi_warps=epi_warps)
     close(out2, ref + bias.float())
     close(out, gelu((ref + bias.float()).bfloat16().float()))
-    L.gemm(A, B, out, epilogue=L.EPI_BIAS_RESIDUAL, bias=bias, aux=aux, cta_pair=cta_pair)
+    L.gemm(A, B, out, epilogue=L.EPI_BIAS_RESIDUAL, bias=bias, aux=aux, cta_pair=cta_pair, epi_warps=epi_warps)
     close(out, ref + bias.float() + aux.float())
     x = aux.float().requires_grad_(True)
     gelu(x).sum().backward()
-    L.gemm(A, B, out, epilogue=L.EPI_MUL_DGELU, aux=aux, cta_pair=cta_pair)
+    L.gemm(A, B, out, epilogue=L.EPI_MUL_DGELU, aux=aux, cta_pair=cta_pair, epi_warps=epi_warps)
     close(out, ref * x.grad)
     acc = torch.randn(M, N, device="cuda")
     want = acc + ref
@@ -149,6 +155,8 @@ def test_gemm_rejects_bad_arguments(L):
         L.gemm(A, B, out)
     with pytest.raises(L.BambooNativeError):
         L.gemm(out, out, out, epilogue=L.EPI_BIAS)                 # bias missing
+    with pytest.raises(L.BambooNativeError):
+        L.gemm(out, out, torch.zeros(16, 16, device="cuda"), epilogue=L.EPI_STORE_F32, epi_warps=4)   # fp32 output
 
 
 @pytest.mark.parametrize("rows,h", [(512, 256), (8192, 1024), (300, 768), (1000, 4096)])
