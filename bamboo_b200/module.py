@@ -253,7 +253,9 @@ class PipelineModule(nn.Module):
         ckpt = self.activation_checkpoint_func
         if ckpt is None:
             from torch.utils.checkpoint import checkpoint as _ckpt
-            ckpt = lambda fn, *a: _ckpt(fn, *a, use_reentrant=True)  # noqa: E731
+            # non-reentrant: the first segment of stage 0 takes integer tokens (nothing that
+            # requires grad goes in), which the reentrant form cannot differentiate through
+            ckpt = lambda fn, *a: _ckpt(fn, *a, use_reentrant=False)  # noqa: E731
         x = forward_input
         for lo in range(0, len(funcs), k):
             hi = min(lo + k, len(funcs))

@@ -20,14 +20,14 @@ def _oracle_losses():
     return [ref.train_batch(step) for step in data], ref
 
 
-def _train(rank, world, store, stages, rc, eager, victim_step, victim_stage=None):
+def _train(rank, world, store, stages, rc, eager, victim_step, victim_stage=None, ckpt_interval=0):
     """Body of one rank.  ``victim_step``: the rank of ``victim_stage`` (default: the last stage)
     announces its preemption so that it is gone from step ``victim_step`` on (None = no failure)."""
     import cpu_layers
     from bamboo_b200 import api
     from bamboo_b200.module import PipelineModule
     model = PipelineModule(cpu_layers.ref_layer_specs(CFG, 0), num_stages=stages, loss_fn=cpu_layers.ref_loss(CFG),
-                           partition_method="uniform", device="cpu")
+                           partition_method="uniform", device="cpu", activation_checkpoint_interval=ckpt_interval)
     config = {"train_micro_batch_size_per_gpu": MB, "gradient_accumulation_steps": GAS,
               "optimizer": {"type": "Adam", "params": {"lr": LR}}, "bamboo_b200": {"p2p_timeout_s": 20}}
     engine, *_ = api.initialize(model=model, config=config, redundancy_level=rc, eager_recovery=eager,
@@ -51,6 +51,16 @@ def test_single_stage_matches_oracle():
     assert got["losses"] == pytest.approx(want, rel=1e-5)
     total = sum(float(p.detach().double().sum()) for p in ref.P.values())
     assert got["checksum"][0] == pytest.approx(total, rel=1e-6)
+
+
+@pytest.mark.parametrize("interval", [1, 2])
+def test_activation_checkpointing_matches_oracle(interval):
+    """Recomputing every `interval` layers in the backward pass changes memory, not numbers
+    (``PipelineModule.forward``, reference ``deepspeed/runtime/pipe/module.py:551-573``)."""
+    want, _ = _oracle_losses()
+    os.environ["BAMBOO_QUIET"] = "1"
+    got = _train(0, 1, None, 1, 0, False, None, ckpt_interval=interval)
+    assert got["losses"] == pytest.approx(want, rel=1e-5)
 
 
 @pytest.mark.parametrize("rc,eager", [(0, False), (1, False), (1, True)])

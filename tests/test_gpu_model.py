@@ -14,14 +14,14 @@ pytestmark = pytest.mark.gpu
 TOL = 2e-2
 
 
-def build_engine(cfg, mb, gas, lr, seed=0):
+def build_engine(cfg, mb, gas, lr, seed=0, ckpt_interval=0):
     from bamboo_b200 import api, models
     from bamboo_b200.module import PipelineModule
     os.environ["BAMBOO_QUIET"] = "1"
     tc = models.TransformerConfig(layers=cfg.layers, hidden=cfg.hidden, heads=cfg.heads, ffn=cfg.ffn, seq=cfg.seq,
                                   vocab=cfg.vocab, causal=cfg.causal, mlm=cfg.mlm)
     model = PipelineModule(models.transformer_layer_specs(tc, seed), num_stages=1, loss_fn=models.transformer_loss(tc),
-                           partition_method="uniform")
+                           partition_method="uniform", activation_checkpoint_interval=ckpt_interval)
     config = {"train_micro_batch_size_per_gpu": mb, "gradient_accumulation_steps": gas, "bf16": {"enabled": True},
               "optimizer": {"type": "Adam", "params": {"lr": lr}}}
     engine, *_ = api.initialize(model=model, config=config)
@@ -88,6 +88,20 @@ def test_bidirectional_ragged_vocab_matches_oracle():
     ref = gpt_ref.RefTrainer(cfg, seed=3, lr=lr, micro_batches=gas)
     engine = build_engine(cfg, mb, gas, lr, seed=3)
     for batches in gpt_ref.synthetic_batches(cfg, mb, gas, 2, seed=5):
+        want = ref.train_batch(batches)
+        got = float(engine.train_batch(data_iter=iter(batches)))
+        assert got == pytest.approx(want, rel=TOL)
+        compare_grads(engine, ref, cfg)
+
+
+def test_activation_checkpointing_on_gpu_matches_oracle():
+    """Every second layer boundary is a checkpoint: the CUDA layers run their forward twice (the
+    cross-entropy gradient, written in place over the logits, then lands in the recomputed copy)."""
+    cfg = gpt_ref.RefConfig(layers=4, hidden=256, heads=4, ffn=1024, seq=128, vocab=1024)
+    mb, gas, lr = 4, 2, 1e-3
+    ref = gpt_ref.RefTrainer(cfg, seed=0, lr=lr, micro_batches=gas)
+    engine = build_engine(cfg, mb, gas, lr, ckpt_interval=2)
+    for batches in gpt_ref.synthetic_batches(cfg, mb, gas, 2, seed=1):
         want = ref.train_batch(batches)
         got = float(engine.train_batch(data_iter=iter(batches)))
         assert got == pytest.approx(want, rel=TOL)
