@@ -177,6 +177,98 @@ class _BlockFn(torch.autograd.Function):
         return (dx.view(ctx.shape), None) + (None,) * 12
 
 
+class _AttnHalfFn(torch.autograd.Function):
+    """First half of a pre-LN block as a layer of its own: x + proj(attention(LN1(x)))."""
+
+    @staticmethod
+    def forward(ctx, x, blk, *params):
+        _require_cuda(x, "AttentionHalf")
+        shape = x.shape
+        h = shape[-1]
+        x2 = x.reshape(-1, h)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        T = x2.shape[0]
+        B, S = (shape[0], shape[1]) if x.dim() == 3 else (1, T)
+        H, D = blk.heads, h // blk.heads
+        dev, bf, f32 = x.device, torch.bfloat16, torch.float32
+        mean1, rstd1 = torch.empty(T, dtype=f32, device=dev), torch.empty(T, dtype=f32, device=dev)
+        h1 = torch.empty(T, h, dtype=bf, device=dev)
+        L.layernorm_fwd(x2, blk.ln1_w, blk.ln1_b, h1, mean1, rstd1, blk.eps)
+        qkv = torch.empty(T, 3 * h, dtype=bf, device=dev)
+        L.gemm(h1, blk.qkv_w, qkv, epilogue=L.EPI_BIAS, bias=blk.qkv_b)
+        att = torch.empty(T, h, dtype=bf, device=dev)
+        lse = torch.empty(B, H, S, dtype=f32, device=dev)
+        L.attention_fwd(qkv, att, lse, B, H, S, D, blk.causal)
+        x1 = torch.empty(T, h, dtype=bf, device=dev)
+        L.gemm(att, blk.proj_w, x1, epilogue=L.EPI_BIAS_RESIDUAL, bias=blk.proj_b, aux=x2)
+        ctx.blk, ctx.dims, ctx.shape = blk, (B, S, H, D), shape
+        ctx.save_for_backward(x2, h1, qkv, att, lse, mean1, rstd1)
+        return x1.view(shape)
+
+    @staticmethod
+    def backward(ctx, dout):
+        blk = ctx.blk
+        B, S, H, D = ctx.dims
+        x2, h1, qkv, att, lse, mean1, rstd1 = ctx.saved_tensors
+        h = x2.shape[1]
+        dx1 = dout.reshape(-1, h)
+        if not dx1.is_contiguous():
+            dx1 = dx1.contiguous()
+        wg = []
+        datt = _linear_backward(dx1, att, blk.proj_w, blk.proj_b, defer=wg)
+        dqkv = torch.empty_like(qkv)
+        L.attention_bwd(qkv, att, datt, lse, dqkv, B, H, S, D, blk.causal)
+        dh1 = _linear_backward(dqkv, h1, blk.qkv_w, blk.qkv_b, defer=wg)
+        flush_wgrads(wg)
+        dx = torch.empty(dx1.shape[0], h, dtype=torch.bfloat16, device=x2.device)
+        L.layernorm_bwd(dh1, x2, blk.ln1_w, mean1, rstd1, dx1, dx, _main_grad(blk.ln1_w), _main_grad(blk.ln1_b))
+        return (dx.view(ctx.shape), None) + (None,) * 6
+
+
+class _MLPHalfFn(torch.autograd.Function):
+    """Second half of a pre-LN block as a layer of its own: x + fc2(gelu(fc1(LN2(x))))."""
+
+    @staticmethod
+    def forward(ctx, x, blk, *params):
+        _require_cuda(x, "MLPHalf")
+        shape = x.shape
+        h = shape[-1]
+        x1 = x.reshape(-1, h)
+        if not x1.is_contiguous():
+            x1 = x1.contiguous()
+        T = x1.shape[0]
+        dev, bf, f32 = x.device, torch.bfloat16, torch.float32
+        mean2, rstd2 = torch.empty(T, dtype=f32, device=dev), torch.empty(T, dtype=f32, device=dev)
+        h2 = torch.empty(T, h, dtype=bf, device=dev)
+        L.layernorm_fwd(x1, blk.ln2_w, blk.ln2_b, h2, mean2, rstd2, blk.eps)
+        ffn = blk.fc1_w.shape[0]
+        pre = torch.empty(T, ffn, dtype=bf, device=dev)
+        act = torch.empty(T, ffn, dtype=bf, device=dev)
+        L.gemm(h2, blk.fc1_w, act, epilogue=L.EPI_BIAS_GELU, bias=blk.fc1_b, out2=pre)
+        out = torch.empty(T, h, dtype=bf, device=dev)
+        L.gemm(act, blk.fc2_w, out, epilogue=L.EPI_BIAS_RESIDUAL, bias=blk.fc2_b, aux=x1)
+        ctx.blk, ctx.shape = blk, shape
+        ctx.save_for_backward(x1, h2, pre, act, mean2, rstd2)
+        return out.view(shape)
+
+    @staticmethod
+    def backward(ctx, dout):
+        blk = ctx.blk
+        x1, h2, pre, act, mean2, rstd2 = ctx.saved_tensors
+        h = x1.shape[1]
+        d2 = dout.reshape(-1, h)
+        if not d2.is_contiguous():
+            d2 = d2.contiguous()
+        wg = []
+        dpre = _linear_backward(d2, act, blk.fc2_w, blk.fc2_b, dx_epilogue=L.EPI_MUL_DGELU, aux=pre, defer=wg)
+        dh2 = _linear_backward(dpre, h2, blk.fc1_w, blk.fc1_b, defer=wg)
+        flush_wgrads(wg)
+        dx1 = torch.empty(d2.shape[0], h, dtype=torch.bfloat16, device=x1.device)
+        L.layernorm_bwd(dh2, x1, blk.ln2_w, mean2, rstd2, d2, dx1, _main_grad(blk.ln2_w), _main_grad(blk.ln2_b))
+        return (dx1.view(ctx.shape), None) + (None,) * 6
+
+
 class _EmbeddingFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, tokens, mod, wte, wpe):
@@ -359,6 +451,40 @@ class TransformerBlock(nn.Module):
     def forward(self, x):
         return _BlockFn.apply(x, self, self.ln1_w, self.ln1_b, self.qkv_w, self.qkv_b, self.proj_w, self.proj_b,
                               self.ln2_w, self.ln2_b, self.fc1_w, self.fc1_b, self.fc2_w, self.fc2_b)
+
+
+class AttentionHalf(nn.Module):
+    """The attention half of a ``TransformerBlock`` as its own pipeline layer (finer stage
+    boundaries); with ``MLPHalf(..., seed=same)`` after it the pair equals the fused block,
+    weights included: both draw from ``Generator(seed)`` in the block's order qkv, proj, fc1, fc2."""
+
+    def __init__(self, hidden, heads, ffn, causal=True, eps=1e-5, seed=0):
+        super().__init__()
+        assert hidden % heads == 0
+        g = torch.Generator().manual_seed(seed)
+        self.heads, self.causal, self.eps = heads, causal, eps
+        self.ln1_w = nn.Parameter(torch.ones(hidden)); self.ln1_b = nn.Parameter(torch.zeros(hidden))
+        self.qkv_w = nn.Parameter(_normal((3 * hidden, hidden), g)); self.qkv_b = nn.Parameter(torch.zeros(3 * hidden))
+        self.proj_w = nn.Parameter(_normal((hidden, hidden), g)); self.proj_b = nn.Parameter(torch.zeros(hidden))
+
+    def forward(self, x):
+        return _AttnHalfFn.apply(x, self, self.ln1_w, self.ln1_b, self.qkv_w, self.qkv_b, self.proj_w, self.proj_b)
+
+
+class MLPHalf(nn.Module):
+    """The MLP half of a ``TransformerBlock`` as its own pipeline layer; see ``AttentionHalf``."""
+
+    def __init__(self, hidden, heads, ffn, causal=True, eps=1e-5, seed=0):
+        super().__init__()
+        g = torch.Generator().manual_seed(seed)
+        _normal((3 * hidden, hidden), g); _normal((hidden, hidden), g)      # the attention half's draws
+        self.eps = eps
+        self.ln2_w = nn.Parameter(torch.ones(hidden)); self.ln2_b = nn.Parameter(torch.zeros(hidden))
+        self.fc1_w = nn.Parameter(_normal((ffn, hidden), g)); self.fc1_b = nn.Parameter(torch.zeros(ffn))
+        self.fc2_w = nn.Parameter(_normal((hidden, ffn), g)); self.fc2_b = nn.Parameter(torch.zeros(hidden))
+
+    def forward(self, x):
+        return _MLPHalfFn.apply(x, self, self.ln2_w, self.ln2_b, self.fc1_w, self.fc1_b, self.fc2_w, self.fc2_b)
 
 
 class LayerNorm(nn.Module):

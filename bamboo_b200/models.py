@@ -21,7 +21,8 @@ from dataclasses import dataclass
 
 import torch
 
-from .layers import CrossEntropyLoss, LayerNorm, Linear, MLMTransform, TokenEmbedding, TransformerBlock
+from .layers import (AttentionHalf, CrossEntropyLoss, LayerNorm, Linear, MLMTransform, MLPHalf, TokenEmbedding,
+                     TransformerBlock)
 from .module import LayerSpec
 
 
@@ -56,11 +57,17 @@ BERT_TOY = TransformerConfig(layers=2, hidden=256, heads=4, ffn=1024, seq=128, v
 GPT_6_7B = TransformerConfig(layers=32, hidden=4096, heads=32, ffn=16384, seq=2048, vocab=50257)
 
 
-def transformer_layer_specs(cfg: TransformerConfig, seed: int = 0):
+def transformer_layer_specs(cfg: TransformerConfig, seed: int = 0, split_blocks: bool = False):
+    """``split_blocks``: every block becomes two pipeline layers (attention half, MLP half) with
+    the same weights and arithmetic, so that stage boundaries can fall inside a block."""
     base = seed * 1000
     specs = [LayerSpec(TokenEmbedding, cfg.vocab, cfg.hidden, cfg.seq, seed=base)]
     for i in range(cfg.layers):
-        specs.append(LayerSpec(TransformerBlock, cfg.hidden, cfg.heads, cfg.ffn, causal=cfg.causal, seed=base + 1 + i))
+        if split_blocks:
+            specs.append(LayerSpec(AttentionHalf, cfg.hidden, cfg.heads, cfg.ffn, causal=cfg.causal, seed=base + 1 + i))
+            specs.append(LayerSpec(MLPHalf, cfg.hidden, cfg.heads, cfg.ffn, causal=cfg.causal, seed=base + 1 + i))
+        else:
+            specs.append(LayerSpec(TransformerBlock, cfg.hidden, cfg.heads, cfg.ffn, causal=cfg.causal, seed=base + 1 + i))
     specs.append(LayerSpec(LayerNorm, cfg.hidden))
     nxt = base + cfg.layers + 2
     if cfg.mlm:

@@ -39,6 +39,8 @@ def parse():
     ap.add_argument("--failover", action="store_true",
                     help="after the timed region: the last stage announces its preemption and leaves; reports the "
                          "pause of the first step after it and the post-failover throughput")
+    ap.add_argument("--whole-blocks", action="store_true",
+                    help="multi-stage runs: keep every transformer block one pipeline layer (coarser stage boundaries)")
     ap.add_argument("--micro-batches", type=int, default=0,
                     help="profiling only: fewer micro-batches per step than the benchmark configuration")
     return ap.parse_args()
@@ -236,9 +238,14 @@ def main():
     h = cfg.hidden
     blk = 24.0 * h * h + 4.0 * cfg.seq * h
     head_cost = 0.65 * 2.0 * h * cfg.vocab / blk
-    costs = [0.0] + [1.0] * cfg.layers + [0.0] + ([0.65 * 2.0 * h * h / blk] if cfg.mlm else []) + [head_cost]
+    # multi-stage runs list every block as two layers (attention half 0.53, MLP half 0.47 of a
+    # block's time), so that stage boundaries can fall inside a block: with 24 blocks and a head
+    # worth 2.3 blocks, whole blocks leave 8 stages 22 % above the mean load
+    split = world > 1 and not args.whole_blocks
+    blocks = [0.53, 0.47] * cfg.layers if split else [1.0] * cfg.layers
+    costs = [0.0] + blocks + [0.0] + ([0.65 * 2.0 * h * h / blk] if cfg.mlm else []) + [head_cost]
     parts = contiguous_partition(costs, world)
-    model = PipelineModule(models.transformer_layer_specs(cfg, 0), num_stages=world, loss_fn=models.transformer_loss(cfg),
+    model = PipelineModule(models.transformer_layer_specs(cfg, 0, split_blocks=split), num_stages=world, loss_fn=models.transformer_loss(cfg),
                            partition_method="custom", custom_partitions=parts)
     engine, *_ = api.initialize(model=model, config={
         "train_micro_batch_size_per_gpu": MICRO_BATCH, "gradient_accumulation_steps": MICRO_BATCHES,

@@ -14,13 +14,13 @@ pytestmark = pytest.mark.gpu
 TOL = 2e-2
 
 
-def build_engine(cfg, mb, gas, lr, seed=0, ckpt_interval=0):
+def build_engine(cfg, mb, gas, lr, seed=0, ckpt_interval=0, split_blocks=False):
     from bamboo_b200 import api, models
     from bamboo_b200.module import PipelineModule
     os.environ["BAMBOO_QUIET"] = "1"
     tc = models.TransformerConfig(layers=cfg.layers, hidden=cfg.hidden, heads=cfg.heads, ffn=cfg.ffn, seq=cfg.seq,
                                   vocab=cfg.vocab, causal=cfg.causal, mlm=cfg.mlm)
-    model = PipelineModule(models.transformer_layer_specs(tc, seed), num_stages=1, loss_fn=models.transformer_loss(tc),
+    model = PipelineModule(models.transformer_layer_specs(tc, seed, split_blocks=split_blocks), num_stages=1, loss_fn=models.transformer_loss(tc),
                            partition_method="uniform", activation_checkpoint_interval=ckpt_interval)
     config = {"train_micro_batch_size_per_gpu": mb, "gradient_accumulation_steps": gas, "bf16": {"enabled": True},
               "optimizer": {"type": "Adam", "params": {"lr": lr}}}
@@ -101,6 +101,20 @@ def test_activation_checkpointing_on_gpu_matches_oracle():
     mb, gas, lr = 4, 2, 1e-3
     ref = gpt_ref.RefTrainer(cfg, seed=0, lr=lr, micro_batches=gas)
     engine = build_engine(cfg, mb, gas, lr, ckpt_interval=2)
+    for batches in gpt_ref.synthetic_batches(cfg, mb, gas, 2, seed=1):
+        want = ref.train_batch(batches)
+        got = float(engine.train_batch(data_iter=iter(batches)))
+        assert got == pytest.approx(want, rel=TOL)
+        compare_grads(engine, ref, cfg)
+
+
+def test_split_blocks_equal_fused_blocks():
+    """Blocks as two pipeline layers each (attention half, MLP half): same weights, same
+    arithmetic, same parameter order - loss and gradients match the oracle like the fused block."""
+    cfg = gpt_ref.RefConfig(layers=3, hidden=256, heads=4, ffn=1024, seq=128, vocab=1024)
+    mb, gas, lr = 4, 2, 1e-3
+    ref = gpt_ref.RefTrainer(cfg, seed=4, lr=lr, micro_batches=gas)
+    engine = build_engine(cfg, mb, gas, lr, seed=4, split_blocks=True)
     for batches in gpt_ref.synthetic_batches(cfg, mb, gas, 2, seed=1):
         want = ref.train_batch(batches)
         got = float(engine.train_batch(data_iter=iter(batches)))
