@@ -137,7 +137,9 @@ def gen_topology(T, R):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("BAMBOO_REFERENCE")
+    if not ref:
+        sys.exit("usage: gen_golden.py <path of the reference checkout>  (or set BAMBOO_REFERENCE)")
     _ref_shims.install(ref)
     from deepspeed.runtime.pipe import schedule as S, topology as T, redundancy as R
     from deepspeed.runtime import utils as U
