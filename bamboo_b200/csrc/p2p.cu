@@ -47,7 +47,9 @@ wait_copy_kernel(const uint4* __restrict__ slot, uint4* __restrict__ dst, long l
     unsigned int backoff = 32;
     for (;;) {
       const unsigned long long v = ld_acquire_sys_u64(flag);
-      if (v == seq) { ok = 1; break; }
+      // a payload slot must hold exactly this message; a liveness ping (no payload) is a counter
+      // that the sender may already have advanced past the one awaited
+      if (v == seq || (n16 == 0 && v > seq)) { ok = 1; break; }
       if (bb::globaltimer_ns() - t0 > timeout_ns) {
         atomicCAS(status, 0, v > seq ? BB_ERR_INVALID_ARG : BB_STATUS_PEER_TIMEOUT);
         __threadfence_system();
