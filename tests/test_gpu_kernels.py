@@ -315,6 +315,33 @@ def test_attention_backward_checksums_at_full_size(L):
     assert L.read_status() == 0
 
 
+def test_ping_counter_may_run_ahead_of_the_receiver(L):
+    """A liveness ping carries no payload: its flag is a counter.  A receiver that waits for ping
+    1 after the sender already signalled ping 3 has its answer (lazy redundancy on more than two
+    stages does exactly that); a payload slot whose flag moved on is an error, and a ping that
+    never comes ends the bounded wait with the peer-timeout status.  All on this GPU's own memory."""
+    import ctypes
+    lib = L.load()
+    flag = torch.zeros(1, dtype=torch.int64, device="cuda")
+    stream = L._stream()
+    fp = ctypes.c_void_p(flag.data_ptr())
+    assert lib.bb_p2p_signal(fp, ctypes.c_ulonglong(3), stream) == 0
+    assert lib.bb_p2p_wait_copy(None, None, ctypes.c_longlong(0), fp, ctypes.c_ulonglong(1),
+                                ctypes.c_ulonglong(200_000_000), None, stream) == 0
+    torch.cuda.synchronize()
+    assert L.read_status() == 0
+    src = torch.ones(64, device="cuda"); dst = torch.zeros(64, device="cuda")
+    assert lib.bb_p2p_wait_copy(ctypes.c_void_p(src.data_ptr()), ctypes.c_void_p(dst.data_ptr()), ctypes.c_longlong(256), fp,
+                                ctypes.c_ulonglong(1), ctypes.c_ulonglong(200_000_000), None, stream) == 0
+    torch.cuda.synchronize()
+    assert L.read_status() == -1 and float(dst.sum()) == 0          # overwritten slot: reported, nothing copied
+    assert lib.bb_p2p_wait_copy(None, None, ctypes.c_longlong(0), fp, ctypes.c_ulonglong(9),
+                                ctypes.c_ulonglong(50_000_000), None, stream) == 0
+    torch.cuda.synchronize()
+    assert L.read_status() == L.STATUS_PEER_TIMEOUT                   # the wait ran out, the context lives on
+    assert L.read_status() == 0
+
+
 def test_status_word_is_clean(L):
     torch.cuda.synchronize()
     assert L.read_status() == 0
