@@ -439,8 +439,7 @@ template <int D> int dq_smem() { return 2 * BLK_M * D * 2 + 4 * BLK_N * D * 2; }
 
 template <int D>
 int launch_fwd(const AttnParams& p, cudaStream_t s) {
-  static bool attr = false;
-  if (!attr) { BB_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<D>())); attr = true; }
+  BB_ONCE_PER_DEVICE(BB_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<D>())));
   dim3 grid((p.S + BLK_M - 1) / BLK_M, p.H, p.B);
   attn_fwd_kernel<D><<<grid, THREADS, fwd_smem<D>(), s>>>(p);
   BB_CUDA_CHECK(cudaGetLastError());
@@ -449,12 +448,10 @@ int launch_fwd(const AttnParams& p, cudaStream_t s) {
 
 template <int D>
 int launch_bwd(const AttnParams& p, cudaStream_t s) {
-  static bool attr = false;
-  if (!attr) {
+  BB_ONCE_PER_DEVICE({
     BB_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dkv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv_smem<D>()));
     BB_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, dq_smem<D>()));
-    attr = true;
-  }
+  });
   const long long units = (long long)p.B * p.S * p.H;
   long long dgrid = (units + 7) / 8, cap = (long long)bb_num_sms() * 8;
   attn_delta_kernel<D><<<(int)(dgrid < cap ? dgrid : cap), 256, 0, s>>>(p);

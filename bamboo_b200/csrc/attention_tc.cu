@@ -805,8 +805,7 @@ int bb_attention_tc_fwd(const void* qkv_q, void* out, float* lse, int B, int H, 
   TcParams p = {};
   p.out = (__nv_bfloat16*)out; p.lse = lse; p.stride_o = stride_o; p.B = B; p.H = H; p.S = S; p.hidden = H * HD;
   p.causal = causal; p.scale = scale; p.status = bb_device_status_word();
-  static bool attr = false;
-  if (!attr) { if (int rc = set_smem(attn_tc_fwd2_kernel, FWD2_SMEM)) return rc; attr = true; }
+  BB_ONCE_PER_DEVICE({ if (int rc = set_smem(attn_tc_fwd2_kernel, FWD2_SMEM)) return rc; });
   dim3 grid((S + 2 * TQ - 1) / (2 * TQ), H, B);
   attn_tc_fwd2_kernel<<<grid, FWD2_THREADS, FWD2_SMEM, stream>>>(tm_q, tm_kv, p);
   BB_CUDA_CHECK(cudaGetLastError());
@@ -828,11 +827,7 @@ int bb_attention_tc_bwd(const void* qkv_q, const void* out, const void* d_out, c
   CUtensorMap tm_qkv64, tm_do64;
   if (int rc = bbhost::encode_2d(&tm_qkv64, qkv_q, T, 3LL * H * HD, stride_qkv, HD, SUB)) return rc;
   if (int rc = bbhost::encode_2d(&tm_do64, d_out, T, (long long)H * HD, stride_o, HD, SUB)) return rc;
-  static bool attr = false;
-  if (!attr) {
-    if (int rc = set_smem(attn_tc_bwd2_kernel, BWD2_SMEM)) return rc;
-    attr = true;
-  }
+  BB_ONCE_PER_DEVICE({ if (int rc = set_smem(attn_tc_bwd2_kernel, BWD2_SMEM)) return rc; });
   const long long chunks = T * H * 8;
   long long dgrid = (chunks + 511) / 512, cap = (long long)bb_num_sms() * 8;
   attn_tc_delta_kernel<<<(int)(dgrid < cap ? dgrid : cap), 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out, p);

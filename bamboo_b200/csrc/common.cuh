@@ -27,6 +27,21 @@ void bb_set_last_error_msg(const char* msg);
 // Device word that kernels write when a bounded wait expires (0 = healthy).
 int* bb_device_status_word();
 int bb_num_sms();
+// Index of the current device, or -1 when it cannot be read or is beyond the per-device tables.
+int bb_current_device();
+
+// Function attributes (the dynamic shared-memory limit) are per device: `body` runs the first
+// time the enclosing call site is reached on each device of the process.  `body` may return
+// from the enclosing function on error; the device is then not marked as done.
+#define BB_ONCE_PER_DEVICE(body)                          \
+  do {                                                    \
+    static unsigned char _bb_done[64];                    \
+    const int _bb_dev = bb_current_device();              \
+    if (_bb_dev < 0 || !_bb_done[_bb_dev]) {              \
+      body;                                               \
+      if (_bb_dev >= 0) _bb_done[_bb_dev] = 1;            \
+    }                                                     \
+  } while (0)
 
 namespace bb {
 

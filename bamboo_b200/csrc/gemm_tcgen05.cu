@@ -620,11 +620,7 @@ int launch(const bb_gemm_desc* g, cudaStream_t stream) {
   if (ksplit < 1) ksplit = 1;
   p.kb_per_split = (total_kb + ksplit - 1) / ksplit;
   p.ksplit = (total_kb + p.kb_per_split - 1) / p.kb_per_split;   // no empty splits
-  static bool attr_set = false;
-  if (!attr_set) {
-    BB_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, PAIR, EW>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-    attr_set = true;
-  }
+  BB_ONCE_PER_DEVICE(BB_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, PAIR, EW>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES)));
   const int tiles = mn_tiles * p.ksplit;
   int workers = workers_max;
   if (g->max_ctas > 0 && g->max_ctas / (PAIR ? 2 : 1) < workers) workers = g->max_ctas / (PAIR ? 2 : 1);

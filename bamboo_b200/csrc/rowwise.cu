@@ -464,13 +464,11 @@ int ln_bwd_main(const void* dy, const void* x, const void* gamma, const float* m
   if (ln_bwd_cols_ok(h)) {
     const int slots = ln_bwd_cols_slots(h), tpr = h / 8;
     const size_t sm_bytes = ((size_t)2 * slots * (tpr / 32) * 2 * LNB_R + (size_t)slots * 2 * h) * sizeof(float);
-    static bool attr_cols = false;
-    if (!attr_cols) {
+    BB_ONCE_PER_DEVICE({
       BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_cols_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
       BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_cols_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
       BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_cols_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
-      attr_cols = true;
-    }
+    });
     const int threads = slots * tpr;
 #define BB_LNC_ARGS (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, mean, rstd, \
                     (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, ws, rows, h, slots
@@ -482,13 +480,11 @@ int ln_bwd_main(const void* dy, const void* x, const void* gamma, const float* m
     return BB_OK;
   }
   const size_t smem = (size_t)warps * 2 * h * sizeof(float);
-  static bool attr = false;
-  if (!attr) {
+  BB_ONCE_PER_DEVICE({
     BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_reg_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
     BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_reg_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
-    attr = true;
-  }
+  });
 #define BB_LN_ARGS (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, mean, rstd, \
                    (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, ws, rows
   if (h == 256) layernorm_bwd_reg_kernel<1><<<grid, warps * 32, smem, s>>>(BB_LN_ARGS);
@@ -540,8 +536,12 @@ static __device__ __align__(256) float g_ln_static_scratch[LN_STATIC_SCRATCH_FLO
 // is only a handle, so the address is looked up (once per device, with that device current).
 float* ln_static_scratch_ptr() {
   static float* ptr[64] = {nullptr};
-  int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  const int dev = bb_current_device();
+  if (dev < 0) {
+    bb_set_last_error_msg("bb_layernorm_bwd_static: the current device cannot be read or its index is 64 or more "
+                          "(the per-device address table holds 64 entries)");
+    return nullptr;
+  }
   if (!ptr[dev]) {
     void* p = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&p, g_ln_static_scratch);

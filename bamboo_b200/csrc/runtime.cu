@@ -30,6 +30,12 @@ int* bb_device_status_word() {
   return ptr[dev];
 }
 
+int bb_current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  return dev;
+}
+
 int bb_num_sms() {
   static int sms[64] = {0};
   int dev = 0;

@@ -79,6 +79,9 @@ class LocalStore:
     def get(self, key):
         return self._d[key]
 
+    def check(self, keys):
+        return all(k in self._d for k in keys)
+
 
 class LocalRendezvous:
     """Stand-in for the etcd rendezvous handler when a job is launched without the elastic
@@ -168,7 +171,6 @@ class PipelineEngine:
                 store = None
         self.global_store = store or LocalStore()
         self.global_store.set(str(self.global_rank), "0")
-        self.global_store.set(f"fail-step-{self.global_rank}", "[]")
         if isinstance(self.global_store, LocalStore) or self.global_rank == 0:
             self.global_store.set("failures", "{}")
         self.fail_lock = self.rdzv_handler.create_lock("fail-lock")
@@ -290,6 +292,9 @@ class PipelineEngine:
         self.state_buffers: Dict[int, ParamArena] = {}
         # who holds the shadow copy of this rank's stage / who owns the stages shadowed here
         self._shadow_holder_rank = self._stage_rank(self.r_user_stage_ids[0]) if self.r_user_stage_ids else None
+        # False once a state transfer into a shadow copy failed: its weights and moments may then
+        # belong to different steps, and a promotion from it would leave the optimisation trajectory
+        self._shadow_valid: Dict[int, bool] = {}
         self._shadow_source_rank = {sid: self._stage_rank(sid) for sid in self.r_stage_ids}
         if self.redundancy_level > 0:
             for sid in self.r_stage_ids:
@@ -419,6 +424,9 @@ class PipelineEngine:
         nxt = self.next_stage
         if nxt not in self.param_buffers or nxt not in self.state_buffers:
             raise RuntimeError("Doesn't have param or state to recover")
+        if not self._shadow_valid.get(nxt, True):
+            raise RuntimeError(f"the shadow copy of stage {nxt} missed a state transfer (its owner stopped answering "
+                               "in the middle of one) and cannot be promoted; restart from a checkpoint")
         t0 = time.time()
         if self.rc_stream is not None:
             # redundant forwards and the shadow's working-copy refresh are ordered on the RC stream
@@ -555,8 +563,10 @@ class PipelineEngine:
             exc = NextStageException(str(exc))
         if isinstance(exc, NextStageException):
             victim = self.next_stage
+            # the other rank that talks to the victim: the owner of the stage after it
+            other = self._stage_rank(self._inc(victim)) if victim != self.num_stages - 1 else None
             victim_rank = self._promote_next_stage()
-            failed_step = self._agree_failed_step(victim_rank, step_idx, wait_for_two=(victim != self.num_stages - 1))
+            failed_step = self._agree_failed_step(victim_rank, step_idx, other)
             self._sched_layers.append(("next", dict(stage_id=victim, failed_step=failed_step, curr_step=step_idx)))
         elif isinstance(exc, PrevStageException):
             victim = self.prev_stage
@@ -564,7 +574,8 @@ class PipelineEngine:
             prev_coord = self.grid.topology().get_coord(prev_rank)
             fallback_rank = self.grid.stage_to_global(self._dec(victim))
             self.grid.topology().modify_mapping(rank=fallback_rank, **prev_coord._asdict())
-            failed_step = self._agree_failed_step(prev_rank, step_idx, wait_for_two=(victim != 0))
+            # the other rank that talks to the victim: the owner of the stage before it
+            failed_step = self._agree_failed_step(prev_rank, step_idx, fallback_rank if victim != 0 else None)
             self._sched_layers.append(("prev", dict(stage_id=victim, failed_step=failed_step, curr_step=step_idx)))
             self._forget_rank(prev_rank)
         elif isinstance(exc, AllReduceException):
@@ -583,23 +594,22 @@ class PipelineEngine:
         else:
             raise Exception(exc)
 
-    def _agree_failed_step(self, victim_rank, my_step, wait_for_two):
-        key = f"fail-step-{victim_rank}"
-        self.fail_lock.acquire(blocking=True, lock_ttl=10)
-        try:
-            try:
-                seen = json.loads(_decode(self.global_store.get(key)))
-            except Exception:
-                seen = []
-            seen.append(my_step)
-            self.global_store.set(key, json.dumps(seen))
-        finally:
-            self.fail_lock.release()
+    def _agree_failed_step(self, victim_rank, my_step, other_rank):
+        """Both neighbours of a dead middle stage notice it, possibly at different schedule steps;
+        the redo window starts at the earlier one.  Every detector publishes its own step under a
+        key of its own (no shared read-modify-write, so concurrent detections cannot lose an
+        entry) and waits - bounded - for the other detector's key.  The result always includes
+        this rank's own step."""
+        self.global_store.set(f"fail-step-{victim_rank}-{self.global_rank}", str(int(my_step)))
+        if other_rank is None or other_rank == self.global_rank:
+            return my_step
+        key = f"fail-step-{victim_rank}-{other_rank}"
         deadline = time.time() + self._config.p2p_timeout_s
-        while wait_for_two and len(seen) < 2 and time.time() < deadline:
+        while time.time() < deadline:
+            if self.global_store.check([key]):
+                return min(my_step, int(_decode(self.global_store.get(key))))
             time.sleep(0.01)
-            seen = json.loads(_decode(self.global_store.get(key)))
-        return min(seen)
+        return my_step
 
     def _aggregate_total_loss(self):
         if self.is_last_stage() and self.total_loss is not None:
@@ -865,7 +875,16 @@ class PipelineEngine:
             self._lp_refreshed = None
         try:
             self.transport.exchange_state(send_to, tensors_out, recv_from, tensors_in, self.global_steps)
-        except PeerTimeout:
+        except PeerTimeout as e:
+            # Transports deliver the three pieces all-or-nothing, so after a failed transfer the
+            # shadow is whole but one step old; it is marked so that a later promotion is refused
+            # rather than silently continued from stale state.  A failed send needs nothing here:
+            # the holder of that shadow records the same on its side.
+            if recv_from is not None and e.peer == recv_from:
+                for sid in self.r_stage_ids:
+                    if sid in self.param_buffers:
+                        self._shadow_valid[sid] = False
+                self.log(f"shadow state of stage(s) {self.r_stage_ids} not refreshed: {e}")
             return
         if recv_from is not None:
             for sid in self.r_stage_ids:

@@ -141,16 +141,27 @@ _I = ctypes.c_int
 _workspaces = {}
 
 
-def workspace(nbytes, tag="default"):
+def workspace(nbytes, tag="default", stream=None):
     """A per-device scratch buffer that only ever grows (allocated through torch so it is
-    accounted in the caching allocator; the native side never allocates)."""
+    accounted in the caching allocator; the native side never allocates).  ``stream`` is the raw
+    handle of the stream the buffer's kernels run on when that is not the current one: a
+    buffer that is replaced by a larger one is first marked as in use on every stream that
+    consumed it, so the caching allocator cannot hand its block to another tensor while
+    kernels queued there still read and write it."""
     import torch
     dev = torch.cuda.current_device()
     key = (dev, tag)
-    buf = _workspaces.get(key)
+    entry = _workspaces.get(key)
+    buf = entry[0] if entry is not None else None
+    users = entry[1] if entry is not None else set()
+    if stream is not None:
+        users.add(int(stream))
     if buf is None or buf.numel() < nbytes:
+        if buf is not None:
+            for raw in users:
+                buf.record_stream(torch.cuda.ExternalStream(raw, device=f"cuda:{dev}"))
         buf = torch.empty(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=f"cuda:{dev}")
-        _workspaces[key] = buf
+    _workspaces[key] = (buf, users)
     return buf
 
 
@@ -198,7 +209,7 @@ def colsum_accum(dy, out, tag="rowwise", stream=None):
     lib = load()
     lib.bb_colsum_workspace_bytes.restype = _LL
     need = lib.bb_colsum_workspace_bytes(_I(rows), _I(n))
-    ws = workspace(need, tag)
+    ws = workspace(need, tag, stream)
     check(lib.bb_colsum_accum(_ptr(dy), _LL(dy.stride(0)), _ptr(out), _ptr(ws), _LL(ws.numel()), _I(rows), _I(n),
                               _stream(stream)), "bb_colsum_accum")
     return out

@@ -14,9 +14,15 @@ ends by releasing the message's sequence number into the slot flag; a receive is
 that waits - bounded - for that number in local memory and copies the slot into a fresh
 tensor.  If the wait runs out the kernel records ``BB_STATUS_PEER_TIMEOUT`` and the host
 raises ``PeerTimeout``, which the engine maps to its next/previous-stage failure handling.
+
+The host learns the outcome of a receive without synchronising with the stream: a one-thread
+kernel behind the receive stores ``(status << 32) | ticket`` into a pinned host word, and the
+host polls that word (no driver call on the per-message path).  Like the reference's blocking
+``recv``, the engine does not issue work that depends on a message before it has landed.
 """
 import ctypes
 import json
+import time
 from datetime import timedelta
 
 import torch
@@ -61,7 +67,13 @@ class MailboxTransport:
         self.blocking = True
         self._in, self._out = {}, {}
         self._lib = L.load()
-        self._event = torch.cuda.Event()
+        # completion record of the latest receive: 8 bytes of pinned host memory the device writes
+        host = ctypes.c_void_p()
+        L.check(self._lib.bb_pinned_alloc(ctypes.c_longlong(64), ctypes.byref(host)), "bb_pinned_alloc")
+        self._done_ptr = host.value
+        self._done = ctypes.c_ulonglong.from_address(host.value)
+        self._ticket = 0
+        self.wait_s = 0.0            # host time spent waiting for receives (per-step figure for benchmarks)
 
     # ------------------------------------------------------------------ channel set-up
     def _key(self, what, src, dst, kind):
@@ -133,17 +145,37 @@ class MailboxTransport:
                                            self._stream()), "bb_p2p_wait_copy")
 
     def _finish_recv(self, peer):
-        """Block the host until the receive kernel retired and turn a recorded timeout into
-        an exception (the reference's receives are blocking too)."""
+        """Wait on the host until the receive kernel retired and turn a recorded timeout into
+        an exception (the reference's receives are blocking too).  The wait polls the pinned
+        completion word; it gives up a little after the device-side limit."""
         if not self.blocking:
             return
-        self._event.record()
-        self._event.synchronize()
-        status = L.read_status()
+        self._ticket = (self._ticket + 1) & 0xFFFFFFFF or 1
+        ticket = self._ticket
+        L.LAUNCHES += 1
+        L.check(self._lib.bb_p2p_notify(ctypes.c_void_p(self._done_ptr), ctypes.c_uint(ticket), self._stream()),
+                "bb_p2p_notify")
+        done = self._done
+        t0 = time.perf_counter()
+        limit = t0 + 2.0 * self.timeout_s + 30.0
+        spins = 0
+        while True:
+            v = done.value
+            if (v & 0xFFFFFFFF) == ticket:
+                break
+            spins += 1
+            if (spins & 0xFFF) == 0 and time.perf_counter() > limit:
+                raise L.BambooNativeError(f"no completion record for a receive from rank {peer} "
+                                          f"after {2.0 * self.timeout_s + 30.0:.0f} s")
+        self.wait_s += time.perf_counter() - t0
+        status = v >> 32
+        if status == 0:
+            return
+        torch.cuda.current_stream(self.device).synchronize()
+        L.read_status()                      # clears the device word
         if status == L.STATUS_PEER_TIMEOUT:
             raise PeerTimeout(peer)
-        if status != 0:
-            raise L.BambooNativeError(f"device status {status} after a receive from rank {peer}")
+        raise L.BambooNativeError(f"device status {status} after a receive from rank {peer}")
 
     def send(self, tensor, dst, kind, slot, seq):
         t = tensor.detach()
@@ -197,9 +229,16 @@ class MailboxTransport:
             for i, t in enumerate(tensors_out):
                 self._put(ch, i, t.data_ptr(), _round_up(t.numel() * t.element_size(), 16), seq)
         if recv_from is not None:
+            # all pieces or none: the kernel copies only after every piece's flag has arrived
             ch = self._in[(recv_from, STATE)]
-            for i, t in enumerate(tensors_in):
-                self._wait_copy(ch, i, t.data_ptr(), _round_up(t.numel() * t.element_size(), 16), seq)
+            n = len(tensors_in)
+            slots = (ctypes.c_void_p * n)(*[ch.slot(i) for i in range(n)])
+            dsts = (ctypes.c_void_p * n)(*[t.data_ptr() for t in tensors_in])
+            sizes = (ctypes.c_longlong * n)(*[_round_up(t.numel() * t.element_size(), 16) for t in tensors_in])
+            L.LAUNCHES += 1
+            L.check(self._lib.bb_p2p_wait_copy_multi(slots, dsts, sizes, ctypes.c_int(n), ctypes.c_void_p(ch.flag(0)),
+                                                     ctypes.c_ulonglong(seq), ctypes.c_ulonglong(int(self.timeout_s * 1e9)),
+                                                     None, self._stream()), "bb_p2p_wait_copy_multi")
             self._finish_recv(recv_from)
 
     def forget_peer(self, peer):
@@ -212,3 +251,7 @@ class MailboxTransport:
 
     def close(self):
         torch.cuda.synchronize(self.device)
+        if self._done_ptr:
+            self._done = None
+            self._lib.bb_pinned_free(ctypes.c_void_p(self._done_ptr))
+            self._done_ptr = 0

@@ -132,19 +132,38 @@ class DistTransport:
     def exchange_state(self, send_to, tensors_out, recv_from, tensors_in, seq):
         """Ship this stage's flat optimizer state to the rank shadowing it and take the
         successor's into the local shadow buffers."""
-        works = []
+        works, staged = [], []
+        peer = send_to
         try:
             if send_to is not None:
                 for t in tensors_out:
                     self._check_cpu(t)
                     works.append((self.dist.isend(t.detach().contiguous(), send_to, tag=3), send_to))
             if recv_from is not None:
+                # received into staging buffers and moved over only when every piece is in, so a
+                # sender that dies half way leaves the shadow whole (one step old), never torn
+                peer = recv_from
                 for t in tensors_in:
-                    works.append((self.dist.irecv(t, recv_from, tag=3), recv_from))
+                    buf = torch.empty_like(t)
+                    staged.append((t, buf))
+                    works.append((self.dist.irecv(buf, recv_from, tag=3), recv_from))
         except RuntimeError as e:  # connection already closed by a dead peer
-            raise PeerTimeout(send_to if send_to is not None else recv_from, str(e)[:200])
-        for w, peer in works:
-            self._wait(w, peer)
+            raise PeerTimeout(peer, str(e)[:200])
+        send_err = recv_err = None
+        n_send = len(works) - len(staged)
+        for i, (w, peer) in enumerate(works):
+            try:
+                self._wait(w, peer)
+            except PeerTimeout as e:
+                if i < n_send:
+                    send_err = send_err or e
+                else:
+                    recv_err = recv_err or e
+        if recv_err is None:
+            for t, buf in staged:
+                t.copy_(buf)
+        if recv_err is not None or send_err is not None:
+            raise recv_err or send_err
 
     def forget_peer(self, peer):
         for k in [k for k in self._meta if k[0] == peer]:

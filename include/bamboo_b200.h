@@ -200,6 +200,28 @@ int bb_p2p_wait_copy(const void* slot, void* dst, long long bytes, const void* f
 /* Release `seq` into a neighbour's flag without payload: the liveness ping of lazy
  * redundancy (buffer_id = -1, engine.py:1902-1905). */
 int bb_p2p_signal(void* flag_peer, unsigned long long seq, void* stream);
+/* Several slots of one mailbox delivered all-or-nothing: waits until each of the `n`
+ * consecutive 8-byte flags at `flags` holds `seq`, then copies slot i to dsts[i]
+ * (bytes[i], multiples of 16).  If the limit expires first nothing is copied and
+ * BB_STATUS_PEER_TIMEOUT is recorded, so the destination never mixes two messages.
+ * Carries the end-of-step refresh of a shadow stage (weights, exp_avg, exp_avg_sq) - a
+ * transfer the reference declares but leaves empty (SendWeights/RecvWeights,
+ * DS/runtime/pipe/engine.py:2084-2137: _exec_recv_weights returns at :2110-2112). */
+#define BB_P2P_MAX_PIECES 4
+int bb_p2p_wait_copy_multi(const void* const* slots, void* const* dsts, const long long* bytes, int n,
+                           const void* flags, unsigned long long seq, unsigned long long timeout_ns,
+                           int* status_word, void* stream);
+/* Completion record for the host without a stream synchronisation: when the stream reaches
+ * this point, one 8-byte store writes (status_word << 32) | ticket into `host_word`
+ * (pinned, device-visible host memory, see bb_pinned_alloc), which the caller polls.
+ * Replaces the implicit host blocking of p2p.recv (DS/runtime/pipe/p2p_direct.py:15-17):
+ * the engine learns that a receive landed - or timed out - before it issues dependent work. */
+int bb_p2p_notify(void* host_word, unsigned int ticket, void* stream);
+/* Pinned, device-visible host memory for such records (set-up time; zero-filled). */
+int bb_pinned_alloc(long long bytes, void** host_ptr);
+int bb_pinned_free(void* host_ptr);
+/* Clears the device status word in stream order (after a recorded timeout was handled). */
+int bb_clear_status(void* stream);
 
 #ifdef __cplusplus
 }

@@ -232,3 +232,152 @@ def test_unannounced_death_mid_batch_is_recovered(die_at_backward):
     assert out["losses"][3:] == pytest.approx(want[3:], rel=1e-5)
     total = sum(float(p.detach().double().sum()) for p in ref.P.values())
     assert sum(out["checksum"].values()) == pytest.approx(total, rel=1e-6)
+
+
+# ---------------------------------------------------------------------------------------------
+# the plumbing configuration at its stated size: 4-layer decoder, hidden 256, 4 heads, FFN 1024,
+# seq 128, vocab 1024, fp32, micro-batch 4 x 4, Adam lr 1e-4, 5 steps, stage 1 preempted after
+# step 3, redundant computation on; fp32 tolerance 1e-4
+C1 = gpt_ref.RefConfig(layers=4, hidden=256, heads=4, ffn=1024, seq=128, vocab=1024)
+C1_MB, C1_GAS, C1_STEPS, C1_LR = 4, 4, 5, 1e-4
+
+
+def _train_c1(rank, world, store, eager):
+    import cpu_layers
+    from bamboo_b200 import api
+    from bamboo_b200.module import PipelineModule
+    model = PipelineModule(cpu_layers.ref_layer_specs(C1, 0), num_stages=2, loss_fn=cpu_layers.ref_loss(C1),
+                           partition_method="uniform", device="cpu")
+    config = {"train_micro_batch_size_per_gpu": C1_MB, "gradient_accumulation_steps": C1_GAS,
+              "optimizer": {"type": "Adam", "params": {"lr": C1_LR}}, "bamboo_b200": {"p2p_timeout_s": 30}}
+    engine, *_ = api.initialize(model=model, config=config, redundancy_level=1, eager_recovery=eager, store=store)
+    engine.capture_grads = True
+    losses, grad_norms = [], []
+    for step, batches in enumerate(gpt_ref.synthetic_batches(C1, C1_MB, C1_GAS, C1_STEPS, seed=1)):
+        if step == 2 and rank == 1:
+            engine.announce_preemption()                  # gone from step 3 on
+        losses.append(float(engine.train_batch(data_iter=iter(batches))))
+        grad_norms.append(float(sum(g.double().pow(2).sum() for g in engine.last_grads.values()).sqrt()))
+    return {"losses": losses, "grad_norms": grad_norms, "stage_ids": list(engine.stage_ids),
+            "checksum": {s: float(engine.arenas[s].master.double().sum()) for s in engine.stage_ids}}
+
+
+@pytest.mark.parametrize("eager", [False, True])
+def test_plumbing_configuration_at_its_stated_size(eager):
+    from dist_utils import run_ranks
+    ref = gpt_ref.RefTrainer(C1, seed=0, lr=C1_LR, micro_batches=C1_GAS)
+    want, want_norm = [], []
+    for batches in gpt_ref.synthetic_batches(C1, C1_MB, C1_GAS, C1_STEPS, seed=1):
+        want.append(ref.train_batch(batches))
+        want_norm.append(float(sum(g.double().pow(2).sum() for g in ref.last_grads.values()).sqrt()))
+    res = run_ranks(_train_c1, 2, eager, timeout=400)
+    assert res[1] == ("exit", 13)
+    status, out = res[0]
+    assert status == "ok", out
+    assert out["stage_ids"] == [0, 1]
+    # stage 0 owns the loss only after it took stage 1 over (steps 3 and 4)
+    assert out["losses"][3:] == pytest.approx(want[3:], rel=1e-4)
+    # after the failover this rank holds every gradient of the model
+    assert out["grad_norms"][3:] == pytest.approx(want_norm[3:], rel=1e-4)
+    total = sum(float(p.detach().double().sum()) for p in ref.P.values())
+    assert sum(out["checksum"].values()) == pytest.approx(total, rel=1e-6)
+
+
+# ---------------------------------------------------------------------------------------------
+# failure bookkeeping details
+def test_concurrent_detectors_agree_on_the_earlier_step():
+    """Both neighbours of a dead middle stage publish their step at the same moment with the
+    default (lock-free) rendezvous stand-in: neither entry may be lost, both return the minimum."""
+    import threading
+    from types import SimpleNamespace
+    from bamboo_b200.engine import LocalStore, PipelineEngine
+    for trial in range(20):
+        store = LocalStore()
+        cfg = SimpleNamespace(p2p_timeout_s=5.0)
+        out = {}
+        barrier = threading.Barrier(2)
+
+        def detect(rank, step, other):
+            eng = SimpleNamespace(global_store=store, global_rank=rank, _config=cfg)
+            barrier.wait()
+            out[rank] = PipelineEngine._agree_failed_step(eng, 1, step, other)
+        ts = [threading.Thread(target=detect, args=(0, 7, 2)), threading.Thread(target=detect, args=(2, 5, 0))]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        assert out == {0: 5, 2: 5}
+
+
+def test_lone_detector_keeps_its_own_step():
+    from types import SimpleNamespace
+    from bamboo_b200.engine import LocalStore, PipelineEngine
+    eng = SimpleNamespace(global_store=LocalStore(), global_rank=0, _config=SimpleNamespace(p2p_timeout_s=0.2))
+    assert PipelineEngine._agree_failed_step(eng, 1, 4, None) == 4
+    assert PipelineEngine._agree_failed_step(eng, 1, 4, 2) == 4          # the other detector never shows up
+
+
+def _partial_state_sender(rank, world, store):
+    """Rank 1 ships one of three state pieces and then goes silent; rank 0 must keep its buffers."""
+    import time
+    import torch.distributed as dist
+    from bamboo_b200.p2p import DistTransport, PeerTimeout
+    tr = DistTransport(dist, timeout_s=2.0)
+    if rank == 1:
+        w = dist.isend(torch.full((8,), 5.0), 0, tag=3)
+        w.wait()
+        time.sleep(4.0)
+        return "sent one piece"
+    bufs = [torch.zeros(8), torch.ones(8), torch.full((8,), 2.0)]
+    try:
+        tr.exchange_state(None, [], 1, bufs, 1)
+    except PeerTimeout as e:
+        return {"peer": e.peer, "bufs": [b.tolist() for b in bufs]}
+    return "no timeout"
+
+
+def test_state_transfer_is_all_or_nothing():
+    from dist_utils import run_ranks
+    res = run_ranks(_partial_state_sender, 2)
+    status, out = res[0]
+    assert status == "ok" and out["peer"] == 1
+    assert out["bufs"] == [[0.0] * 8, [1.0] * 8, [2.0] * 8]
+
+
+def _stale_shadow(rank, world, store):
+    import cpu_layers
+    from bamboo_b200 import api
+    from bamboo_b200.module import PipelineModule
+    from bamboo_b200.p2p import PeerTimeout
+    model = PipelineModule(cpu_layers.ref_layer_specs(CFG, 0), num_stages=2, loss_fn=cpu_layers.ref_loss(CFG),
+                           partition_method="uniform", device="cpu")
+    config = {"train_micro_batch_size_per_gpu": MB, "gradient_accumulation_steps": GAS,
+              "optimizer": {"type": "Adam", "params": {"lr": LR}}, "bamboo_b200": {"p2p_timeout_s": 20}}
+    engine, *_ = api.initialize(model=model, config=config, redundancy_level=1, store=store)
+    data = gpt_ref.synthetic_batches(CFG, MB, GAS, 2, seed=1)
+    engine.train_batch(data_iter=iter(data[0]))
+    if rank == 0:
+        real = engine.transport.exchange_state
+
+        def failing(send_to, tensors_out, recv_from, tensors_in, seq):
+            real(send_to, tensors_out, recv_from, tensors_in, seq)      # keeps the peer in step
+            raise PeerTimeout(recv_from, "injected: the owner went silent during the transfer")
+        engine.transport.exchange_state = failing
+    engine.train_batch(data_iter=iter(data[1]))
+    if rank != 0:
+        return None
+    valid = dict(engine._shadow_valid)
+    try:
+        engine._promote_next_stage()
+        refused = False
+    except RuntimeError as e:
+        refused = "cannot be promoted" in str(e)
+    return {"valid": valid, "refused": refused}
+
+
+def test_failed_shadow_refresh_blocks_promotion():
+    """A state transfer that timed out leaves the shadow one step behind: it is marked and a
+    later promotion is refused instead of continuing from stale weights."""
+    from dist_utils import run_ranks
+    res = run_ranks(_stale_shadow, 2)
+    status, out = res[0]
+    assert status == "ok", out
+    assert out["valid"] == {1: False} and out["refused"]

@@ -37,8 +37,10 @@ def _run(fn, L, x, dy, dres, gamma, beta):
 def test_static_scratch_entry_point_matches_regular_one():
     from bamboo_b200 import lib as L
     L.load()
-    # two different problems back to back: the second reuses scratch the first one dirtied
-    for rows, h, seed in ((4096, 1024, 1), (1000, 768, 2)):
+    # different problems back to back: each reuses scratch the previous one dirtied.  Hidden
+    # sizes that are multiples of 256 take the column-owner kernel, 1000 the generic
+    # row kernel, 512 and 768 the register-resident row kernels
+    for rows, h, seed in ((4096, 1024, 1), (1000, 768, 2), (777, 1000, 3), (2048, 512, 4)):
         args = _inputs(rows, h, seed)
         want = _run(L.layernorm_bwd, L, *args)
         got = _run(L.layernorm_bwd_static, L, *args)
@@ -46,6 +48,27 @@ def test_static_scratch_entry_point_matches_regular_one():
             # same kernels, same grid, same summation order: bit-identical
             assert torch.equal(a, b)
     assert L.read_status() == 0
+
+
+def test_static_scratch_entry_point_allocates_nothing():
+    """The entry point's defining property: with outputs allocated beforehand, a call changes
+    neither the driver's free-memory figure nor the caching allocator's reservation."""
+    from bamboo_b200 import lib as L
+    L.load()
+    x, dy, dres, gamma, beta = _inputs(4096, 1024, 5)
+    rows, h = x.shape
+    y = torch.empty_like(x)
+    mean, rstd = torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda")
+    L.layernorm_fwd(x, gamma, beta, y, mean, rstd, 1e-5)
+    dx = torch.empty_like(x)
+    dg, db = torch.zeros(h, device="cuda"), torch.zeros(h, device="cuda")
+    for _ in range(2):                                     # the first call on a device looks the array up
+        L.layernorm_bwd_static(dy, x, gamma, mean, rstd, dres, dx, dg, db)
+    torch.cuda.synchronize()
+    free0, reserved0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_reserved()
+    L.layernorm_bwd_static(dy, x, gamma, mean, rstd, dres, dx, dg, db)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0 and torch.cuda.memory_reserved() == reserved0
 
 
 def test_static_scratch_entry_point_rejects_oversized_problems():
