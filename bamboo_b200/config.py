@@ -9,6 +9,7 @@ DeepSpeed 0.5.2 has no such key and the sm_100a kernels compute in bf16.
 import json
 from typing import Optional
 
+RC_MAX_CTAS_DEFAULT = 0
 ADAM = "adam"
 ADAMW = "adamw"
 
@@ -74,6 +75,10 @@ class PipeConfig:
         # stream kernel never waits for a whole tile loop).  Off: measured on 2 GPUs it cost 4 %
         # (308 ms vs 296 ms per step) - the shorter wait does not pay for the slower GEMMs.
         self.rc_short_ctas = bool(ext.get("rc_short_ctas", False))
+        # SM budget of a redundant-computation GEMM: 0 = every SM (persistent CTAs, like the main
+        # stream's), n > 0 = at most n CTAs, so that the main stream always finds free SMs.
+        v = int(ext.get("rc_max_ctas", RC_MAX_CTAS_DEFAULT))
+        self.rc_max_ctas = RC_MAX_CTAS_DEFAULT if v == -2 else v
         self.shadow_sync = bool(ext.get("shadow_sync", True))
 
     def adam_args(self):

@@ -117,6 +117,31 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// Bounded wait with cluster-scope acquire: for barriers that another CTA of the cluster arrives on
+// after writing this CTA's shared memory with plain stores (st.shared::cluster).
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort, int* status) {
+  uint32_t ok;
+  uint64_t t0 = 0;
+  for (uint32_t spin = 0;; ++spin) {
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, P;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    if (ok) return true;
+    if ((spin & 1023u) == 1023u) {
+      if (*abort) return false;
+      uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > BB_WAIT_LIMIT_NS) {
+        *abort = 1;
+        if (status) atomicCAS(status, 0, BB_STATUS_KERNEL_WAIT_TIMEOUT);
+        return false;
+      }
+    }
+  }
+}
+
 // Bounded wait that polls with test_wait (never suspends the thread): for hand-offs on a
 // latency-critical path, where the wake-up delay of a suspended try_wait would dominate.
 __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* abort, int* status) {
@@ -256,6 +281,10 @@ __device__ __forceinline__ uint32_t mapa_shared(uint32_t smem_addr, uint32_t ran
   uint32_t r;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
   return r;
+}
+// plain 4-byte store into the shared memory of another CTA of the cluster (address from mapa_shared)
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");

@@ -4,6 +4,13 @@
 // accumulators, warps 2-9 drain TMEM (tcgen05.ld) and run the epilogue (coalesced global
 // stores from warp-private staging slabs) while the next tile's main loop is already running.
 //
+// Work units are handed out dynamically: the first unit of a CTA is its own index, every further
+// one comes from a per-launch ticket counter in global memory (one atomicAdd per unit, issued a
+// whole unit ahead of its use), and the producer thread passes it to the MMA and epilogue warps
+// (and to the second CTA of a pair) through a four-entry ring in shared memory.  A CTA that
+// starts late - because a kernel of another stream still held its SM - therefore takes fewer
+// units instead of stretching the launch by its fixed share.
+//
 // Large problems run as CTA pairs (cta_group::2, clusters of two): a pair owns a 256 x 256
 // tile, each CTA loads its own 128 rows of A and only HALF of the B tile, rank 0 issues one
 // 256-row MMA for both and each CTA drains its own 128 accumulator rows.  Per CTA that is a
@@ -19,6 +26,9 @@
 #include "common.cuh"
 #include "bamboo_b200.h"
 #include "tma_host.cuh"
+#include <atomic>
+#include <mutex>
+#include <stdlib.h>
 
 namespace {
 
@@ -32,6 +42,7 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
 // epilogue warp; shared memory is better spent on main-loop stages.
 constexpr int SLAB_BYTES = 32 * 128;
 constexpr int NUM_SLABS = 8;
+constexpr int SCHED_RING = 4;  // work units announced ahead of their consumption (power of two)
 
 template <int BN, bool PAIR> struct Cfg {
   static constexpr int B_ROWS = PAIR ? BN / 2 : BN;      // B rows (output columns) this CTA loads
@@ -49,6 +60,9 @@ struct GemmParams {
   int epi;
   int ksplit, kb_per_split;   // split-K work units (fp32 add-reduction epilogue only)
   int n_fast;                 // tile order: consecutive work units walk along N (else along M)
+  int dynamic;                // 1: work units after a CTA's first come from the ticket counter
+  unsigned int* ticket;       // this launch's ticket counter (global memory)
+  unsigned int ticket_base;   // its value before this launch's first ticket
   void* D; void* D2; const void* bias; const void* aux;
   long long ldd, ld_aux;
   int* status;
@@ -245,12 +259,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   uint64_t* empty_bar = bars + C::STAGES;         // [STAGES]
   uint64_t* tmem_full = bars + 2 * C::STAGES;     // [2]
   uint64_t* tmem_empty = bars + 2 * C::STAGES + 2;  // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 4);
+  uint64_t* sched_full = bars + 2 * C::STAGES + 4;  // [SCHED_RING]
+  uint64_t* sched_empty = sched_full + SCHED_RING;  // [SCHED_RING] (pairs: rank 0's are used by both CTAs)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sched_empty + SCHED_RING);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* sched_tile = reinterpret_cast<volatile int*>(tmem_slot + 2);   // [SCHED_RING]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  // work units are strided over CTAs (pairs: over clusters; both CTAs walk the same units)
+  // work units go to CTAs (pairs: to clusters; both CTAs of a pair walk the same units)
   const uint32_t rank = PAIR ? bb::cluster_ctarank() : 0u;
   const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int num_workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
@@ -265,6 +282,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     for (int s = 0; s < C::STAGES; ++s) { bb::mbar_init(&full_bar[s], 1); bb::mbar_init(&empty_bar[s], 1); }
     // accumulator hand-back: one arrival per epilogue warp (of both CTAs for a pair, on rank 0's barrier)
     for (int a = 0; a < 2; ++a) { bb::mbar_init(&tmem_full[a], 1); bb::mbar_init(&tmem_empty[a], (PAIR ? 2 : 1) * 4 * EW); }
+    // work-unit ring: one announcement per entry; read by the MMA warp and the epilogue warps of
+    // this CTA and, for a pair, by the producer and the epilogue warps of the second CTA
+    for (int r = 0; r < SCHED_RING; ++r) { bb::mbar_init(&sched_full[r], 1); bb::mbar_init(&sched_empty[r], (PAIR ? 2 : 1) * (1 + 4 * EW)); }
     bb::fence_barrier_init();
     bb::tma_prefetch_desc(&tmA);
     bb::tma_prefetch_desc(&tmB);
@@ -279,12 +299,31 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   bb::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Next work unit of this CTA as announced by the scheduling thread (-1: no more).  Called by a
+  // whole warp (`warp_wide`) or by a single thread; the entry is handed back once it has been read.
+  auto next_unit = [&](uint32_t it, int& tile, bool warp_wide) -> bool {
+    const int r = (int)(it & (SCHED_RING - 1));
+    const uint32_t ph = (it / SCHED_RING) & 1u;
+    const bool got = PAIR ? bb::mbar_wait_cluster(&sched_full[r], ph, abort_flag, p.status)
+                          : bb::mbar_wait(&sched_full[r], ph, abort_flag, p.status);
+    if (warp_wide) { if (!__all_sync(0xffffffffu, got)) return false; }
+    else if (!got) return false;
+    tile = sched_tile[r];
+    if (warp_wide) __syncwarp();
+    if (!warp_wide || lane == 0) {
+      if (PAIR) bb::mbar_arrive_cluster(bb::mapa_shared(bb::smem_u32(&sched_empty[r]), 0));
+      else bb::mbar_arrive(&sched_empty[r]);
+    }
+    return true;
+  };
+
   if (warp == 0) {
     // ------------------------------------------------ TMA producer
     if (lane == 0) {
       int s = 0; uint32_t phase = 0;
       bool alive = true;
-      for (int tile = worker; tile < num_tiles && alive; tile += num_workers) {
+      // operand loads of one work unit
+      auto load_unit = [&](int tile) {
         const int mn = tile % num_mn, ks = tile / num_mn;
         const int mi = p.n_fast ? mn / num_n : mn % num_m, ni = p.n_fast ? mn % num_n : mn / num_m;
         const int m0 = mi * C::TILE_M + (int)rank * BM;                    // this CTA's A rows
@@ -328,6 +367,46 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           }
           if (++s == C::STAGES) { s = 0; phase ^= 1; }
         }
+      };
+      if (rank == 0) {
+        // ---- scheduling thread: announces every work unit of this CTA (pair) to its consumers
+        auto announce = [&](uint32_t it, int tile) -> bool {
+          const int r = (int)(it & (SCHED_RING - 1));
+          const uint32_t ph = (it / SCHED_RING) & 1u;
+          const bool free_ = PAIR ? bb::mbar_wait_cluster(&sched_empty[r], ph ^ 1, abort_flag, p.status)
+                                  : bb::mbar_wait(&sched_empty[r], ph ^ 1, abort_flag, p.status);
+          if (!free_) return false;
+          sched_tile[r] = tile;
+          if (PAIR) {
+            bb::st_shared_cluster_u32(bb::mapa_shared(bb::smem_u32(const_cast<int*>(&sched_tile[r])), 1), (uint32_t)tile);
+            bb::mbar_arrive_cluster(bb::mapa_shared(bb::smem_u32(&sched_full[r]), 1));
+          }
+          bb::mbar_arrive(&sched_full[r]);
+          return true;
+        };
+        // ticket t of this launch stands for work unit num_workers + t (units below num_workers are
+        // the CTAs' first ones); every scheduling thread draws until its first ticket past the
+        // end, so a launch consumes exactly num_tiles tickets - the host relies on that count
+        auto draw = [&]() -> int { return num_workers + (int)(atomicAdd(p.ticket, 1u) - p.ticket_base); };
+        uint32_t it = 0;
+        int cur = worker, nxt = worker;
+        while (cur < num_tiles) {
+          nxt = p.dynamic ? draw() : cur + num_workers;     // in flight while this unit's loads are issued
+          if (!announce(it++, cur)) { alive = false; break; }
+          load_unit(cur);
+          if (!alive) break;
+          cur = nxt;
+        }
+        if (alive) { if (!announce(it++, -1)) alive = false; }
+        else if (p.dynamic) { while (nxt < num_tiles) nxt = draw(); }
+      } else {
+        // second CTA of a pair: follows rank 0's announcements
+        for (uint32_t it = 0; alive; ++it) {
+          int tile;
+          if (!next_unit(it, tile, false)) { alive = false; break; }
+          if (tile < 0) break;
+          load_unit(tile);
+        }
       }
       if constexpr (PAIR) {
         // rank 0's MMA commits arrive on this CTA's barriers too: wait until the last one of every
@@ -356,7 +435,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     int acc = 0; uint32_t acc_phase = 0;
     bool alive = true;
     // pairs: rank 0 issues for both CTAs; the other CTA's MMA warp only allocates and frees TMEM
-    for (int tile = worker; tile < num_tiles && alive && rank == 0; tile += num_workers) {
+    for (uint32_t it = 0; alive && rank == 0; ++it) {
+      int tile;
+      if (!next_unit(it, tile, true)) { alive = false; break; }
+      if (tile < 0) break;
       if (!bb::mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status)) { alive = false; break; }
       bb::tc_fence_after_sync();
       const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
@@ -409,7 +491,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       // derivative) on short reductions, where eight warps cannot finish a tile's epilogue
       // within the next tile's main loop: sixteen warps, 32 bf16 columns per pass (bf16 outputs only).
       uint8_t* slab = panels + (warp - 2) * (SLAB_BYTES / 2);
-      for (int tile = worker; tile < num_tiles && alive; tile += num_workers) {
+      for (uint32_t it = 0; alive; ++it) {
+        int tile;
+        if (!next_unit(it, tile, true)) { alive = false; break; }
+        if (tile < 0) break;
         const int mn = tile % num_mn;
         const int mi = p.n_fast ? mn / num_n : mn % num_m, ni = p.n_fast ? mn % num_n : mn / num_m;
         const int m0 = mi * C::TILE_M + (int)rank * BM, n0 = ni * BN;
@@ -472,7 +557,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       }
     } else {
     uint8_t* slab = panels + (warp - 2) * SLAB_BYTES;
-    for (int tile = worker; tile < num_tiles && alive; tile += num_workers) {
+    for (uint32_t it = 0; alive; ++it) {
+      int tile;
+      if (!next_unit(it, tile, true)) { alive = false; break; }
+      if (tile < 0) break;
       const int mn = tile % num_mn;
       const int mi = p.n_fast ? mn / num_n : mn % num_m, ni = p.n_fast ? mn % num_n : mn / num_m;
       const int m0 = mi * C::TILE_M + (int)rank * BM, n0 = ni * BN;
@@ -577,6 +665,40 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 // ---------------------------------------------------------------- host side
 using bbhost::encode_2d;
 
+// Ticket counters of the dynamic work distribution: a launch takes the next slot of a ring of
+// counters in device memory and draws exactly `units` tickets from it (see the scheduling
+// thread), so the host knows every counter's value without reading it back and nothing is ever
+// reset.  A slot is reused 65536 launches later, long after the launch that held it retired.
+constexpr unsigned TICKET_SLOTS = 1u << 16;
+__device__ unsigned int g_gemm_tickets[TICKET_SLOTS];
+
+struct TicketTable {
+  unsigned int* dev = nullptr;
+  std::atomic<unsigned> next{0};
+  unsigned base[TICKET_SLOTS] = {};
+};
+
+// BB_GEMM_STATIC_SCHEDULE=1 in the environment restores the fixed stride (unit i of a CTA =
+// its index + i x CTAs), for A/B measurements of the two distributions.
+const bool g_static_schedule = [] { const char* e = getenv("BB_GEMM_STATIC_SCHEDULE"); return e && e[0] == '1'; }();
+
+TicketTable* ticket_table() {
+  static TicketTable* tables[64] = {nullptr};
+  static std::mutex mu;
+  const int dev = bb_current_device();
+  if (dev < 0) return nullptr;
+  TicketTable* t = tables[dev];
+  if (t) return t;
+  std::lock_guard<std::mutex> lock(mu);
+  if (tables[dev]) return tables[dev];
+  void* ptr = nullptr;
+  if (cudaGetSymbolAddress(&ptr, g_gemm_tickets) != cudaSuccess) return nullptr;
+  t = new TicketTable();
+  t->dev = static_cast<unsigned int*>(ptr);
+  tables[dev] = t;
+  return t;
+}
+
 template <int BN, bool PAIR, int EW>
 int launch(const bb_gemm_desc* g, cudaStream_t stream) {
   using C = Cfg<BN, PAIR>;
@@ -630,6 +752,17 @@ int launch(const bb_gemm_desc* g, cudaStream_t stream) {
   // persistent CTA that found a free SM keeps it for its whole tile loop, and a persistent kernel
   // of the main stream launched meanwhile waits for that SM with a fixed share of the tiles.
   if (g->max_ctas < 0) workers = tiles;
+  // more units than CTAs: every unit after a CTA's first is drawn from this launch's ticket counter
+  p.dynamic = 0; p.ticket = nullptr; p.ticket_base = 0;
+  unsigned slot = 0;
+  TicketTable* tt = nullptr;
+  if (tiles > workers && !g_static_schedule) {
+    tt = ticket_table();
+    if (!tt) { bb_set_last_error_msg("bb_gemm_bf16: ticket counters unavailable on this device"); return BB_ERR_CUDA; }
+    slot = tt->next.fetch_add(1u) & (TICKET_SLOTS - 1);
+    p.dynamic = 1; p.ticket = tt->dev + slot; p.ticket_base = tt->base[slot];
+    tt->base[slot] += (unsigned)tiles;
+  }
   if constexpr (PAIR) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * workers); cfg.blockDim = dim3(num_threads(EW));
@@ -638,11 +771,23 @@ int launch(const bb_gemm_desc* g, cudaStream_t stream) {
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    BB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<BN, true, EW>, tmA, tmB, p));
+    cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<BN, true, EW>, tmA, tmB, p);
+    if (le != cudaSuccess) {
+      if (tt) tt->base[slot] -= (unsigned)tiles;     // nothing ran: the counter keeps its value
+      bb_set_last_error("gemm_bf16_tcgen05_kernel (pair) launch", le);
+      return BB_ERR_CUDA;
+    }
   } else {
     gemm_bf16_tcgen05_kernel<BN, false, EW><<<workers, num_threads(EW), C::SMEM_BYTES, stream>>>(tmA, tmB, p);
   }
-  BB_CUDA_CHECK(cudaGetLastError());
+  {
+    cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) {
+      if (tt) tt->base[slot] -= (unsigned)tiles;     // nothing ran: the counter keeps its value
+      bb_set_last_error("gemm_bf16_tcgen05_kernel launch", le);
+      return BB_ERR_CUDA;
+    }
+  }
   return BB_OK;
 }
 

@@ -690,7 +690,8 @@ class PipelineEngine:
                 label.record_stream(self.rc_stream)
             from . import lib as _lib
             with torch.cuda.stream(self.rc_stream):
-                _lib.GEMM_MAX_CTAS = -1 if self._config.rc_short_ctas else 0    # short CTAs: see bb_gemm_desc.max_ctas
+                # SM budget of the redundant GEMMs (bb_gemm_desc.max_ctas): -1 = one unit per CTA
+                _lib.GEMM_MAX_CTAS = -1 if self._config.rc_short_ctas else self._config.rc_max_ctas
                 try:
                     self._forward_stage(inputs, buffer_id, stage_id, retain=self._config.rc_retain_graph)
                 finally:

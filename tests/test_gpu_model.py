@@ -144,3 +144,64 @@ def test_layers_refuse_cpu_tensors():
     blk = layers.TransformerBlock(64, 1, 256)
     with pytest.raises(lib.BambooNativeError):
         blk(torch.zeros(1, 8, 64))
+
+
+# ---------------------------------------------------------------------------------------------
+# the benchmark configurations at their own dimensions (depth cut to two blocks so that the fp32
+# oracle finishes in seconds on the host): the kernels take the same paths as in the timed runs -
+# hidden 1024 with 16 heads of 64, 1024-token causal tiles (16 key sub-blocks per query tile),
+# vocabulary 50257 padded to 50304, CTA-pair GEMMs on the K >= 2048 shapes
+def test_gpt2_medium_dimensions_match_oracle():
+    cfg = gpt_ref.RefConfig(layers=2, hidden=1024, heads=16, ffn=4096, seq=1024, vocab=50257)
+    mb, gas, lr = 2, 2, 1e-4
+    ref = gpt_ref.RefTrainer(cfg, seed=0, lr=lr, micro_batches=gas)
+    engine = build_engine(cfg, mb, gas, lr)
+    for batches in gpt_ref.synthetic_batches(cfg, mb, gas, 2, seed=1):
+        want = ref.train_batch(batches)
+        got = float(engine.train_batch(data_iter=iter(batches)))
+        assert got == pytest.approx(want, rel=TOL)
+        compare_grads(engine, ref, cfg)
+    from bamboo_b200 import lib
+    torch.cuda.synchronize()
+    assert lib.read_status() == 0
+
+
+def test_bert_large_dimensions_match_oracle():
+    """Masked-LM encoder at its benchmark dimensions: seq 512, bidirectional attention, vocabulary
+    30522 padded to 30592, loss on the 15 % chosen positions."""
+    cfg = gpt_ref.RefConfig(layers=2, hidden=1024, heads=16, ffn=4096, seq=512, vocab=30522, causal=False, mlm=True)
+    mb, gas, lr = 2, 2, 1e-4
+    ref = gpt_ref.RefTrainer(cfg, seed=0, lr=lr, micro_batches=gas)
+    engine = build_engine(cfg, mb, gas, lr)
+    for batches in gpt_ref.synthetic_mlm_batches(cfg, mb, gas, 2, seed=7):
+        want = ref.train_batch(batches)
+        got = float(engine.train_batch(data_iter=iter(batches)))
+        assert got == pytest.approx(want, rel=TOL)
+        compare_grads(engine, ref, cfg)
+    from bamboo_b200 import lib
+    torch.cuda.synchronize()
+    assert lib.read_status() == 0
+
+
+def test_checkpoint_round_trip_on_cuda_arena(tmp_path):
+    """Per-layer checkpoint files written from a CUDA parameter arena and loaded into a fresh
+    engine: master weights and Adam moments come back bit-identical, the bf16 working copy is
+    re-derived, and the next step's loss is the same number."""
+    cfg = gpt_ref.RefConfig(layers=2, hidden=256, heads=4, ffn=1024, seq=128, vocab=1000)
+    mb, gas, lr = 2, 2, 1e-3
+    data = gpt_ref.synthetic_batches(cfg, mb, gas, 3, seed=1)
+    a = build_engine(cfg, mb, gas, lr)
+    for batches in data[:2]:
+        a.train_batch(data_iter=iter(batches))
+    ckpt = str(tmp_path / "ckpt")
+    a.save_checkpoint(ckpt, client_state={"k": 1})
+    want = float(a.train_batch(data_iter=iter(data[2])))
+    files = sorted(os.listdir(os.path.join(ckpt, "global_step2")))
+    assert files == [f"layer_{i:02d}-model_states.pt" for i in range(5)] + ["mp_rank_00_model_states.pt"]
+    b = build_engine(cfg, mb, gas, lr)
+    path, client = b.load_checkpoint(ckpt)
+    assert path is not None and client == {"k": 1} and b.global_steps == 2
+    got = float(b.train_batch(data_iter=iter(data[2])))
+    assert got == want
+    for name in ("master", "exp_avg", "exp_avg_sq", "lp"):
+        assert torch.equal(getattr(a.arenas[0], name), getattr(b.arenas[0], name)), name

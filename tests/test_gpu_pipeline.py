@@ -102,3 +102,65 @@ def test_data_parallel_replicas_average_gradients():
         assert res[r][0] == "ok" and res[r][1]["status"] == 0
         assert res[r][1]["losses"] == pytest.approx([w[r] for w in want], rel=2e-2)
     assert res[0][1]["checksum"] == res[1][1]["checksum"]          # replicas stay bit-identical
+
+
+# ---------------------------------------------------------------------------------------------
+# a failure that nobody announced, seen in the middle of a batch through the transport: stage 1
+# stays alive but stops answering for longer than the receive limit
+def _train_silent_peer(rank, world, store, go_silent_in_step, at_backward):
+    import time
+    import torch.distributed as dist
+    from bamboo_b200 import api, engine as E, lib, models
+    from bamboo_b200.module import PipelineModule
+    tc = models.TransformerConfig(layers=CFG.layers, hidden=CFG.hidden, heads=CFG.heads, ffn=CFG.ffn, seq=CFG.seq,
+                                  vocab=CFG.vocab)
+    model = PipelineModule(models.transformer_layer_specs(tc, 0), num_stages=world, loss_fn=models.transformer_loss(tc),
+                           partition_method="type:TransformerBlock")
+    config = {"train_micro_batch_size_per_gpu": MB, "gradient_accumulation_steps": GAS, "bf16": {"enabled": True},
+              "optimizer": {"type": "Adam", "params": {"lr": LR}}, "bamboo_b200": {"p2p_timeout_s": 30}}
+    engine, *_ = api.initialize(model=model, config=config, redundancy_level=1, eager_recovery=False, store=store)
+    if rank == 1:
+        calls = {"n": 0}
+        orig = E.PipelineEngine._exec_backward_pass
+
+        def silent_backward(self, buffer_id, stage_id):
+            if self.global_steps == go_silent_in_step:
+                calls["n"] += 1
+                if calls["n"] == at_backward:
+                    # nothing of this rank is in flight on its GPU while it is silent; it leaves the
+                    # job only after the survivor has finished (the host sleeps, the GPU idles)
+                    torch.cuda.synchronize()
+                    time.sleep(25.0)
+                    os._exit(0)
+            return orig(self, buffer_id, stage_id)
+        E.PipelineEngine._INSTRUCTION_MAP[E.schedule.BackwardPass] = silent_backward
+    data = gpt_ref.synthetic_batches(CFG, MB, GAS, STEPS, seed=1)
+    losses, waited = [], None
+    for step, batches in enumerate(data):
+        if step == go_silent_in_step:
+            # start-up skew is over: from here on a neighbour has 2 s to answer
+            engine._config.p2p_timeout_s = 2.0
+            engine.transport.timeout_s = 2.0
+        t0 = time.time()
+        losses.append(float(engine.train_batch(data_iter=iter(batches))))
+        if step == go_silent_in_step:
+            waited = time.time() - t0
+    torch.cuda.synchronize()
+    return {"losses": losses, "stage_ids": list(engine.stage_ids), "status": lib.read_status(), "waited": waited}
+
+
+@needs2
+@pytest.mark.parametrize("at_backward", [1, 3])
+def test_silent_stage_is_detected_by_the_bounded_wait_and_replaced(at_backward):
+    """Stage 1 goes silent during step 3 after some of its backward passes (host sleep, its GPU
+    idle, NVLS off).  Stage 0's receive kernel gives up after its 2 s limit and records the
+    time-out; the engine turns that into the next-stage failure, promotes the shadow stage,
+    replays the dead stage's part of the batch and finishes the run with the oracle's losses."""
+    from dist_utils import run_ranks
+    want = _oracle()
+    res = run_ranks(_train_silent_peer, 2, 3, at_backward, backend="nccl", timeout=300)
+    status, out = res[0]
+    assert status == "ok", out
+    assert out["stage_ids"] == [0, 1] and out["status"] == 0
+    assert 2.0 <= out["waited"] < 15.0                    # one bounded wait, not a hang
+    assert out["losses"][3:] == pytest.approx(want[3:], rel=2e-2)
