@@ -242,6 +242,7 @@ class PipelineEngine:
         if self.r_stage_ids:
             self._sched_layers.append(("eager" if self.eager_recovery else "lazy", dict(stage_id=self.next_stage)))
         self._seq = collections.Counter()
+        self._fwd_done: Dict[Tuple[int, int], object] = {}   # (stage, buffer) -> event behind that forward
 
     # ------------------------------------------------------------------ helpers
     def _inc(self, s):
@@ -326,6 +327,7 @@ class PipelineEngine:
             self.pipe_buffers[k] = []
         self.num_pipe_buffers = 0
         self._losses = {}
+        self._fwd_done.clear()
 
     def _reserve_pipe_buffers(self, n):
         for k, v in self.pipe_buffers.items():
@@ -677,8 +679,12 @@ class PipelineEngine:
         inputs = self.pipe_buffers[in_key][buffer_id]
         shadow = self._is_shadow(stage_id)
         if shadow and self.rc_stream is not None:
-            # redundant computation: off the critical path, on the low-priority stream
-            ready = torch.cuda.current_stream().record_event()
+            # redundant computation: off the critical path, on the low-priority stream.  It starts
+            # as soon as its input exists: the event recorded behind this rank's own forward of the
+            # same micro-batch (not the present end of the main stream, which already holds later work)
+            ready = self._fwd_done.pop((self._dec(stage_id), buffer_id), None) if stage_id != 0 else None
+            if ready is None:
+                ready = torch.cuda.current_stream().record_event()
             self.rc_stream.wait_event(ready)
             # the redundant forward may run many micro-batches later than it was issued: its
             # inputs must not go back to the main stream's allocator before it has read them
@@ -699,6 +705,8 @@ class PipelineEngine:
                 self._rc_event = self.rc_stream.record_event()
         else:
             self._forward_stage(inputs, buffer_id, stage_id, retain=(not shadow) or self._config.rc_retain_graph)
+            if self.rc_stream is not None and not shadow and self._inc(stage_id) in self.r_stage_ids:
+                self._fwd_done[(stage_id, buffer_id)] = torch.cuda.current_stream().record_event()
         if stage_id == 0:
             self.pipe_buffers["data"][buffer_id] = None
         if stage_id == self.num_stages - 1:
@@ -909,6 +917,26 @@ class PipelineEngine:
         except Exception:
             return True
 
+    def _sends_before_redundant_work(self, step_cmds):
+        """Execution order inside one step of an eager-RC stream.  The stream puts the successor's
+        queued [load, receive, forward] in front of this stage's own instructions; issuing those
+        ~50 launches takes the host a couple of milliseconds, during which this stage's finished
+        activation (or gradient) would sit unsent and the neighbour would wait for it.  The sends
+        of the step are therefore issued first, then the redundant work, then the rest in its
+        emitted order.  (Sends are non-blocking store kernels; the emitted stream is unchanged.)"""
+        last = -1
+        for i, c in enumerate(step_cmds):
+            sid = c.kwargs.get("stage_id") if hasattr(c, "kwargs") else None
+            if sid is not None and sid in self.r_stage_ids and sid not in self.stage_ids \
+                    and type(c) in (schedule.ForwardPass, schedule.RecvActivation):
+                last = i
+        if last < 0:
+            return step_cmds
+        shadow, own = step_cmds[:last + 1], step_cmds[last + 1:]
+        sends = [c for c in own if type(c) in (schedule.SendActivation, schedule.SendGrad)]
+        rest = [c for c in own if type(c) not in (schedule.SendActivation, schedule.SendGrad)]
+        return sends + shadow + rest
+
     _INSTRUCTION_MAP = {
         schedule.OptimizerStep: _exec_optimizer_step,
         schedule.ReduceGrads: _exec_reduce_grads,
@@ -949,6 +977,8 @@ class PipelineEngine:
                 rest = [c for c in step_cmds if type(c) is not schedule.ReduceGrads]
                 k = next(i for i, c in enumerate(rest) if type(c) is schedule.OptimizerStep)
                 step_cmds = rest[:k] + reduces + rest[k:]
+            if self.eager_recovery:
+                step_cmds = self._sends_before_redundant_work(step_cmds)
             for cmd in step_cmds:
                 try:
                     fn = self._INSTRUCTION_MAP.get(type(cmd))
