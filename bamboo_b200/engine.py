@@ -243,6 +243,7 @@ class PipelineEngine:
             self._sched_layers.append(("eager" if self.eager_recovery else "lazy", dict(stage_id=self.next_stage)))
         self._seq = collections.Counter()
         self._fwd_done: Dict[Tuple[int, int], object] = {}   # (stage, buffer) -> event behind that forward
+        self._shadow_ctx = False        # True while an instruction of a redundant-work group executes
 
     # ------------------------------------------------------------------ helpers
     def _inc(self, s):
@@ -651,6 +652,14 @@ class PipelineEngine:
         if self.pipe_buffers["label"][buffer_id] is not None or self.pipe_buffers["data"][buffer_id] is not None:
             return
         batch = self._next_batch()
+        if self._shadow_ctx and self.rc_stream is not None:
+            # a load that only the redundant forward consumes: its copies go to that stream, so the
+            # forward is ordered behind them without waiting for the main stream's queued work
+            with torch.cuda.stream(self.rc_stream):
+                return self._place_micro_batch(batch, buffer_id)
+        return self._place_micro_batch(batch, buffer_id)
+
+    def _place_micro_batch(self, batch, buffer_id):
         if 0 in self.stage_ids or 0 in self.r_stage_ids:
             x = batch[0]
             if torch.is_tensor(x):
@@ -679,13 +688,13 @@ class PipelineEngine:
         inputs = self.pipe_buffers[in_key][buffer_id]
         shadow = self._is_shadow(stage_id)
         if shadow and self.rc_stream is not None:
-            # redundant computation: off the critical path, on the low-priority stream.  It starts
-            # as soon as its input exists: the event recorded behind this rank's own forward of the
-            # same micro-batch (not the present end of the main stream, which already holds later work)
-            ready = self._fwd_done.pop((self._dec(stage_id), buffer_id), None) if stage_id != 0 else None
-            if ready is None:
-                ready = torch.cuda.current_stream().record_event()
-            self.rc_stream.wait_event(ready)
+            # redundant computation: off the critical path, on the low-priority stream.  Its load
+            # and its input hand-off were issued on that stream too (see _exec_load_micro_batch,
+            # _exec_recv_activations), behind the event of this rank's own forward of the same
+            # micro-batch - not behind the present end of the main stream, which holds later work
+            if not self._shadow_ctx:
+                # issued outside a redundant-work group (its inputs were produced on the main stream)
+                self.rc_stream.wait_event(torch.cuda.current_stream().record_event())
             # the redundant forward may run many micro-batches later than it was issued: its
             # inputs must not go back to the main stream's allocator before it has read them
             for t in (inputs if isinstance(inputs, tuple) else (inputs,)):
@@ -773,7 +782,18 @@ class PipelineEngine:
         if self._dec(stage_id) in self.stage_ids or (self.eager_recovery and stage_id in self.r_stage_ids):
             if buffer_id >= 0 and self.pipe_buffers[f"input_{stage_id}"][buffer_id] is None:
                 src = self.pipe_buffers[f"output_{self._dec(stage_id)}"][buffer_id]
-                t = src.detach().clone()
+                if self._shadow_ctx and self.rc_stream is not None and self._is_shadow(stage_id):
+                    # hand-off to the redundant forward: the copy runs on its stream, as soon as this
+                    # rank's own forward of the micro-batch has produced the source
+                    ready = self._fwd_done.pop((self._dec(stage_id), buffer_id), None)
+                    if ready is None:
+                        ready = torch.cuda.current_stream().record_event()
+                    self.rc_stream.wait_event(ready)
+                    with torch.cuda.stream(self.rc_stream):
+                        t = src.detach().clone()
+                    src.record_stream(self.rc_stream)
+                else:
+                    t = src.detach().clone()
                 t.requires_grad = True
                 self.pipe_buffers[f"input_{stage_id}"][buffer_id] = t
             return
@@ -931,11 +951,11 @@ class PipelineEngine:
                     and type(c) in (schedule.ForwardPass, schedule.RecvActivation):
                 last = i
         if last < 0:
-            return step_cmds
+            return step_cmds, ()
         shadow, own = step_cmds[:last + 1], step_cmds[last + 1:]
         sends = [c for c in own if type(c) in (schedule.SendActivation, schedule.SendGrad)]
         rest = [c for c in own if type(c) not in (schedule.SendActivation, schedule.SendGrad)]
-        return sends + shadow + rest
+        return sends + shadow + rest, {id(c) for c in shadow}
 
     _INSTRUCTION_MAP = {
         schedule.OptimizerStep: _exec_optimizer_step,
@@ -977,9 +997,11 @@ class PipelineEngine:
                 rest = [c for c in step_cmds if type(c) is not schedule.ReduceGrads]
                 k = next(i for i, c in enumerate(rest) if type(c) is schedule.OptimizerStep)
                 step_cmds = rest[:k] + reduces + rest[k:]
+            shadow_ids = ()
             if self.eager_recovery:
-                step_cmds = self._sends_before_redundant_work(step_cmds)
+                step_cmds, shadow_ids = self._sends_before_redundant_work(step_cmds)
             for cmd in step_cmds:
+                self._shadow_ctx = id(cmd) in shadow_ids
                 try:
                     fn = self._INSTRUCTION_MAP.get(type(cmd))
                     if fn is None:
