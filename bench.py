@@ -47,6 +47,8 @@ def parse():
                     help="redundant forwards keep their autograd graph, as the reference's shadow forwards do")
     ap.add_argument("--rc-max-ctas", type=int, default=-2,
                     help="SM budget of a redundant-computation GEMM (see bamboo_b200.rc_max_ctas; -2 = library default)")
+    ap.add_argument("--rc-blind-partition", action="store_true",
+                    help="eager RC: balance the stages alone (default: balance own stage + redundant forward of the next)")
     ap.add_argument("--dp", type=int, default=0, help="pipeline replicas (default 1; 2 for gpt-6.7b on 8 GPUs)")
     ap.add_argument("--whole-blocks", action="store_true",
                     help="multi-stage runs: keep every transformer block one pipeline layer (coarser stage boundaries)")
@@ -60,32 +62,48 @@ def model_config(name):
     return {"gpt2-medium": models.GPT2_MEDIUM, "bert-large": models.BERT_LARGE, "gpt-6.7b": models.GPT_6_7B}.get(name, models.GPT_TOY)
 
 
-def contiguous_partition(costs, parts):
+def contiguous_partition(costs, parts, rc_frac=0.0):
     """Boundaries of `parts` non-empty contiguous groups of `costs` with the smallest maximum
-    group sum and, among those, the smallest sum of squares (dynamic programme over prefixes).
-    The package's `partition_balanced` follows the reference's bottleneck search, which may leave
-    the last stages empty when one heavy layer (the vocabulary head) ends the list."""
+    stage load and, among those, the smallest sum of squared loads.  The load of a stage is its
+    own cost plus `rc_frac` x the cost of the stage after it: with eager redundant computation a
+    rank also runs its successor's forward (a third of that stage's forward+backward time),
+    except the last rank, whose shadow stage is never run ahead.  `rc_frac` = 0 balances the
+    stages themselves.  (The package's `partition_balanced` follows the reference's bottleneck
+    search, which may leave the last stages empty when one heavy layer - the vocabulary head -
+    ends the list.)  Dynamic programme over (groups so far, start and end of the last group)."""
     n = len(costs)
     pre = [0.0]
     for c in costs:
         pre.append(pre[-1] + c)
     INF = (float("inf"), float("inf"))
-    best = [[INF] * (n + 1) for _ in range(parts + 1)]
-    arg = [[0] * (n + 1) for _ in range(parts + 1)]
-    best[0][0] = (0.0, 0.0)
-    for k in range(1, parts + 1):
-        for j in range(k, n + 1):
-            for i in range(k - 1, j):
-                if best[k - 1][i] == INF:
-                    continue
-                load = pre[j] - pre[i]
-                cand = (max(best[k - 1][i][0], load), best[k - 1][i][1] + load * load)
-                if cand < best[k][j]:
-                    best[k][j], arg[k][j] = cand, i
-    bounds, j = [n], n
+    # best[k][i][j]: k groups cover costs[:j], the last one is costs[i:j]; its own load is still
+    # open (it depends on the group after it), the value covers the k-1 groups before it
+    best = [dict() for _ in range(parts + 1)]
+    for j in range(1, n - parts + 2):
+        best[1][(0, j)] = ((0.0, 0.0), None)
+    for k in range(2, parts + 1):
+        for (h, i), (val, _) in best[k - 1].items():
+            for j in range(i + 1, n - (parts - k) + 1):
+                prev_load = (pre[i] - pre[h]) + rc_frac * (pre[j] - pre[i])
+                cand = (max(val[0], prev_load), val[1] + prev_load * prev_load)
+                cur = best[k].get((i, j))
+                if cur is None or cand < cur[0]:
+                    best[k][(i, j)] = (cand, h)
+    final, arg = INF, None
+    for (i, j), (val, h) in best[parts].items():
+        if j != n:
+            continue
+        load = pre[j] - pre[i]
+        cand = (max(val[0], load), val[1] + load * load)
+        if cand < final:
+            final, arg = cand, (i, j)
+    bounds = [n]
+    i, j = arg
     for k in range(parts, 0, -1):
-        j = arg[k][j]
-        bounds.append(j)
+        bounds.append(i)
+        if k > 1:
+            h = best[k][(i, j)][1]
+            i, j = h, i
     return bounds[::-1]
 
 
@@ -299,7 +317,13 @@ def main():
     if stages == 1:
         rc = "off"
     split = stages > 1 and not args.whole_blocks
-    parts = contiguous_partition(stage_costs(cfg, split), stages)
+    def parts_for(arm_rc):
+        # with eager RC every rank but the last also runs its successor's forward: that load is
+        # balanced; every other arm (RC off, lazy) balances the stages alone
+        frac = (1.0 / 3.0) if (arm_rc == "eager" and not args.rc_blind_partition) else 0.0
+        return contiguous_partition(stage_costs(cfg, split), stages, rc_frac=frac)
+
+    parts = parts_for(rc)
     dev = torch.device("cuda", local_rank)
     tokens_per_step = MICRO_BATCH * MICRO_BATCHES * dp * cfg.seq
     base_store = None
@@ -310,7 +334,8 @@ def main():
     def build(arm_rc, tag):
         topo = PipeDataParallelTopology(num_pp=stages, num_dp=dp)
         model = PipelineModule(models.transformer_layer_specs(cfg, 0, split_blocks=split), topology=topo,
-                               loss_fn=models.transformer_loss(cfg), partition_method="custom", custom_partitions=parts)
+                               loss_fn=models.transformer_loss(cfg), partition_method="custom",
+                               custom_partitions=parts_for(arm_rc))
         store = dist.PrefixStore(f"bench-{tag}", base_store) if base_store is not None else None
         engine, *_ = api.initialize(model=model, config={
             "train_micro_batch_size_per_gpu": MICRO_BATCH, "gradient_accumulation_steps": MICRO_BATCHES,
@@ -398,7 +423,8 @@ def main():
         clocks_off = sampler_off.stop()
         off_losses = share_loss(off, "off")
         rc_off = {"tokens_per_s": tokens_per_step * args.steps / (off["ms_dev"] * 1e-3), "ms_per_step": off["ms_dev"] / args.steps,
-                  "loss": off_losses[2 * n_warm] if off_losses else None, "clocks": clocks_off}
+                  "loss": off_losses[2 * n_warm] if off_losses else None, "clocks": clocks_off,
+                  "stage_boundaries": parts_for("off")}
         off["engine"].transport.close()
         del off
         gc.collect()
