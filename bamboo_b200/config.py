@@ -71,6 +71,7 @@ class PipeConfig:
         self.rc_retain_graph = bool(ext.get("rc_retain_graph", True))
         self.p2p_timeout_s = float(ext.get("p2p_timeout_s", 30.0))
         self.rc_stream_priority_low = bool(ext.get("rc_low_priority_stream", True))
+        self.main_stream_high_priority = bool(ext.get("main_stream_high_priority", True))
         # redundant-computation GEMMs as one tile per CTA instead of persistent CTAs (so that a main-
         # stream kernel never waits for a whole tile loop).  Off: measured on 2 GPUs it cost 4 %
         # (308 ms vs 296 ms per step) - the shorter wait does not pay for the slower GEMMs.

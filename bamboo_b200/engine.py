@@ -231,11 +231,17 @@ class PipelineEngine:
         self.rc_stream = None
         self._rc_event = None
         self._lp_refreshed = None
+        self._main_stream = None
         if self.native and self.eager_recovery:
+            # Priorities: the stage's own work runs on a stream of the highest priority, weight
+            # gradients one level below (layers.py), redundant computation at the lowest: whenever
+            # thread blocks of several streams are pending, the GPU places the own stage's first.
+            # (The default stream has the LOWEST priority, so the own work must leave it for the
+            # order to mean anything.)
             lo, hi = torch.cuda.Stream.priority_range() if hasattr(torch.cuda.Stream, "priority_range") else (0, -1)
-            prio = 0 if self._config.rc_stream_priority_low else -1
-            self.rc_stream = torch.cuda.Stream(device=self.device, priority=prio)
-            self._main_priority_stream = torch.cuda.Stream(device=self.device, priority=-1)
+            self.rc_stream = torch.cuda.Stream(device=self.device, priority=lo if self._config.rc_stream_priority_low else hi)
+            if self._config.rc_stream_priority_low and self._config.main_stream_high_priority:
+                self._main_stream = torch.cuda.Stream(device=self.device, priority=hi)
 
         # ---- schedule constructors (composed like the reference: base, RC wrapper, failover wrappers)
         self._sched_layers: List = []  # list of (kind, kwargs) applied on top of TrainSchedule(own stage)
@@ -511,6 +517,20 @@ class PipelineEngine:
     def train_batch(self, data_iter=None, debug=False, mem_status=False, mem_log=False):
         """Run one optimizer step over ``gradient_accumulation_steps`` micro-batches.  Returns
         the mean micro-batch loss on the rank that owns the last stage, 0 elsewhere."""
+        if self._main_stream is None:
+            return self._train_batch(data_iter, debug, mem_status, mem_log)
+        # the step runs on the engine's high-priority stream, fenced on both sides against the
+        # caller's stream (inputs produced there before the call, the returned loss used there after)
+        caller = torch.cuda.current_stream(self.device)
+        self._main_stream.wait_stream(caller)
+        with torch.cuda.stream(self._main_stream):
+            out = self._train_batch(data_iter, debug, mem_status, mem_log)
+        caller.wait_stream(self._main_stream)
+        if torch.is_tensor(out):
+            out.record_stream(caller)
+        return out
+
+    def _train_batch(self, data_iter=None, debug=False, mem_status=False, mem_log=False):
         global should_stop
         self.rdzv_handler.write("/rdzv/cluster_status", "train")
         if should_stop:

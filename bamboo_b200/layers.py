@@ -51,7 +51,10 @@ def _wgrad_stream(device):
     persistent GEMM leaves idle."""
     st = _side_streams.get(device.index)
     if st is None:
-        st = torch.cuda.Stream(device=device)
+        # one level below the highest priority: above redundant computation, below the chain of
+        # input gradients it runs beside
+        lo, hi = torch.cuda.Stream.priority_range()
+        st = torch.cuda.Stream(device=device, priority=min(hi + 1, lo))
         _side_streams[device.index] = st
     return st
 
