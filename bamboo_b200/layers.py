@@ -14,6 +14,7 @@ autograd only carries activation gradients.
 
 There is no fallback: these modules raise on CPU tensors.
 """
+import ctypes
 import math
 from typing import Iterable, List, Optional
 
@@ -272,6 +273,92 @@ class _MLPHalfFn(torch.autograd.Function):
         return (dx1.view(ctx.shape), None) + (None,) * 6
 
 
+# One foreign call per half block (bb_block_half_fwd / bb_block_half_bwd) instead of one per
+# kernel.  False, or an active lib.gemm_hook (per-GEMM timing), selects the per-kernel Functions
+# above; both issue the same kernels in the same order.
+NATIVE_BLOCKS = True
+
+
+def _half_desc(mod, half, T, B, S, need_grads):
+    """The module's cached bb_block_desc for this geometry; rebuilt when its parameters moved
+    (another arena) or the GEMM CTA budget changed."""
+    names = ("ln1_w", "ln1_b", "qkv_w", "qkv_b", "proj_w", "proj_b") if half == L.HALF_ATTENTION else \
+            ("ln2_w", "ln2_b", "fc1_w", "fc1_b", "fc2_w", "fc2_b")
+    params = [getattr(mod, n) for n in names]
+    key = (half, T, B, S, L.GEMM_MAX_CTAS, params[2].data_ptr(), need_grads)
+    cache = mod.__dict__.setdefault("_desc_cache", {})
+    d = cache.get(key)
+    if d is not None:
+        return d
+    h = params[2].shape[1]
+    heads = getattr(mod, "heads", 1)
+    d = L.BlockDesc(tokens=T, batch=B, seq=S, heads=heads, head_dim=h // heads, hidden=h,
+                    ffn=params[2].shape[0] if half == L.HALF_MLP else 0, causal=int(getattr(mod, "causal", True)),
+                    eps=mod.eps, max_ctas=L.GEMM_MAX_CTAS,
+                    ln_w=params[0].data_ptr(), ln_b=params[1].data_ptr(), w1=params[2].data_ptr(), b1=params[3].data_ptr(),
+                    w2=params[4].data_ptr(), b2=params[5].data_ptr())
+    if need_grads:
+        g = [_main_grad(p).data_ptr() for p in params]
+        d.g_ln_w, d.g_ln_b, d.g_w1, d.g_b1, d.g_w2, d.g_b2 = g
+    lib = L.load()
+    d._saved_bytes = lib.bb_block_saved_bytes(ctypes.byref(d), half)
+    d._scratch_bytes = lib.bb_block_scratch_bytes(ctypes.byref(d), half)
+    if d._saved_bytes < 0:
+        raise L.BambooNativeError("bb_block_saved_bytes rejected the block geometry")
+    if len(cache) > 16:
+        cache.clear()
+    cache[key] = d
+    return d
+
+
+class _HalfFn(torch.autograd.Function):
+    """Half a pre-LN block through one native call each way: x + proj(attention(LN1(x))) or
+    x + fc2(gelu(fc1(LN2(x))))."""
+
+    @staticmethod
+    def forward(ctx, x, mod, half, *params):
+        _require_cuda(x, "transformer block")
+        shape = x.shape
+        h = shape[-1]
+        x2 = x.reshape(-1, h)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        T = x2.shape[0]
+        B, S = (shape[0], shape[1]) if x.dim() == 3 else (1, T)
+        d = _half_desc(mod, half, T, B, S, False)
+        saved = torch.empty(d._saved_bytes, dtype=torch.uint8, device=x.device)
+        out = torch.empty(T, h, dtype=torch.bfloat16, device=x.device)
+        L.block_half_fwd(d, half, x2, saved, out)
+        ctx.mod, ctx.half, ctx.geom, ctx.shape = mod, half, (T, B, S), shape
+        ctx.save_for_backward(x2, saved)
+        return out.view(shape)
+
+    @staticmethod
+    def backward(ctx, dout):
+        x2, saved = ctx.saved_tensors
+        T, B, S = ctx.geom
+        h = x2.shape[1]
+        d2 = dout.reshape(-1, h)
+        if not d2.is_contiguous():
+            d2 = d2.contiguous()
+        d = _half_desc(ctx.mod, ctx.half, T, B, S, True)
+        scratch = torch.empty(d._scratch_bytes, dtype=torch.uint8, device=x2.device)
+        dx = torch.empty(T, h, dtype=torch.bfloat16, device=x2.device)
+        side = None
+        if WGRAD_SIDE_STREAM:
+            st = _wgrad_stream(x2.device)
+            side = st.cuda_stream
+            # operands of the weight-gradient kernels: not to be handed out again before that stream is done
+            for t in (d2, saved, scratch):
+                t.record_stream(st)
+        L.block_half_bwd(d, ctx.half, x2, saved, d2, dx, scratch, side)
+        return (dx.view(ctx.shape), None, None) + (None,) * 6
+
+
+def _use_native_blocks():
+    return NATIVE_BLOCKS and L.gemm_hook is None
+
+
 class _EmbeddingFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, tokens, mod, wte, wpe):
@@ -452,6 +539,11 @@ class TransformerBlock(nn.Module):
         self.fc2_w = nn.Parameter(_normal((hidden, ffn), g)); self.fc2_b = nn.Parameter(torch.zeros(hidden))
 
     def forward(self, x):
+        if _use_native_blocks():
+            x1 = _HalfFn.apply(x, self, L.HALF_ATTENTION, self.ln1_w, self.ln1_b, self.qkv_w, self.qkv_b, self.proj_w,
+                               self.proj_b)
+            return _HalfFn.apply(x1, self, L.HALF_MLP, self.ln2_w, self.ln2_b, self.fc1_w, self.fc1_b, self.fc2_w,
+                                 self.fc2_b)
         return _BlockFn.apply(x, self, self.ln1_w, self.ln1_b, self.qkv_w, self.qkv_b, self.proj_w, self.proj_b,
                               self.ln2_w, self.ln2_b, self.fc1_w, self.fc1_b, self.fc2_w, self.fc2_b)
 
@@ -471,6 +563,9 @@ class AttentionHalf(nn.Module):
         self.proj_w = nn.Parameter(_normal((hidden, hidden), g)); self.proj_b = nn.Parameter(torch.zeros(hidden))
 
     def forward(self, x):
+        if _use_native_blocks():
+            return _HalfFn.apply(x, self, L.HALF_ATTENTION, self.ln1_w, self.ln1_b, self.qkv_w, self.qkv_b, self.proj_w,
+                                 self.proj_b)
         return _AttnHalfFn.apply(x, self, self.ln1_w, self.ln1_b, self.qkv_w, self.qkv_b, self.proj_w, self.proj_b)
 
 
@@ -487,6 +582,8 @@ class MLPHalf(nn.Module):
         self.fc2_w = nn.Parameter(_normal((hidden, ffn), g)); self.fc2_b = nn.Parameter(torch.zeros(hidden))
 
     def forward(self, x):
+        if _use_native_blocks():
+            return _HalfFn.apply(x, self, L.HALF_MLP, self.ln2_w, self.ln2_b, self.fc1_w, self.fc1_b, self.fc2_w, self.fc2_b)
         return _MLPHalfFn.apply(x, self, self.ln2_w, self.ln2_b, self.fc1_w, self.fc1_b, self.fc2_w, self.fc2_b)
 
 

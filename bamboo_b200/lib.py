@@ -36,6 +36,24 @@ class GemmDesc(ctypes.Structure):
     ]
 
 
+class BlockDesc(ctypes.Structure):
+    """bb_block_desc: one half of a transformer block (see include/bamboo_b200.h)."""
+    _fields_ = [
+        ("tokens", ctypes.c_int), ("batch", ctypes.c_int), ("seq", ctypes.c_int), ("heads", ctypes.c_int),
+        ("head_dim", ctypes.c_int), ("hidden", ctypes.c_int), ("ffn", ctypes.c_int), ("causal", ctypes.c_int),
+        ("eps", ctypes.c_float), ("max_ctas", ctypes.c_int),
+        ("ln_w", ctypes.c_void_p), ("ln_b", ctypes.c_void_p), ("w1", ctypes.c_void_p), ("b1", ctypes.c_void_p),
+        ("w2", ctypes.c_void_p), ("b2", ctypes.c_void_p),
+        ("g_ln_w", ctypes.c_void_p), ("g_ln_b", ctypes.c_void_p), ("g_w1", ctypes.c_void_p), ("g_b1", ctypes.c_void_p),
+        ("g_w2", ctypes.c_void_p), ("g_b2", ctypes.c_void_p),
+    ]
+
+
+HALF_ATTENTION, HALF_MLP = 0, 1
+# kernels behind one call of bb_block_half_fwd / bb_block_half_bwd, per half (launch accounting)
+HALF_FWD_LAUNCHES = {HALF_ATTENTION: 4, HALF_MLP: 3}
+HALF_BWD_LAUNCHES = {HALF_ATTENTION: 14, HALF_MLP: 11}
+
 _lib = None
 _lock = threading.Lock()
 # number of kernels launched through this binding (benchmarks report it)
@@ -59,6 +77,8 @@ def load():
         lib = ctypes.CDLL(LIB_PATH)
         lib.bb_last_error.restype = ctypes.c_char_p
         lib.bb_version.restype = ctypes.c_int
+        lib.bb_block_saved_bytes.restype = ctypes.c_longlong
+        lib.bb_block_scratch_bytes.restype = ctypes.c_longlong
         _lib = lib
     return _lib
 
@@ -310,3 +330,22 @@ def cast_f32_to_bf16(src, dst):
     LAUNCHES += 1
     check(load().bb_cast_f32_to_bf16(_ptr(src), _ptr(dst), _LL(src.numel()), _stream()), "bb_cast_f32_to_bf16")
     return dst
+
+
+def block_half_fwd(desc, half, x, saved, out):
+    global LAUNCHES
+    LAUNCHES += HALF_FWD_LAUNCHES[half]
+    check(load().bb_block_half_fwd(ctypes.byref(desc), _I(half), _ptr(x), _ptr(saved), _ptr(out), _stream()),
+          "bb_block_half_fwd")
+    return out
+
+
+def block_half_bwd(desc, half, x, saved, dout, dx, scratch, side_stream=None):
+    """``side_stream``: raw handle of the stream for the weight gradients (None: the current stream)."""
+    global LAUNCHES
+    LAUNCHES += HALF_BWD_LAUNCHES[half]
+    main = _stream()
+    side = main if side_stream is None else ctypes.c_void_p(side_stream)
+    check(load().bb_block_half_bwd(ctypes.byref(desc), _I(half), _ptr(x), _ptr(saved), _ptr(dout), _ptr(dx), _ptr(scratch),
+                                   _LL(scratch.numel()), main, side), "bb_block_half_bwd")
+    return dx

@@ -160,6 +160,38 @@ int bb_cross_entropy_bwd(const void* logits, long long ld, const long long* targ
  * (DeepSpeedExamples/pipeline_parallelism/bert.py:126-147) stops before the language-model head. */
 int bb_gelu_bwd(const void* dy, const void* pre, void* dx, long long n, void* stream);
 
+/* ---- whole transformer half-blocks ------------------------------------------------- */
+/* One call issues every kernel of half a pre-LN transformer block, so the host pays for one
+ * foreign call instead of one per kernel (the Python host of a pipeline stage otherwise spends
+ * more time issuing a micro-batch than the GPU needs to run it).  Same kernels, same order and
+ * same arithmetic as calling the entry points above one by one.
+ *   attention half:  out = x + proj(attention(qkv(LN1(x))))
+ *   MLP half:        out = x + fc2(gelu(fc1(LN2(x))))
+ * `saved` (bb_block_saved_bytes) receives what the backward pass needs; the backward entry
+ * points write dx, accumulate every weight / bias / LayerNorm gradient into the fp32 pointers of
+ * the descriptor and use `scratch` (bb_block_scratch_bytes) for intermediates.  Weight gradients
+ * are issued on `side_stream` behind an event recorded on `stream` (pass the same stream twice
+ * to keep everything in order on one stream).
+ * Replaces: one layer call of PipelineModule.forward (DS/runtime/pipe/module.py:516-574; block
+ * body EX/pipeline_parallelism/gpt2.py:66-121) and its share of loss.backward()
+ * (DS/runtime/pipe/engine.py:1680-1727). */
+enum { BB_HALF_ATTENTION = 0, BB_HALF_MLP = 1 };
+typedef struct bb_block_desc {
+  int tokens, batch, seq, heads, head_dim, hidden, ffn, causal;
+  float eps;
+  int max_ctas;                      /* forwarded to every GEMM (see bb_gemm_desc.max_ctas) */
+  /* bf16 parameters: LayerNorm gain/bias, then the two linear layers of the half
+   * (attention: qkv [3h,h], proj [h,h]; MLP: fc1 [ffn,h], fc2 [h,ffn]) with their biases */
+  const void *ln_w, *ln_b, *w1, *b1, *w2, *b2;
+  /* fp32 gradient accumulators of the same parameters (backward only) */
+  float *g_ln_w, *g_ln_b, *g_w1, *g_b1, *g_w2, *g_b2;
+} bb_block_desc;
+long long bb_block_saved_bytes(const bb_block_desc* d, int half);
+long long bb_block_scratch_bytes(const bb_block_desc* d, int half);
+int bb_block_half_fwd(const bb_block_desc* d, int half, const void* x, void* saved, void* out, void* stream);
+int bb_block_half_bwd(const bb_block_desc* d, int half, const void* x, const void* saved, const void* dout, void* dx,
+                      void* scratch, long long scratch_bytes, void* stream, void* side_stream);
+
 /* ---- optimizer -------------------------------------------------------------------- */
 /* One Adam / AdamW step over a flat parameter arena: fp32 master weights, gradient and
  * moments; refreshes the bf16 working copy (may be NULL) and optionally clears the
