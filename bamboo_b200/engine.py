@@ -232,16 +232,18 @@ class PipelineEngine:
         self._rc_event = None
         self._lp_refreshed = None
         self._main_stream = None
-        if self.native and self.eager_recovery:
+        if self.native:
             # Priorities: the stage's own work runs on a stream of the highest priority, weight
             # gradients one level below (layers.py), redundant computation at the lowest: whenever
             # thread blocks of several streams are pending, the GPU places the own stage's first.
             # (The default stream has the LOWEST priority, so the own work must leave it for the
             # order to mean anything.)
             lo, hi = torch.cuda.Stream.priority_range() if hasattr(torch.cuda.Stream, "priority_range") else (0, -1)
-            self.rc_stream = torch.cuda.Stream(device=self.device, priority=lo if self._config.rc_stream_priority_low else hi)
-            if self._config.rc_stream_priority_low and self._config.main_stream_high_priority:
+            if self._config.main_stream_high_priority:
                 self._main_stream = torch.cuda.Stream(device=self.device, priority=hi)
+            if self.eager_recovery:
+                self.rc_stream = torch.cuda.Stream(device=self.device,
+                                                   priority=lo if self._config.rc_stream_priority_low else hi)
 
         # ---- schedule constructors (composed like the reference: base, RC wrapper, failover wrappers)
         self._sched_layers: List = []  # list of (kind, kwargs) applied on top of TrainSchedule(own stage)
