@@ -81,6 +81,9 @@ class PipeConfig:
         v = int(ext.get("rc_max_ctas", RC_MAX_CTAS_DEFAULT))
         self.rc_max_ctas = RC_MAX_CTAS_DEFAULT if v == -2 else v
         self.shadow_sync = bool(ext.get("shadow_sync", True))
+        # redundant forwards are handed to the GPU layer by layer while the host waits for a
+        # neighbour's message with the main stream drained, the remainder at the end of the batch
+        self.rc_deferred = bool(ext.get("rc_deferred", True))
 
     def adam_args(self):
         p = self.optimizer_params

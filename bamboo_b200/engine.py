@@ -129,8 +129,10 @@ def _decode(v):
 class PipelineEngine:
     def __init__(self, model: PipelineModule, config=None, redundancy_level=0, sync_save=False, eager_recovery=False,
                  training_data=None, collate_fn=None, rdzv_handler=None, store=None, transport=None, dist=None,
-                 lr_scheduler=None):
+                 lr_scheduler=None, prev_state=None):
         assert isinstance(model, PipelineModule), "model must base PipelineModule"
+        self._init_args = dict(config=config, redundancy_level=redundancy_level, sync_save=sync_save,
+                               eager_recovery=eager_recovery, collate_fn=collate_fn, lr_scheduler=lr_scheduler)
         self.module = model
         self.grid = model._grid
         self.device = model.device
@@ -209,7 +211,6 @@ class PipelineEngine:
 
         self.init_redundancy()
         self.init_pipe_buffers()
-
         self.data_iterator = None
         self.training_dataloader = None
         self.batch_fn = None
@@ -252,6 +253,15 @@ class PipelineEngine:
         self._seq = collections.Counter()
         self._fwd_done: Dict[Tuple[int, int], object] = {}   # (stage, buffer) -> event behind that forward
         self._shadow_ctx = False        # True while an instruction of a redundant-work group executes
+        self._rc_queue = collections.deque()                  # redundant forwards not yet (fully) issued
+        if self.rc_stream is not None and hasattr(self.transport, "idle_hook") and self._config.rc_deferred:
+            self.transport.idle_hook = self._rc_pump
+
+        # not the first rendezvous of the run: some member already trained; fetch the layers of this
+        # rank's new seat from whoever held them (reference: pipe/engine.py:149-165)
+        decision = self.rdzv_handler.get_global_decision()
+        if self.dist is not None and self.world_size > 1 and any(len(i.previous_coordinates) for i in decision):
+            self._join_from_previous(decision, prev_state or {})
 
     # ------------------------------------------------------------------ helpers
     def _inc(self, s):
@@ -439,6 +449,7 @@ class PipelineEngine:
             raise RuntimeError(f"the shadow copy of stage {nxt} missed a state transfer (its owner stopped answering "
                                "in the middle of one) and cannot be promoted; restart from a checkpoint")
         t0 = time.time()
+        self._rc_pump(everything=True)
         if self.rc_stream is not None:
             # redundant forwards and the shadow's working-copy refresh are ordered on the RC stream
             torch.cuda.current_stream().wait_stream(self.rc_stream)
@@ -548,7 +559,8 @@ class PipelineEngine:
         self.total_loss = None
         self._compute_loss = True
         if not self.join and self.rdzv_handler.should_reconfigure(self.global_steps, failures):
-            raise PipelineError("cluster reconfiguration (re-rendezvous with layer transfer) is not built yet")
+            self._reconfigure(failures)
+            failures = {}
         self.check_preemptions(failures)
         self.join = False
 
@@ -565,6 +577,7 @@ class PipelineEngine:
             kind, kw = self._sched_layers[-1]
             kw["failed_step"], kw["curr_step"] = 0, 0
 
+        self._rc_pump(everything=True)
         self.agg_train_loss = self._aggregate_total_loss()
         self.transport.end_step()
         elapsed = time.time() - t_start
@@ -575,6 +588,124 @@ class PipelineEngine:
                   f"samples/sec: {self.train_batch_size() / max(elapsed, 1e-9):0.3f}", flush=True)
         self._clean_pipe_buffers()
         return self.agg_train_loss
+
+    # ------------------------------------------------------------------ re-partitioning
+    def get_model_state(self):
+        """``{layer index: [params {name: fp32 tensor}, [{"exp_avg": t, "exp_avg_sq": t}, ...]]}`` of
+        every stage this rank owns: views into the arenas (reference ``get_model_state``,
+        ``pipe/engine.py:565-572``, which hands out per-layer ``state_dict`` and optimizer state)."""
+        from .checkpoint import _named_slices
+        state = {}
+        for sid in self.stage_ids:
+            arena = self.arenas[sid]
+            if self.native:
+                self._join_wgrad_stream()
+            for name, off, n, shape in _named_slices(self, arena, sid):
+                layer_key, pname = name.split(".", 1)
+                if not layer_key.isdigit():
+                    continue                               # tied modules keep their own copy on every stage
+                entry = state.setdefault(int(layer_key), [collections.OrderedDict(), []])
+                entry[0][pname] = arena.master[off:off + n].view(shape)
+                entry[1].append({"exp_avg": arena.exp_avg[off:off + n].view(shape),
+                                 "exp_avg_sq": arena.exp_avg_sq[off:off + n].view(shape)})
+        return state
+
+    def _load_model_state(self, state, stage_ids=None):
+        """Fill the arenas of the given stages (default: the owned ones) from per-layer state."""
+        from .checkpoint import _named_slices
+        loaded = set()
+        with torch.no_grad():
+            for sid in (self.stage_ids if stage_ids is None else stage_ids):
+                arena = self.arenas[sid]
+                seen = collections.Counter()
+                for name, off, n, shape in _named_slices(self, arena, sid):
+                    layer_key, pname = name.split(".", 1)
+                    if not layer_key.isdigit() or int(layer_key) not in state:
+                        continue
+                    params, moments = state[int(layer_key)]
+                    k = seen[layer_key]
+                    seen[layer_key] += 1
+                    arena.master[off:off + n].copy_(params[pname].reshape(-1))
+                    if arena.exp_avg is not None and k < len(moments):
+                        arena.exp_avg[off:off + n].copy_(moments[k]["exp_avg"].reshape(-1))
+                        arena.exp_avg_sq[off:off + n].copy_(moments[k]["exp_avg_sq"].reshape(-1))
+                    loaded.add(int(layer_key))
+                arena.refresh_lp()
+                arena.step_count = self.global_steps
+        return loaded
+
+    def _join_from_previous(self, decision, prev_state):
+        from . import reconfigure as R
+        from .checkpoint import _named_slices
+        self.join = True
+        self.global_steps = self.rdzv_handler.get_current_step()
+        prev_stages = max(s for info in decision for _, s in info.previous_coordinates) + 1
+        if prev_stages == self.num_stages:
+            old_parts = list(self.module.parts)
+        else:
+            old_parts = self.module.get_new_partition(prev_stages)
+        recv = R.get_recv_decisions(old_parts, self.module.parts, decision)
+        send = R.get_send_decisions(recv)
+        shapes = {}
+        for name, off, n, shape in _named_slices(self, self.arenas[self.stage_id], self.stage_id):
+            layer_key, pname = name.split(".", 1)
+            if layer_key.isdigit():
+                shapes.setdefault(int(layer_key), collections.OrderedDict())[pname] = tuple(shape)
+        t0 = time.time()
+        received = R.transfer_layers(self.dist, self.global_rank, self.world_size, recv, send, prev_state, shapes,
+                                     device=self.device)
+        state = dict(received)
+        state.update(prev_state)                      # what this rank already held wins, like the reference
+        need = set(range(self.module.parts[self.stage_id], self.module.parts[self.stage_id + 1])) & set(shapes)
+        loaded = self._load_model_state(state, [self.stage_id])
+        missing = need - loaded
+        if missing:
+            raise PipelineError(f"re-partition left layers {sorted(missing)} of stage {self.stage_id} without state")
+        self.timers["layer_transfer_s"] = time.time() - t0
+        self.log(f"joined at step {self.global_steps}: received layers {sorted(received)} "
+                 f"in {self.timers['layer_transfer_s']:.3f} s")
+        # shadow copies restart from their owners' state
+        self._sync_shadow_state()
+
+    def _reconfigure(self, failures):
+        """The rendezvous decided to re-form the cluster at this step (a member holding two stages
+        is about to leave, or waiting members make another pipeline): re-join, rebuild the
+        process group and the pipeline module for the new grid, move layers to their new owners
+        and continue from the same optimisation state (reference: ``pipe/engine.py:1129-1164``,
+        ``reconfigure_cluster`` ``:630-658``)."""
+        import torch.distributed as tdist
+        from .topology import PipeDataParallelTopology
+        if failures.get(str(self.global_rank), -1) == self.global_steps:
+            self.log("We are reconfiguring and I will die soon anyway. I'm leaving")
+            self.global_store.set(str(self.global_rank), "1")
+            self.transport.close()
+            sys.exit(13)
+        state = self.get_model_state()
+        state = {k: [collections.OrderedDict((n, t.clone()) for n, t in v[0].items()),
+                     [{kk: tt.clone() for kk, tt in m.items()} for m in v[1]]] for k, v in state.items()}
+        self.log(f"Triggered a reconfiguration on global step {self.global_steps}")
+        store, rank, world, num_pipelines, num_stages, decision = self.rdzv_handler.next_rendezvous(self.global_rank)
+        for info in decision:
+            if info.rank == rank and len(info.active_coordinates) == 0:
+                self.log("-------- I'M LEAVING!!")
+                sys.exit(125)
+        self.rdzv_handler.write("/rdzv/cluster_status", "init")
+        self.rdzv_handler.write("/rdzv/last_reconfig", self.global_steps)
+        self.transport.close()
+        backend = tdist.get_backend()
+        tdist.destroy_process_group()
+        tdist.init_process_group(backend, store=store, rank=rank, world_size=world)
+        old = self.module
+        topo = PipeDataParallelTopology(num_pp=num_stages, num_dp=num_pipelines, custom_mapping=decision)
+        model = PipelineModule(layers=old._layer_specs, loss_fn=old.loss_fn, topology=topo,
+                               partition_method=old.partition_method,
+                               activation_checkpoint_interval=old.activation_checkpoint_interval, device=self.device)
+        keep = (self.data_iterator, self.training_dataloader, self.batch_fn, self.rdzv_handler)
+        args = dict(self._init_args)
+        cfg = args.pop("config")
+        raw = cfg._raw if isinstance(cfg, PipeConfig) else cfg
+        self.__init__(model, PipeConfig(raw, num_pipelines), rdzv_handler=keep[3], prev_state=state, **args)
+        self.data_iterator, self.training_dataloader, self.batch_fn = keep[:3]
 
     def _handle_detected_failure(self, status):
         """A neighbour stopped answering in the middle of a batch (``status`` = (step index,
@@ -725,15 +856,13 @@ class PipelineEngine:
             label = self.pipe_buffers["label"][buffer_id] if stage_id == self.num_stages - 1 else None
             if torch.is_tensor(label) and label.is_cuda:
                 label.record_stream(self.rc_stream)
-            from . import lib as _lib
-            with torch.cuda.stream(self.rc_stream):
-                # SM budget of the redundant GEMMs (bb_gemm_desc.max_ctas): -1 = one unit per CTA
-                _lib.GEMM_MAX_CTAS = -1 if self._config.rc_short_ctas else self._config.rc_max_ctas
-                try:
-                    self._forward_stage(inputs, buffer_id, stage_id, retain=self._config.rc_retain_graph)
-                finally:
-                    _lib.GEMM_MAX_CTAS = 0
-                self._rc_event = self.rc_stream.record_event()
+            if self._config.rc_deferred and hasattr(self.transport, "idle_hook"):
+                # issued layer by layer whenever the host finds the main stream idle (waiting for a
+                # neighbour's message), the rest at the end of the batch: see _rc_pump
+                self._rc_queue.append(self._rc_forward_chunks(inputs, label, buffer_id, stage_id))
+            else:
+                for _ in self._rc_forward_chunks(inputs, label, buffer_id, stage_id):
+                    pass
         else:
             self._forward_stage(inputs, buffer_id, stage_id, retain=(not shadow) or self._config.rc_retain_graph)
             if self.rc_stream is not None and not shadow and self._inc(stage_id) in self.r_stage_ids:
@@ -742,6 +871,47 @@ class PipelineEngine:
             self.pipe_buffers["data"][buffer_id] = None
         if stage_id == self.num_stages - 1:
             self.pipe_buffers["label"][buffer_id] = None
+
+    def _rc_forward_chunks(self, inputs, label, buffer_id, stage_id):
+        """A redundant forward as a generator: every ``next()`` issues one layer of the shadow
+        stage on the redundant-computation stream; the last one stores the stage's output (or its
+        loss).  Issuing it in pieces lets the host hand the GPU redundant work only while the own
+        stage has nothing to run."""
+        from . import lib as _lib
+        retain = self._config.rc_retain_graph
+        last = stage_id == self.num_stages - 1
+        budget = -1 if self._config.rc_short_ctas else self._config.rc_max_ctas
+        x = tuple(t.clone() for t in inputs) if isinstance(inputs, tuple) else inputs
+        for f in self.module.func_buckets[stage_id]:
+            with torch.cuda.stream(self.rc_stream), (torch.enable_grad() if retain else torch.no_grad()):
+                _lib.GEMM_MAX_CTAS = budget     # SM budget of the redundant GEMMs (bb_gemm_desc.max_ctas)
+                try:
+                    x = f(x)
+                finally:
+                    _lib.GEMM_MAX_CTAS = 0
+            yield
+        with torch.cuda.stream(self.rc_stream), (torch.enable_grad() if retain else torch.no_grad()):
+            if not last:
+                self.pipe_buffers[f"output_{stage_id}"][buffer_id] = x
+            else:
+                self._losses[(buffer_id, stage_id)] = (self.loss_model(x, label)
+                                                       if self._compute_loss and self.loss_model is not None else x)
+            self._rc_event = self.rc_stream.record_event()
+        yield
+
+    def _rc_pump(self, everything=False):
+        """Issue one pending chunk of redundant work (or all of it).  Called by the transport while
+        the host waits for a message and the main stream has drained, by the end of the batch and
+        before anything that needs the redundant results."""
+        while self._rc_queue:
+            try:
+                next(self._rc_queue[0])
+            except StopIteration:
+                self._rc_queue.popleft()
+                continue
+            if not everything:
+                return True
+        return False
 
     def _forward_stage(self, inputs, buffer_id, stage_id, retain=True):
         ctx = torch.enable_grad() if retain else torch.no_grad()
@@ -909,6 +1079,9 @@ class PipelineEngine:
     def _sync_shadow_state(self):
         """End of step: every live stage ships (weights, exp_avg, exp_avg_sq) to the rank that
         shadows it, and the shadow's working copy is refreshed."""
+        # redundant forwards of this batch read the shadow's working copy: all of them are issued
+        # before the refresh that follows on their stream
+        self._rc_pump(everything=True)
         if self.redundancy_level == 0 or self.num_stages == 1 or not self._config.shadow_sync:
             return
         # after a failover the ring is broken at the dead rank: only intact pairs keep syncing

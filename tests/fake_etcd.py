@@ -235,7 +235,9 @@ class Lock:
 
     def __init__(self, client, lock_name):
         with Lock._guard:
-            self._lock = Lock._locks.setdefault((id(client.server), lock_name), threading.Lock())
+            # a client that is a proxy of a server in another process has no `server`: the lock is
+            # then local to this process
+            self._lock = Lock._locks.setdefault((id(getattr(client, "server", client)), lock_name), threading.Lock())
         self.is_taken = False
 
     def acquire(self, blocking=True, lock_ttl=3600, timeout=0):
@@ -247,3 +249,40 @@ class Lock:
             self._lock.release()
             self.is_taken = False
         return True
+
+
+# ---------------------------------------------------------------------------------- across processes
+# One key space for several worker processes: a manager process holds the Server, workers get
+# proxies of a Client in front of it (results and exceptions travel by pickle).
+from multiprocessing.managers import BaseManager  # noqa: E402
+
+_SHARED = None
+
+
+def _shared_client():
+    global _SHARED
+    if _SHARED is None:
+        _SHARED = Server()
+    return Client(_SHARED)
+
+
+class EtcdManager(BaseManager):
+    pass
+
+
+EtcdManager.register("Client", callable=_shared_client,
+                     exposed=("get", "read", "write", "set", "update", "test_and_set", "refresh", "delete", "watch"))
+
+
+def start_shared_server(authkey=b"fake-etcd"):
+    """Starts the manager process; returns (manager, address).  Workers call ``connect(address)``."""
+    import multiprocessing as mp
+    mgr = EtcdManager(address=("127.0.0.1", 0), authkey=authkey, ctx=mp.get_context("spawn"))
+    mgr.start()
+    return mgr, mgr.address
+
+
+def connect(address, authkey=b"fake-etcd"):
+    mgr = EtcdManager(address=tuple(address), authkey=authkey)
+    mgr.connect()
+    return mgr.Client()
