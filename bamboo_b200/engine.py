@@ -909,6 +909,7 @@ class PipelineEngine:
             except StopIteration:
                 self._rc_queue.popleft()
                 continue
+            self.instr_counts["rc_chunks_flushed" if everything else "rc_chunks_in_idle_time"] += 1
             if not everything:
                 return True
         return False

@@ -76,8 +76,10 @@ class MailboxTransport:
         # called while the host waits for a message and the stream has drained up to the wait:
         # the engine uses it to issue redundant computation into the otherwise idle GPU
         self.idle_hook = None
+        self.measure_idle = False
         self._pre_wait = None
         self.wait_s = 0.0            # host time spent waiting for receives (per-step figure for benchmarks)
+        self.idle_s = 0.0            # part of it during which the stream had drained up to the wait
 
     # ------------------------------------------------------------------ channel set-up
     def _key(self, what, src, dst, kind):
@@ -165,19 +167,25 @@ class MailboxTransport:
         spins = 0
         hook, pre = self.idle_hook, self._pre_wait
         self._pre_wait = None
+        drained_at = None
         while True:
             v = done.value
             if (v & 0xFFFFFFFF) == ticket:
                 break
             spins += 1
-            if hook is not None and (spins & 0x1F) == 0 and (pre is None or pre.query()):
+            if pre is not None and (spins & 0x1F) == 0 and (drained_at is not None or pre.query()):
                 # everything queued before the wait has run: the stream now sits in the wait kernel
-                if not hook():
+                if drained_at is None:
+                    drained_at = time.perf_counter()
+                if hook is not None and not hook():
                     hook = None
             if (spins & 0xFFF) == 0 and time.perf_counter() > limit:
                 raise L.BambooNativeError(f"no completion record for a receive from rank {peer} "
                                           f"after {2.0 * self.timeout_s + 30.0:.0f} s")
-        self.wait_s += time.perf_counter() - t0
+        now = time.perf_counter()
+        self.wait_s += now - t0
+        if drained_at is not None:
+            self.idle_s += now - drained_at      # the GPU's own-stage stream had nothing but the wait
         status = v >> 32
         if status == 0:
             return
@@ -208,7 +216,7 @@ class MailboxTransport:
         for d in ch.shape:
             numel *= d
         raw = torch.empty(ch.nbytes, dtype=torch.uint8, device=self.device)
-        if self.idle_hook is not None:
+        if self.idle_hook is not None or self.measure_idle:
             self._pre_wait = torch.cuda.Event()
             self._pre_wait.record()
         self._wait_copy(ch, slot, raw.data_ptr(), ch.nbytes, seq)

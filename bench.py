@@ -390,7 +390,17 @@ def main():
         timed(host[:n_warm], read_loss=True)
         n0 = lib.LAUNCHES
         wait0 = getattr(engine.transport, "wait_s", 0.0)
+        idle0 = getattr(engine.transport, "idle_s", 0.0)
+        if hasattr(engine.transport, "measure_idle"):
+            engine.transport.measure_idle = True
+        c0 = dict(engine.instr_counts)
         ms_dev = timed(resident, read_loss=False)
+        idle_ms = (getattr(engine.transport, "idle_s", 0.0) - idle0) * 1e3 / args.steps
+        print(f"# rank {rank} arm {arm_rc}: {ms_dev / args.steps:.1f} ms/step, host issue {info['issue_ms'] / args.steps:.1f} ms, "
+              f"waiting for messages {(getattr(engine.transport, 'wait_s', 0.0) - wait0) * 1e3 / args.steps:.1f} ms of which "
+              f"with the stream drained {idle_ms:.1f} ms; redundant chunks in idle time "
+              f"{engine.instr_counts.get('rc_chunks_in_idle_time', 0) - c0.get('rc_chunks_in_idle_time', 0)}, flushed "
+              f"{engine.instr_counts.get('rc_chunks_flushed', 0) - c0.get('rc_chunks_flushed', 0)}", file=sys.stderr, flush=True)
         issue_ms = info["issue_ms"] / args.steps
         recv_wait_ms = (getattr(engine.transport, "wait_s", 0.0) - wait0) * 1e3 / args.steps
         launches = lib.LAUNCHES - n0

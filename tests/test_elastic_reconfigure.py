@@ -91,6 +91,8 @@ def _member(idx, address, late, queue):
 def test_job_grows_from_one_pipeline_to_two():
     import fake_etcd
     mgr, address = fake_etcd.start_shared_server()
+    # what the launcher publishes before any member joins: the number of stages of a pipeline
+    fake_etcd.connect(address).write(f"{PREFIX}/run_{RUN}/rdzv/default_pipelines", "2")
     ctx = mp.get_context("spawn")
     queue = ctx.Queue()
     procs = [ctx.Process(target=_member, args=(i, address, i >= 2, queue)) for i in range(4)]
