@@ -41,6 +41,7 @@ from .p2p import ACT, GRAD, DistTransport, NullTransport, PeerTimeout
 from .partition import get_redundant_stage_ids, get_redundant_user_stage_ids
 
 should_stop = False
+_live_stores = []
 
 
 def sig_handler(signum, frame):
@@ -695,6 +696,9 @@ class PipelineEngine:
         backend = tdist.get_backend()
         tdist.destroy_process_group()
         tdist.init_process_group(backend, store=store, rank=rank, world_size=world)
+        # the process group holds the store through its C++ base only; the Python object (whose
+        # methods it calls back) has to be kept alive on this side
+        _live_stores.append(store)
         old = self.module
         topo = PipeDataParallelTopology(num_pp=num_stages, num_dp=num_pipelines, custom_mapping=decision)
         model = PipelineModule(layers=old._layer_specs, loss_fn=old.loss_fn, topology=topo,

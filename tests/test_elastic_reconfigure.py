@@ -43,10 +43,11 @@ def _member(idx, address, late, queue):
         torch.set_num_threads(1)
         client = fake_etcd.connect(address)
         if late:
-            # newcomers show up once the first two are training
+            # newcomers show up while the first two run the step before the one at which the job is to
+            # grow (the decision of a step records its number as rdzv/current_step)
             while True:
                 try:
-                    if json.loads(client.get(f"{PREFIX}/run_{RUN}/rdzv/active_version").value)["status"] == "final":
+                    if json.loads(client.get(f"{PREFIX}/run_{RUN}/rdzv/current_step").value) >= GROW_AT - 1:
                         break
                 except Exception:
                     pass
