@@ -84,6 +84,7 @@ class PipeConfig:
         # redundant forwards are handed to the GPU layer by layer while the host waits for a
         # neighbour's message with the main stream drained, the remainder at the end of the batch
         self.rc_deferred = bool(ext.get("rc_deferred", True))
+        self.rc_chunks_in_flight = int(ext.get("rc_chunks_in_flight", 2))
 
     def adam_args(self):
         p = self.optimizer_params

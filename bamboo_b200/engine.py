@@ -255,7 +255,7 @@ class PipelineEngine:
         self._fwd_done: Dict[Tuple[int, int], object] = {}   # (stage, buffer) -> event behind that forward
         self._shadow_ctx = False        # True while an instruction of a redundant-work group executes
         self._rc_queue = collections.deque()                  # redundant forwards not yet (fully) issued
-        self._rc_inflight = None                              # event behind the chunk issued last in idle time
+        self._rc_inflight = collections.deque()               # events behind the chunks issued in idle time
         if self.rc_stream is not None and hasattr(self.transport, "idle_hook") and self._config.rc_deferred:
             self.transport.idle_hook = self._rc_pump
 
@@ -908,12 +908,13 @@ class PipelineEngine:
         """Issue one pending chunk of redundant work (or all of it).  Called by the transport while
         the host waits for a message and the main stream has drained, by the end of the batch and
         before anything that needs the redundant results."""
-        if not everything and self._rc_inflight is not None:
-            # at most one chunk ahead of the GPU: whatever is already queued on the redundant stream
-            # would compete with the own stage's kernels once the awaited message arrives
-            if not self._rc_inflight.query():
+        if not everything:
+            # a bounded number of chunks ahead of the GPU: whatever is already queued on the redundant
+            # stream competes with the own stage's kernels once the awaited message arrives
+            while self._rc_inflight and self._rc_inflight[0].query():
+                self._rc_inflight.popleft()
+            if len(self._rc_inflight) >= self._config.rc_chunks_in_flight:
                 return bool(self._rc_queue)
-            self._rc_inflight = None
         while self._rc_queue:
             try:
                 next(self._rc_queue[0])
@@ -922,7 +923,7 @@ class PipelineEngine:
                 continue
             self.instr_counts["rc_chunks_flushed" if everything else "rc_chunks_in_idle_time"] += 1
             if not everything:
-                self._rc_inflight = self.rc_stream.record_event()
+                self._rc_inflight.append(self.rc_stream.record_event())
                 return True
         return False
 

@@ -49,6 +49,8 @@ def parse():
                     help="SM budget of a redundant-computation GEMM (see bamboo_b200.rc_max_ctas; -2 = library default)")
     ap.add_argument("--rc-blind-partition", action="store_true",
                     help="eager RC: balance the stages alone (default: balance own stage + redundant forward of the next)")
+    ap.add_argument("--engine-options", default="{}",
+                    help="JSON object merged into the engine's bamboo_b200 configuration section (A/B measurements)")
     ap.add_argument("--dp", type=int, default=0, help="pipeline replicas (default 1; 2 for gpt-6.7b on 8 GPUs)")
     ap.add_argument("--whole-blocks", action="store_true",
                     help="multi-stage runs: keep every transformer block one pipeline layer (coarser stage boundaries)")
@@ -341,8 +343,8 @@ def main():
             "train_micro_batch_size_per_gpu": MICRO_BATCH, "gradient_accumulation_steps": MICRO_BATCHES,
             "train_batch_size": MICRO_BATCH * MICRO_BATCHES * dp,
             "bf16": {"enabled": True}, "optimizer": {"type": "Adam", "params": {"lr": 1e-4}},
-            "bamboo_b200": {"rc_retain_graph": bool(args.rc_retain_graph),
-                            "rc_max_ctas": args.rc_max_ctas}},
+            "bamboo_b200": dict({"rc_retain_graph": bool(args.rc_retain_graph), "rc_max_ctas": args.rc_max_ctas},
+                                **json.loads(args.engine_options))},
             redundancy_level=0 if arm_rc == "off" else 1, eager_recovery=(arm_rc == "eager"), store=store)
         return engine
 
