@@ -904,7 +904,7 @@ class PipelineEngine:
             self._rc_event = self.rc_stream.record_event()
         yield
 
-    def _rc_pump(self, everything=False):
+    def _rc_pump(self, everything=False, idle_for_s=0.0):
         """Issue one pending chunk of redundant work (or all of it).  Called by the transport while
         the host waits for a message and the main stream has drained, by the end of the batch and
         before anything that needs the redundant results."""
@@ -913,7 +913,11 @@ class PipelineEngine:
             # stream competes with the own stage's kernels once the awaited message arrives
             while self._rc_inflight and self._rc_inflight[0].query():
                 self._rc_inflight.popleft()
-            if len(self._rc_inflight) >= self._config.rc_chunks_in_flight:
+            # a wait that has already lasted long is a pipeline bubble, not a hand-over gap: deeper queue
+            allowed = self._config.rc_chunks_in_flight
+            if idle_for_s > 0.0005:
+                allowed = min(allowed + int(idle_for_s / 0.0005), 4 * allowed)
+            if len(self._rc_inflight) >= allowed:
                 return bool(self._rc_queue)
         while self._rc_queue:
             try:

@@ -177,7 +177,7 @@ class MailboxTransport:
                 # everything queued before the wait has run: the stream now sits in the wait kernel
                 if drained_at is None:
                     drained_at = time.perf_counter()
-                if hook is not None and not hook():
+                if hook is not None and not hook(idle_for_s=time.perf_counter() - drained_at):
                     hook = None
             if (spins & 0xFFF) == 0 and time.perf_counter() > limit:
                 raise L.BambooNativeError(f"no completion record for a receive from rank {peer} "

@@ -47,6 +47,9 @@ def parse():
                     help="redundant forwards keep their autograd graph, as the reference's shadow forwards do")
     ap.add_argument("--rc-max-ctas", type=int, default=-2,
                     help="SM budget of a redundant-computation GEMM (see bamboo_b200.rc_max_ctas; -2 = library default)")
+    ap.add_argument("--rc-frac", type=float, default=0.12,
+                    help="eager RC: weight of the next stage's cost in a rank's load when the stage boundaries are "
+                         "chosen (1/3 = the redundant forward at full price, 0 = ignore it; most of it hides in idle time)")
     ap.add_argument("--rc-blind-partition", action="store_true",
                     help="eager RC: balance the stages alone (default: balance own stage + redundant forward of the next)")
     ap.add_argument("--engine-options", default="{}",
@@ -322,7 +325,7 @@ def main():
     def parts_for(arm_rc):
         # with eager RC every rank but the last also runs its successor's forward: that load is
         # balanced; every other arm (RC off, lazy) balances the stages alone
-        frac = (1.0 / 3.0) if (arm_rc == "eager" and not args.rc_blind_partition) else 0.0
+        frac = args.rc_frac if (arm_rc == "eager" and not args.rc_blind_partition) else 0.0
         return contiguous_partition(stage_costs(cfg, split), stages, rc_frac=frac)
 
     parts = parts_for(rc)
