@@ -9,7 +9,7 @@ DeepSpeed 0.5.2 has no such key and the sm_100a kernels compute in bf16.
 import json
 from typing import Optional
 
-RC_MAX_CTAS_DEFAULT = 0
+RC_MAX_CTAS_DEFAULT = -1
 ADAM = "adam"
 ADAMW = "adamw"
 
@@ -77,7 +77,9 @@ class PipeConfig:
         # (308 ms vs 296 ms per step) - the shorter wait does not pay for the slower GEMMs.
         self.rc_short_ctas = bool(ext.get("rc_short_ctas", False))
         # SM budget of a redundant-computation GEMM: 0 = every SM (persistent CTAs, like the main
-        # stream's), n > 0 = at most n CTAs, so that the main stream always finds free SMs.
+        # stream's), n > 0 = at most n CTAs, -1 = one work unit per CTA.  Default -1: a low-priority
+        # CTA is not preempted, so it should be short-lived - the own stage's next kernel then finds
+        # its SMs within microseconds (4 stages, 12-step runs: 156.9 ms/step vs 158.6 with persistent CTAs).
         v = int(ext.get("rc_max_ctas", RC_MAX_CTAS_DEFAULT))
         self.rc_max_ctas = RC_MAX_CTAS_DEFAULT if v == -2 else v
         self.shadow_sync = bool(ext.get("shadow_sync", True))
