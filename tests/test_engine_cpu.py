@@ -381,3 +381,24 @@ def test_failed_shadow_refresh_blocks_promotion():
     status, out = res[0]
     assert status == "ok", out
     assert out["valid"] == {1: False} and out["refused"]
+
+
+def test_four_by_two_grid_middle_stage_failover():
+    """The GPT-6.7B configuration's failure case on a small model: 4 stages x 2 replicas (rank =
+    stage * 2 + replica), replica-0 stage 2 (rank 4) is preempted after step 2.  Rank 2 promotes its
+    shadow of stage 2 and takes rank 4's seat in that stage's all-reduce, rank 6 re-points its
+    predecessor to rank 2, rank 5 switches to the fallback group; every survivor keeps the oracle's
+    trajectory."""
+    from dist_utils import run_ranks
+    want, ref = _oracle_grid(2)
+    res = run_ranks(_train_grid, 8, 4, 2, 1, 4, 2, timeout=400)
+    assert res[4] == ("exit", 13)
+    for r in (0, 1, 2, 3, 5, 6, 7):
+        assert res[r][0] == "ok", res[r]
+    assert res[2][1]["stage_ids"] == [1, 2]
+    assert res[6][1]["losses"] == pytest.approx([w[0] for w in want], rel=1e-5)     # last stage of replica 0
+    assert res[7][1]["losses"] == pytest.approx([w[1] for w in want], rel=1e-5)     # last stage of replica 1
+    total = sum(float(p.detach().double().sum()) for p in ref.P.values())
+    replica1 = sum(sum(res[r][1]["checksum"].values()) for r in (1, 3, 5, 7))
+    replica0 = sum(sum(res[r][1]["checksum"].values()) for r in (0, 2, 6))
+    assert replica1 == pytest.approx(total, rel=1e-6) and replica0 == pytest.approx(total, rel=1e-6)
