@@ -192,6 +192,44 @@ int bb_block_half_fwd(const bb_block_desc* d, int half, const void* x, void* sav
 int bb_block_half_bwd(const bb_block_desc* d, int half, const void* x, const void* saved, const void* dout, void* dx,
                       void* scratch, long long scratch_bytes, void* stream, void* side_stream);
 
+/* ---- convolutional stages (channels-last) ----------------------------------------- */
+/* ResNet-152 stage compute, bf16 NHWC.  A convolution is bb_gemm_bf16 over a patch matrix:
+ * rows = output pixels (n, ho, wo), columns = (tap r, tap s, input channel), weight stored
+ * [Cout, k, k, Cin]; a 1 x 1 / stride 1 convolution reads the activation tensor itself as that
+ * matrix.  bb_im2col_nhwc builds the patch matrix (zero padding), bb_col2im_nhwc is its adjoint
+ * (input gradient from the patch-matrix gradient; gather form, fixed summation order).  C and
+ * ld_col (elements per patch-matrix row, >= k*k*C) are multiples of 8; Ho = (H + 2 pad - k) /
+ * stride + 1.
+ * Replaces: torch.nn.Conv2d forward / backward (cuDNN) of torchvision's resnet152 as split by
+ * join_resnet_layers (EX/osdi22-cv/resnet-exp.py:69-83; blocks EX/pipeline_parallelism/resnet.py:49-171). */
+int bb_im2col_nhwc(const void* x, void* col, int N, int H, int W, int C, int k, int stride, int pad, int Ho, int Wo,
+                   long long ld_col, void* stream);
+int bb_col2im_nhwc(const void* dcol, void* dx, int N, int H, int W, int C, int k, int stride, int pad, int Ho, int Wo,
+                   long long ld_col, void* stream);
+/* Batch normalisation with batch statistics over the rows of y [rows, C] (rows = N*H*W), C = 8 x
+ * a power of two <= 2048: bb_bn_stats -> mean / rstd (biased variance); bb_bn_apply -> z = (y -
+ * mean) * rstd * gamma + beta (+ residual) (ReLU if relu != 0); bb_bn_bwd takes dz, masks it with
+ * z > 0 when relu, writes dy (gradient w.r.t. the convolution output), optionally dres (the
+ * masked gradient, for the residual branch) and accumulates dgamma / dbeta (fp32).  `workspace`:
+ * bb_bn_workspace_bytes(rows, C).  Replaces: nn.BatchNorm2d (training mode) + ReLU + the residual
+ * add of the bottleneck blocks and their autograd backward.  Running statistics are not kept
+ * (they do not enter the training step). */
+long long bb_bn_workspace_bytes(long long rows, int C);
+int bb_bn_stats(const void* y, long long rows, int C, float eps, float* mean, float* rstd, void* workspace,
+                long long workspace_bytes, void* stream);
+int bb_bn_apply(const void* y, const float* mean, const float* rstd, const void* gamma, const void* beta,
+                const void* residual, void* z, long long rows, int C, int relu, void* stream);
+int bb_bn_bwd(const void* dz, const void* z, const void* y, const float* mean, const float* rstd, const void* gamma,
+              void* dy, void* dres, float* dgamma, float* dbeta, long long rows, int C, int relu, void* workspace,
+              long long workspace_bytes, void* stream);
+/* 3 x 3 / stride 2 / padding 1 max pooling (argmax: 1 byte per output element, position 0..8 in
+ * the window, first maximum wins) and global average pooling over HW pixels.
+ * Replaces: model.maxpool / model.avgpool of the same layer list. */
+int bb_maxpool3x3s2_fwd(const void* x, void* y, void* argmax, int N, int H, int W, int C, void* stream);
+int bb_maxpool3x3s2_bwd(const void* dy, const void* argmax, void* dx, int N, int H, int W, int C, void* stream);
+int bb_avgpool_fwd(const void* x, void* y, int N, int HW, int C, void* stream);
+int bb_avgpool_bwd(const void* dy, void* dx, int N, int HW, int C, void* stream);
+
 /* ---- optimizer -------------------------------------------------------------------- */
 /* One Adam / AdamW step over a flat parameter arena: fp32 master weights, gradient and
  * moments; refreshes the bf16 working copy (may be NULL) and optionally clears the
