@@ -349,3 +349,92 @@ def block_half_bwd(desc, half, x, saved, dout, dx, scratch, side_stream=None):
     check(load().bb_block_half_bwd(ctypes.byref(desc), _I(half), _ptr(x), _ptr(saved), _ptr(dout), _ptr(dx), _ptr(scratch),
                                    _LL(scratch.numel()), main, side), "bb_block_half_bwd")
     return dx
+
+
+# ---------------------------------------------------------------------------- convolutional stages
+def im2col(x, col, k, stride, pad, Ho, Wo):
+    """x: [N,H,W,C] bf16 -> col: [N*Ho*Wo, ld] patch matrix, columns (r, s, c)."""
+    global LAUNCHES
+    LAUNCHES += 1
+    N, H, W, C = x.shape
+    check(load().bb_im2col_nhwc(_ptr(x), _ptr(col), _I(N), _I(H), _I(W), _I(C), _I(k), _I(stride), _I(pad), _I(Ho), _I(Wo),
+                                _LL(col.stride(0)), _stream()), "bb_im2col_nhwc")
+    return col
+
+
+def col2im(dcol, dx, k, stride, pad, Ho, Wo):
+    global LAUNCHES
+    LAUNCHES += 1
+    N, H, W, C = dx.shape
+    check(load().bb_col2im_nhwc(_ptr(dcol), _ptr(dx), _I(N), _I(H), _I(W), _I(C), _I(k), _I(stride), _I(pad), _I(Ho), _I(Wo),
+                                _LL(dcol.stride(0)), _stream()), "bb_col2im_nhwc")
+    return dx
+
+
+def _bn_ws(rows, C):
+    lib = load()
+    lib.bb_bn_workspace_bytes.restype = _LL
+    need = lib.bb_bn_workspace_bytes(_LL(rows), _I(C))
+    if need < 0:
+        raise BambooNativeError(f"batch norm over {C} channels: the channel count must be 8 x a power of two <= 2048")
+    return workspace(need, "bn")
+
+
+def bn_stats(y, mean, rstd, eps=1e-5):
+    global LAUNCHES
+    LAUNCHES += 2
+    rows, C = y.shape
+    ws = _bn_ws(rows, C)
+    check(load().bb_bn_stats(_ptr(y), _LL(rows), _I(C), _F(eps), _ptr(mean), _ptr(rstd), _ptr(ws), _LL(ws.numel()), _stream()),
+          "bb_bn_stats")
+
+
+def bn_apply(y, mean, rstd, gamma, beta, residual, z, relu):
+    global LAUNCHES
+    LAUNCHES += 1
+    rows, C = y.shape
+    check(load().bb_bn_apply(_ptr(y), _ptr(mean), _ptr(rstd), _ptr(gamma), _ptr(beta), _ptr(residual), _ptr(z), _LL(rows), _I(C),
+                             _I(int(relu)), _stream()), "bb_bn_apply")
+    return z
+
+
+def bn_bwd(dz, z, y, mean, rstd, gamma, dy, dres, dgamma, dbeta, relu):
+    global LAUNCHES
+    LAUNCHES += 3
+    rows, C = y.shape
+    ws = _bn_ws(rows, C)
+    check(load().bb_bn_bwd(_ptr(dz), _ptr(z), _ptr(y), _ptr(mean), _ptr(rstd), _ptr(gamma), _ptr(dy), _ptr(dres), _ptr(dgamma),
+                           _ptr(dbeta), _LL(rows), _I(C), _I(int(relu)), _ptr(ws), _LL(ws.numel()), _stream()), "bb_bn_bwd")
+    return dy
+
+
+def maxpool_fwd(x, y, argmax):
+    global LAUNCHES
+    LAUNCHES += 1
+    N, H, W, C = x.shape
+    check(load().bb_maxpool3x3s2_fwd(_ptr(x), _ptr(y), _ptr(argmax), _I(N), _I(H), _I(W), _I(C), _stream()), "bb_maxpool3x3s2_fwd")
+    return y
+
+
+def maxpool_bwd(dy, argmax, dx):
+    global LAUNCHES
+    LAUNCHES += 1
+    N, H, W, C = dx.shape
+    check(load().bb_maxpool3x3s2_bwd(_ptr(dy), _ptr(argmax), _ptr(dx), _I(N), _I(H), _I(W), _I(C), _stream()), "bb_maxpool3x3s2_bwd")
+    return dx
+
+
+def avgpool_fwd(x, y):
+    global LAUNCHES
+    LAUNCHES += 1
+    N, H, W, C = x.shape
+    check(load().bb_avgpool_fwd(_ptr(x), _ptr(y), _I(N), _I(H * W), _I(C), _stream()), "bb_avgpool_fwd")
+    return y
+
+
+def avgpool_bwd(dy, dx):
+    global LAUNCHES
+    LAUNCHES += 1
+    N, H, W, C = dx.shape
+    check(load().bb_avgpool_bwd(_ptr(dy), _ptr(dx), _I(N), _I(H * W), _I(C), _stream()), "bb_avgpool_bwd")
+    return dx

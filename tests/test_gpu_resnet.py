@@ -1,0 +1,189 @@
+"""Channels-last ResNet stage kernels and layers against fp32 PyTorch (bf16 tolerance 2e-2):
+patch gather and its adjoint, batch norm with batch statistics, pooling, one bottleneck block at
+ResNet-152's own dimensions, and a small bottleneck ResNet through the public API (loss and every
+gradient tensor against the oracle)."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from oracle import resnet_ref  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+
+
+@pytest.fixture(scope="module")
+def L():
+    from bamboo_b200 import lib
+    lib.load()
+    return lib
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("k,stride,C,H", [(3, 1, 16, 14), (3, 2, 64, 15), (7, 2, 8, 32), (1, 2, 32, 8)])
+def test_patch_gather_and_its_adjoint(L, k, stride, C, H):
+    g = torch.Generator(device="cuda").manual_seed(1)
+    N, W, pad = 2, H + 3, (k - 1) // 2
+    x = torch.randn(N, H, W, C, device="cuda", generator=g).bfloat16()
+    Ho, Wo = (H + 2 * pad - k) // stride + 1, (W + 2 * pad - k) // stride + 1
+    col = torch.empty(N * Ho * Wo, k * k * C, dtype=torch.bfloat16, device="cuda")
+    L.im2col(x, col, k, stride, pad, Ho, Wo)
+    # torch.unfold orders columns (c, r, s); ours (r, s, c)
+    ref = F.unfold(x.float().permute(0, 3, 1, 2), k, padding=pad, stride=stride)          # [N, C*k*k, Ho*Wo]
+    ref = ref.view(N, C, k * k, Ho * Wo).permute(0, 3, 2, 1).reshape(N * Ho * Wo, k * k * C)
+    assert torch.equal(col.float(), ref)                                                   # a gather: exact
+    # adjoint: <im2col(x), d> == <x, col2im(d)> ; compare with fold
+    d = torch.randn(N * Ho * Wo, k * k * C, device="cuda", generator=g).bfloat16()
+    dx = torch.empty_like(x)
+    L.col2im(d, dx, k, stride, pad, Ho, Wo)
+    dref = d.float().view(N, Ho * Wo, k * k, C).permute(0, 3, 2, 1).reshape(N, C * k * k, Ho * Wo)
+    want = F.fold(dref, (H, W), k, padding=pad, stride=stride).permute(0, 2, 3, 1)
+    assert _rel(dx, want) <= 5e-3
+    torch.cuda.synchronize()
+    assert L.read_status() == 0
+
+
+@pytest.mark.parametrize("rows,C,relu,res", [(1000, 64, True, True), (4096, 256, True, False), (333, 2048, False, False),
+                                             (50000, 16, True, True)])
+def test_batch_norm_forward_backward(L, rows, C, relu, res):
+    g = torch.Generator(device="cuda").manual_seed(2)
+    y = (torch.randn(rows, C, device="cuda", generator=g) * 2 + 0.5).bfloat16()
+    gamma = (1 + 0.2 * torch.randn(C, device="cuda", generator=g)).bfloat16()
+    beta = (0.1 * torch.randn(C, device="cuda", generator=g)).bfloat16()
+    r = torch.randn(rows, C, device="cuda", generator=g).bfloat16() if res else None
+    dz = torch.randn(rows, C, device="cuda", generator=g).bfloat16()
+    mean, rstd = torch.empty(C, device="cuda"), torch.empty(C, device="cuda")
+    L.bn_stats(y, mean, rstd, 1e-5)
+    z = torch.empty_like(y)
+    L.bn_apply(y, mean, rstd, gamma, beta, r, z, relu)
+    yf = y.float().requires_grad_(True)
+    gf, bf_ = gamma.float().requires_grad_(True), beta.float().requires_grad_(True)
+    rf = r.float().requires_grad_(True) if res else None
+    zr = F.batch_norm(yf, None, None, gf, bf_, training=True, eps=1e-5)
+    if res:
+        zr = zr + rf
+    if relu:
+        zr = F.relu(zr)
+    assert (mean - yf.detach().mean(0)).abs().max().item() <= 1e-3
+    assert _rel(z, zr.detach()) <= TOL
+    # backward uses the kernel's own z for the ReLU mask; elements within bf16 rounding of 0 may differ
+    zr.backward(dz.float())
+    dy = torch.empty_like(y)
+    dres = torch.empty_like(y) if res else None
+    dg, db = torch.zeros(C, device="cuda"), torch.zeros(C, device="cuda")
+    L.bn_bwd(dz, z, y, mean, rstd, gamma, dy, dres, dg, db, relu)
+    assert _rel(dy, yf.grad) <= TOL
+    assert _rel(dg, gf.grad) <= TOL and _rel(db, bf_.grad) <= TOL
+    if res:
+        assert _rel(dres, rf.grad) <= TOL
+    torch.cuda.synchronize()
+    assert L.read_status() == 0
+
+
+def test_pooling(L):
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = F.relu(torch.randn(3, 17, 22, 32, device="cuda", generator=g)).bfloat16()          # many exact ties at 0
+    from bamboo_b200 import resnet
+    xr = x.float().permute(0, 3, 1, 2).requires_grad_(True)
+    want = F.max_pool2d(xr, 3, 2, 1)
+    xs = x.clone().requires_grad_(True)
+    got = resnet._MaxPoolFn.apply(xs)
+    assert torch.equal(got.float(), want.detach().permute(0, 2, 3, 1))
+    d = torch.randn_like(got)
+    got.backward(d)
+    want.backward(d.float().permute(0, 3, 1, 2))
+    assert _rel(xs.grad, xr.grad.permute(0, 2, 3, 1)) <= 5e-3
+    x2 = torch.randn(4, 7, 7, 2048, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    a = resnet._AvgPoolFn.apply(x2)
+    assert _rel(a, x2.detach().float().mean((1, 2))) <= 5e-3
+    a.backward(torch.ones_like(a))
+    assert _rel(x2.grad, torch.full_like(x2, 1 / 49.0)) <= 5e-3
+
+
+def _block_params(blk, prefix):
+    out = {}
+    for name in ("conv1", "conv2", "conv3", "down"):
+        m = getattr(blk, name)
+        if m is None:
+            continue
+        cout = m.weight.shape[0]
+        cin = m.weight.shape[1] // (m.k * m.k)
+        out[f"{prefix}.{name}.weight"] = m.weight.detach().float().view(cout, m.k, m.k, cin).permute(0, 3, 1, 2).contiguous()
+        out[f"{prefix}.{name}.bn_weight"] = m.bn_weight.detach().float().clone()
+        out[f"{prefix}.{name}.bn_bias"] = m.bn_bias.detach().float().clone()
+    return out
+
+
+@pytest.mark.parametrize("cin,mid,stride,down,hw", [(256, 64, 1, False, 56), (256, 128, 2, True, 56), (1024, 256, 1, False, 14)])
+def test_bottleneck_at_resnet152_dimensions(L, cin, mid, stride, down, hw):
+    """One block with ResNet-152's channel counts and feature-map sizes against the same block in
+    fp32 PyTorch: output and input gradient."""
+    from bamboo_b200 import resnet
+    from bamboo_b200.arena import ParamArena
+    blk = resnet.Bottleneck(cin, mid, stride=stride, downsample=down, seed=5)
+    P = {k: v.cuda().requires_grad_(True) for k, v in _block_params(blk, "1").items()}
+    ParamArena(list(blk.parameters()), torch.device("cuda"), torch.bfloat16)
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn(4, hw, hw, cin, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    out = blk(x)
+    xr = x.detach().float().permute(0, 3, 1, 2).requires_grad_(True)
+    identity = resnet_ref._conv_bn(P, "1.down", xr, stride, 1, False) if down else xr
+    y = resnet_ref._conv_bn(P, "1.conv1", xr, 1, 1, True)
+    y = resnet_ref._conv_bn(P, "1.conv2", y, stride, 3, True)
+    want = resnet_ref._conv_bn(P, "1.conv3", y, 1, 1, True, residual=identity)
+    assert _rel(out, want.detach().permute(0, 2, 3, 1)) <= TOL
+    d = torch.randn_like(out)
+    out.backward(d)
+    want.backward(d.float().permute(0, 3, 1, 2))
+    assert _rel(x.grad, xr.grad.permute(0, 2, 3, 1)) <= 2 * TOL
+    m = blk.conv2
+    got_w = m.weight.main_grad.view(mid, 3, 3, mid).permute(0, 3, 1, 2)
+    assert _rel(got_w, P["1.conv2.weight"].grad) <= 2 * TOL
+    torch.cuda.synchronize()
+    assert L.read_status() == 0
+
+
+def test_small_resnet_training_steps_match_oracle():
+    """Bottleneck ResNet (one block per stage, width 64, 64 x 64 images, 40 classes) through
+    PipelineModule / initialize / train_batch: loss and every gradient tensor per step."""
+    from bamboo_b200 import api, resnet
+    from bamboo_b200.module import PipelineModule
+    os.environ["BAMBOO_QUIET"] = "1"
+    blocks, width, classes, size = (1, 1, 1, 1), 64, 40, 64
+    mb, gas, lr = 8, 2, 1e-3
+    model = PipelineModule(resnet.resnet_layer_specs(blocks, classes, width, seed=0), num_stages=1,
+                           loss_fn=resnet.resnet_loss(classes), partition_method="uniform")
+    engine, *_ = api.initialize(model=model, config={
+        "train_micro_batch_size_per_gpu": mb, "gradient_accumulation_steps": gas, "bf16": {"enabled": True},
+        "optimizer": {"type": "Adam", "params": {"lr": lr}}})
+    engine.capture_grads = True
+    ref = resnet_ref.RefTrainer(blocks, classes, width, seed=0, lr=lr, micro_batches=gas)
+    arena = engine.arenas[0]
+    names = [n for n, _ in engine.module.get_named_param(0)]
+    for batches in resnet_ref.synthetic_batches(mb, gas, 2, size=size, classes=classes, seed=1):
+        want = ref.train_batch(batches)
+        got = float(engine.train_batch(data_iter=iter([(resnet_ref.to_channels_last_8(x), y) for x, y in batches])))
+        assert got == pytest.approx(want, rel=TOL)
+        flat = engine.last_grads[0].cpu()
+        num = den = 0.0
+        for name, (i, off, n) in zip(names, arena.named_slices()):
+            g_ref = ref.last_grads[name]
+            shape = arena.params[i].shape
+            g_got = flat[off:off + n].view(shape)
+            if name.endswith(".weight") and g_ref.dim() == 4:
+                co, ci, k, _ = g_ref.shape
+                g_ref = g_ref.permute(0, 2, 3, 1).reshape(co, k * k * ci)
+            assert g_got.shape == g_ref.shape, name
+            num += float((g_got - g_ref).double().pow(2).sum()); den += float(g_ref.double().pow(2).sum())
+            assert _rel(g_got, g_ref) <= 10 * TOL, (name, _rel(g_got, g_ref))
+        assert (num / den) ** 0.5 <= 2 * TOL
+    from bamboo_b200 import lib
+    torch.cuda.synchronize()
+    assert lib.read_status() == 0
