@@ -32,7 +32,7 @@ def parse():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="bamboo_b200", choices=["bamboo_b200", "reference"])
     ap.add_argument("--rc", default="auto", choices=["auto", "off", "lazy", "eager"])
-    ap.add_argument("--model", default="gpt2-medium", choices=["gpt2-medium", "bert-large", "gpt-6.7b", "toy"],
+    ap.add_argument("--model", default="gpt2-medium", choices=["gpt2-medium", "bert-large", "gpt-6.7b", "resnet152", "toy"],
                     help="gpt2-medium is the headline configuration (micro-batch 8 x 16, seq 1024); bert-large is the "
                          "masked-LM configuration (micro-batch 16 x 32, seq 512, bidirectional attention)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -62,8 +62,42 @@ def parse():
     return ap.parse_args()
 
 
+class ResNetBench:
+    """ResNet-152 workload (BASELINE configuration 4): 224 x 224 images, 1000 classes, micro-batch
+    32 x 16; the unit of throughput is a sample."""
+    blocks, classes, size, width = (3, 8, 36, 3), 1000, 224, 64
+    seq, mlm, layers, hidden, vocab = 1, False, 50, 2048, 1000          # fields the shared code reads
+
+    def flops_per_token(self):
+        from bamboo_b200 import resnet
+        return 3 * resnet.conv_flops_per_image(self.blocks, self.size, self.classes, self.width)
+
+    def layer_costs(self):
+        """Relative cost of every pipeline layer (stem, 50 blocks, head): its convolution FLOPs."""
+        from bamboo_b200 import resnet
+        def upto(nblocks):            # FLOPs of the network truncated after `nblocks` bottlenecks (no head)
+            done, out = 0, []
+            for n in self.blocks:
+                take = min(n, nblocks - done)
+                if take <= 0:
+                    break
+                out.append(take); done += take
+            return resnet.conv_flops_per_image(tuple(out), self.size, 8, self.width) if out else None
+        stem = resnet.conv_flops_per_image((), self.size, 8, self.width)
+        costs, prev = [stem], stem
+        for i in range(1, sum(self.blocks) + 1):
+            cur = upto(i)
+            # the truncated count adds a tiny 8-class head on top of the last block's channels: negligible
+            costs.append(max(cur - prev, 0)); prev = cur
+        costs.append(2 * 2048 * self.classes)
+        unit = sum(costs) / len(costs)
+        return [c / unit for c in costs]
+
+
 def model_config(name):
     from bamboo_b200 import models
+    if name == "resnet152":
+        return ResNetBench()
     return {"gpt2-medium": models.GPT2_MEDIUM, "bert-large": models.BERT_LARGE, "gpt-6.7b": models.GPT_6_7B}.get(name, models.GPT_TOY)
 
 
@@ -163,6 +197,20 @@ def synthetic_tokens(cfg, steps, seed, pin, replicas=1):
     from bamboo_b200 import models
     g = torch.Generator().manual_seed(seed)
     out = []
+    if isinstance(cfg, ResNetBench):
+        # N(0, 1) images in the kernels' input layout ([N, H, W, 8] bf16: 3 image channels, 5 zero
+        # planes), uniform labels.  One set of micro-batches serves every step (400 MB of pinned
+        # memory per step otherwise); the data never repeats inside a step.
+        step = []
+        for _ in range(MICRO_BATCHES * replicas):
+            img = torch.zeros(MICRO_BATCH, cfg.size, cfg.size, 8, dtype=torch.bfloat16)
+            img[..., :3] = torch.randn(MICRO_BATCH, cfg.size, cfg.size, 3, generator=g).to(torch.bfloat16)
+            lab = torch.randint(0, cfg.classes, (MICRO_BATCH,), generator=g)
+            if pin:
+                img, lab = img.pin_memory(), lab.pin_memory()
+            step.append((img, lab))
+        per_replica = [step[r * MICRO_BATCHES:(r + 1) * MICRO_BATCHES] for r in range(replicas)]
+        return [per_replica for _ in range(steps)]
     for _ in range(steps):
         per_replica = []
         for _ in range(replicas):
@@ -190,6 +238,19 @@ def cpu_baseline(cfg, seconds_budget=25.0):
     from oracle import gpt_ref
     cores = len(os.sched_getaffinity(0))
     torch.set_num_threads(cores)
+    if isinstance(cfg, ResNetBench):
+        from oracle import resnet_ref
+        ref = resnet_ref.RefTrainer(cfg.blocks, cfg.classes, cfg.width, seed=0, lr=1e-4, micro_batches=1)
+        t_wall = time.perf_counter()
+        n = 4
+        batch = resnet_ref.synthetic_batches(n, 1, 1, size=cfg.size, classes=cfg.classes, seed=1)[0]
+        t0 = time.perf_counter()
+        ref.train_batch(batch)
+        dt = time.perf_counter() - t0
+        return {"value": n / dt, "unit": METRIC, "cores": cores, "kind": "port", "extrapolated": True,
+                "sample_ms": (time.perf_counter() - t_wall) * 1e3, "sample_tokens": n,
+                "sample": f"one fp32 step over {n} images of {cfg.size} x {cfg.size} (forward, backward, Adam update); "
+                          "batch statistics over 4 images instead of 32"}
     rc = gpt_ref.RefConfig(cfg.layers, cfg.hidden, cfg.heads, cfg.ffn, cfg.seq, cfg.vocab, cfg.causal, cfg.mlm)
     ref = gpt_ref.RefTrainer(rc, seed=0, lr=1e-4, micro_batches=1)
     g = torch.Generator().manual_seed(1)
@@ -276,6 +337,8 @@ def stage_costs(cfg, split):
     `split` every block is two layers (attention half 0.53, MLP half 0.47 of a block's time), so
     that stage boundaries can fall inside a block: with 24 blocks and a head worth 2.3 blocks,
     whole blocks leave 8 stages 22 % above the mean load."""
+    if isinstance(cfg, ResNetBench):
+        return cfg.layer_costs()
     h = cfg.hidden
     blk = 24.0 * h * h + 4.0 * cfg.seq * h
     head_cost = 0.65 * 2.0 * h * cfg.vocab / blk
@@ -290,6 +353,10 @@ def main():
         MICRO_BATCH, MICRO_BATCHES = 16, 32
     elif args.model == "gpt-6.7b":
         MICRO_BATCH, MICRO_BATCHES = 2, 32
+    elif args.model == "resnet152":
+        global METRIC
+        METRIC = "samples/sec"
+        MICRO_BATCH, MICRO_BATCHES = 32, 16
     if args.micro_batches:
         MICRO_BATCHES = args.micro_batches
     if args.impl == "reference":
@@ -321,7 +388,7 @@ def main():
     rc = args.rc if args.rc != "auto" else ("eager" if stages > 1 else "off")
     if stages == 1:
         rc = "off"
-    split = stages > 1 and not args.whole_blocks
+    split = stages > 1 and not args.whole_blocks and not isinstance(cfg, ResNetBench)
     def parts_for(arm_rc):
         # with eager RC every rank but the last also runs its successor's forward: that load is
         # balanced; every other arm (RC off, lazy) balances the stages alone
@@ -338,8 +405,12 @@ def main():
 
     def build(arm_rc, tag):
         topo = PipeDataParallelTopology(num_pp=stages, num_dp=dp)
-        model = PipelineModule(models.transformer_layer_specs(cfg, 0, split_blocks=split), topology=topo,
-                               loss_fn=models.transformer_loss(cfg), partition_method="custom",
+        if isinstance(cfg, ResNetBench):
+            from bamboo_b200 import resnet
+            specs, loss_fn = resnet.resnet_layer_specs(cfg.blocks, cfg.classes, cfg.width, seed=0), resnet.resnet_loss(cfg.classes)
+        else:
+            specs, loss_fn = models.transformer_layer_specs(cfg, 0, split_blocks=split), models.transformer_loss(cfg)
+        model = PipelineModule(specs, topology=topo, loss_fn=loss_fn, partition_method="custom",
                                custom_partitions=parts_for(arm_rc))
         store = dist.PrefixStore(f"bench-{tag}", base_store) if base_store is not None else None
         engine, *_ = api.initialize(model=model, config={
@@ -509,7 +580,9 @@ def main():
         "metric": METRIC, "value": value, "unit": METRIC, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{args.model} ({cfg.layers} layers, hidden {cfg.hidden}, seq {cfg.seq}, vocab {cfg.vocab}) "
+        "config": {"workload": (f"resnet152 (bottleneck blocks {list(cfg.blocks)}, {cfg.size} x {cfg.size} x 3 images, {cfg.classes} classes, "
+                                 "bf16 channels-last) " if isinstance(cfg, ResNetBench) else
+                                 f"{args.model} ({cfg.layers} layers, hidden {cfg.hidden}, seq {cfg.seq}, vocab {cfg.vocab}) ") +
                                f"pipeline step, {stages} stage(s) x {dp} replica(s), micro-batch {MICRO_BATCH} x {MICRO_BATCHES}",
                    "rc": rc, "rc_retain_graph": bool(args.rc_retain_graph),
                    "parallelism": f"pp{stages}" + (f"dp{dp}" if dp > 1 else ""), "stage_boundaries": parts,
