@@ -107,6 +107,37 @@ def test_pooling(L):
     assert _rel(x2.grad, torch.full_like(x2, 1 / 49.0)) <= 5e-3
 
 
+@pytest.mark.parametrize("cin,cout,k,stride,hw", [(8, 64, 7, 2, 64), (64, 64, 3, 1, 28), (64, 128, 3, 2, 28), (256, 512, 1, 2, 14),
+                                                  (64, 256, 1, 1, 28)])
+def test_conv_bn_layer_without_relu(L, cin, cout, k, stride, hw):
+    """Convolution + batch norm with no ReLU behind it (no activation mask that bf16 rounding could
+    flip): output, input gradient, weight gradient and batch-norm gradients at 2e-2."""
+    from bamboo_b200 import resnet
+    from bamboo_b200.arena import ParamArena
+    m = resnet.ConvBN(cin, cout, k, stride=stride, relu=False, generator=torch.Generator().manual_seed(9))
+    w_ref = m.weight.detach().float().view(cout, k, k, cin).permute(0, 3, 1, 2).contiguous().cuda().requires_grad_(True)
+    g_ref = torch.ones(cout, device="cuda", requires_grad=True)
+    b_ref = torch.zeros(cout, device="cuda", requires_grad=True)
+    ParamArena(list(m.parameters()), torch.device("cuda"), torch.bfloat16)
+    g = torch.Generator(device="cuda").manual_seed(6)
+    x = torch.randn(4, hw, hw, cin, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    out = m(x)
+    xr = x.detach().float().permute(0, 3, 1, 2).requires_grad_(True)
+    y = F.conv2d(xr, w_ref, None, stride=stride, padding=(k - 1) // 2)
+    want = F.batch_norm(y, None, None, g_ref, b_ref, training=True, eps=1e-5)
+    assert _rel(out, want.detach().permute(0, 2, 3, 1)) <= TOL
+    d = torch.randn_like(out)
+    out.backward(d)
+    want.backward(d.float().permute(0, 3, 1, 2))
+    errs = {"dx": _rel(x.grad, xr.grad.permute(0, 2, 3, 1)),
+            "dW": _rel(m.weight.main_grad.view(cout, k, k, cin).permute(0, 3, 1, 2), w_ref.grad),
+            "dgamma": _rel(m.bn_weight.main_grad, g_ref.grad), "dbeta": _rel(m.bn_bias.main_grad, b_ref.grad)}
+    print(f"conv {cin}->{cout} k{k} s{stride}: {errs}")
+    assert max(errs.values()) <= TOL, errs
+    torch.cuda.synchronize()
+    assert L.read_status() == 0
+
+
 def _block_params(blk, prefix):
     out = {}
     for name in ("conv1", "conv2", "conv3", "down"):
@@ -159,12 +190,18 @@ def test_bottleneck_at_resnet152_dimensions(L, cin, mid, stride, down, hw):
 
 
 def test_small_resnet_training_steps_match_oracle():
-    """Bottleneck ResNet (one block per stage, width 64, 64 x 64 images, 40 classes) through
-    PipelineModule / initialize / train_batch: loss and every gradient tensor per step."""
+    """Bottleneck ResNet (one block per stage, width 64, 128 x 128 images, 40 classes) through
+    PipelineModule / initialize / train_batch.  The loss must match the fp32 oracle at 2e-2.  For the
+    gradients an fp32 reference alone is the wrong yardstick in a ReLU / max-pool network: wherever
+    a pre-activation lies within bf16 rounding of zero (or two window entries within rounding of
+    each other) the mask differs, and every such flip is a full-size element-wise error that the
+    batch-norm backward passes spread further.  So the same oracle is also run in bf16 on the GPU
+    (torch / cuDNN kernels, rounding at the same points): the CUDA layers must be as close to the
+    fp32 oracle as that bf16 pipeline is (factor 1.5), tensor by tensor and for the whole model."""
     from bamboo_b200 import api, resnet
     from bamboo_b200.module import PipelineModule
     os.environ["BAMBOO_QUIET"] = "1"
-    blocks, width, classes, size = (1, 1, 1, 1), 64, 40, 64
+    blocks, width, classes, size = (1, 1, 1, 1), 64, 40, 128
     mb, gas, lr = 8, 2, 1e-3
     model = PipelineModule(resnet.resnet_layer_specs(blocks, classes, width, seed=0), num_stages=1,
                            loss_fn=resnet.resnet_loss(classes), partition_method="uniform")
@@ -175,25 +212,43 @@ def test_small_resnet_training_steps_match_oracle():
     ref = resnet_ref.RefTrainer(blocks, classes, width, seed=0, lr=lr, micro_batches=gas)
     arena = engine.arenas[0]
     names = [n for n, _ in engine.module.get_named_param(0)]
-    for batches in resnet_ref.synthetic_batches(mb, gas, 2, size=size, classes=classes, seed=1):
+
+    def ours_layout(name, g):
+        if name.endswith(".weight") and g.dim() == 4:
+            co, ci, k, _ = g.shape
+            return g.permute(0, 2, 3, 1).reshape(co, k * k * ci)
+        return g
+
+    for step, batches in enumerate(resnet_ref.synthetic_batches(mb, gas, 2, size=size, classes=classes, seed=1)):
+        if step > 0:
+            # after an Adam update from gradients that differ at the bf16 level the two weight sets are
+            # no longer the same point (Adam normalises the step size): only the loss is compared
+            want = ref.train_batch(batches)
+            got = float(engine.train_batch(data_iter=iter([(resnet_ref.to_channels_last_8(x), y) for x, y in batches])))
+            assert got == pytest.approx(want, rel=TOL)
+            continue
+        # the bf16 torch pipeline from the oracle's current weights
+        P16 = {k: v.detach().cuda().bfloat16().requires_grad_(True) for k, v in ref.P.items()}
+        for images, labels in batches:
+            (resnet_ref.forward_loss(P16, images.cuda().bfloat16(), labels.cuda(), blocks) / gas).backward()
         want = ref.train_batch(batches)
         got = float(engine.train_batch(data_iter=iter([(resnet_ref.to_channels_last_8(x), y) for x, y in batches])))
         assert got == pytest.approx(want, rel=TOL)
         flat = engine.last_grads[0].cpu()
-        num = den = worst = 0.0
+        n_o = n_b = den = 0.0
         for name, (i, off, n) in zip(names, arena.named_slices()):
-            g_ref = ref.last_grads[name]
-            shape = arena.params[i].shape
-            g_got = flat[off:off + n].view(shape)
-            if name.endswith(".weight") and g_ref.dim() == 4:
-                co, ci, k, _ = g_ref.shape
-                g_ref = g_ref.permute(0, 2, 3, 1).reshape(co, k * k * ci)
+            g_ref = ours_layout(name, ref.last_grads[name])
+            g_b16 = ours_layout(name, P16[name].grad.float().cpu()) if P16[name].grad is not None else torch.zeros_like(g_ref)
+            g_got = flat[off:off + n].view(arena.params[i].shape)
             assert g_got.shape == g_ref.shape, name
-            num += float((g_got - g_ref).double().pow(2).sum()); den += float(g_ref.double().pow(2).sum())
-            worst = max(worst, _rel(g_got, g_ref))
-            assert _rel(g_got, g_ref) <= 10 * TOL, (name, _rel(g_got, g_ref))
-        print(f"small resnet step: loss {got:.5f} vs {want:.5f}, gradients: whole model {(num / den) ** 0.5:.4f}, worst tensor {worst:.4f}")
-        assert (num / den) ** 0.5 <= 3 * TOL
+            e_o, e_b = _rel(g_got, g_ref), _rel(g_b16, g_ref)
+            n_o += float((g_got - g_ref).double().pow(2).sum()); n_b += float((g_b16 - g_ref).double().pow(2).sum())
+            den += float(g_ref.double().pow(2).sum())
+            print(f"   {name}: ours {e_o:.4f}  torch-bf16 {e_b:.4f}")
+            assert e_o <= max(1.5 * e_b, 2 * TOL), (name, e_o, e_b)
+        e_o, e_b = (n_o / den) ** 0.5, (n_b / den) ** 0.5
+        print(f"small resnet step: loss {got:.5f} vs {want:.5f}; gradients vs fp32: ours {e_o:.4f}, torch bf16 {e_b:.4f}")
+        assert e_o <= max(1.5 * e_b, TOL)
     from bamboo_b200 import lib
     torch.cuda.synchronize()
     assert lib.read_status() == 0
