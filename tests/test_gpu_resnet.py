@@ -173,18 +173,25 @@ def test_bottleneck_at_resnet152_dimensions(L, cin, mid, stride, down, hw):
     d = torch.randn_like(out)
     out.backward(d)
     want.backward(d.float().permute(0, 3, 1, 2))
-    # An element-wise gradient behind three ReLUs: wherever a pre-activation lies within bf16
-    # rounding of zero the mask differs from the fp32 reference's, and a fraction f of flipped
-    # elements costs sqrt(f) in relative L2 error (f ~ 0.3 % per ReLU here).  Sums over pixels
-    # (the weight gradients) average that out.
-    e_dx = _rel(x.grad, xr.grad.permute(0, 2, 3, 1))
+    # Gradients behind three ReLUs: wherever a pre-activation lies within bf16 rounding of zero the
+    # mask differs from the fp32 reference's, and a fraction f of flipped elements costs about
+    # sqrt(f) in relative L2 error (f ~ 0.3 % per ReLU here; with a random upstream gradient the
+    # weight-gradient sums do not average it out).  Yardstick: the same block in bf16 on torch's
+    # own kernels; the CUDA layers must be as close to fp32 as that pipeline (factor 1.5).
+    P16 = {k: v.detach().bfloat16().requires_grad_(True) for k, v in P.items()}
+    x16 = x.detach().permute(0, 3, 1, 2).contiguous().requires_grad_(True)
+    id16 = resnet_ref._conv_bn(P16, "1.down", x16, stride, 1, False) if down else x16
+    y16 = resnet_ref._conv_bn(P16, "1.conv1", x16, 1, 1, True)
+    y16 = resnet_ref._conv_bn(P16, "1.conv2", y16, stride, 3, True)
+    resnet_ref._conv_bn(P16, "1.conv3", y16, 1, 1, True, residual=id16).backward(d.permute(0, 3, 1, 2))
     m = blk.conv2
-    got_w = m.weight.main_grad.view(mid, 3, 3, mid).permute(0, 3, 1, 2)
-    e_dw = _rel(got_w, P["1.conv2.weight"].grad)
-    e_dg = _rel(blk.conv3.bn_weight.main_grad, P["1.conv3.bn_weight"].grad)
-    print(f"bottleneck {cin}/{mid}/s{stride}: out {_rel(out, want.detach().permute(0, 2, 3, 1)):.4f} dx {e_dx:.4f} "
-          f"dW(conv2) {e_dw:.4f} dgamma(conv3) {e_dg:.4f}")
-    assert e_dx <= 0.12 and e_dw <= 3 * TOL and e_dg <= 3 * TOL
+    ours = {"dx": x.grad, "dW": m.weight.main_grad.view(mid, 3, 3, mid).permute(0, 3, 1, 2), "dgamma": blk.conv3.bn_weight.main_grad}
+    bf16 = {"dx": x16.grad.permute(0, 2, 3, 1), "dW": P16["1.conv2.weight"].grad, "dgamma": P16["1.conv3.bn_weight"].grad}
+    fp32 = {"dx": xr.grad.permute(0, 2, 3, 1), "dW": P["1.conv2.weight"].grad, "dgamma": P["1.conv3.bn_weight"].grad}
+    for key in ours:
+        e_o, e_b = _rel(ours[key], fp32[key]), _rel(bf16[key], fp32[key])
+        print(f"bottleneck {cin}/{mid}/s{stride} {key}: ours {e_o:.4f}  torch-bf16 {e_b:.4f}")
+        assert e_o <= max(1.5 * e_b, TOL), (key, e_o, e_b)
     torch.cuda.synchronize()
     assert L.read_status() == 0
 
