@@ -517,3 +517,107 @@ extern "C" int bb_avgpool_bwd(const void* dy, void* dx, int N, int HW, int C, vo
   BB_CUDA_CHECK(cudaGetLastError());
   return BB_OK;
 }
+
+// ---------------------------------------------------------------------------------- one call per layer
+// Convolution + batch norm (+ residual, + ReLU) forward and backward with every kernel issued from
+// one foreign call: a ResNet-152 step has ~2500 such layers-times-micro-batches, and a Python host
+// that pays per kernel becomes the bottleneck.  Same kernels and order as calling the entry points
+// above one by one.
+namespace {
+
+inline long long up256(long long n) { return (n + 255) & ~255LL; }
+
+struct ConvSizes {
+  int Ho, Wo;
+  long long P, K;
+  bool direct;                       // 1 x 1 / stride 1: the activation tensor is the patch matrix
+  long long col_bytes, dy_bytes, dcol_bytes, bn_bytes;
+};
+
+bool conv_sizes(const bb_conv_desc* d, ConvSizes* s) {
+  if (!d || d->N <= 0 || d->H <= 0 || d->W <= 0 || d->Cin <= 0 || (d->Cin & 7) || d->Cout <= 0 || d->k <= 0 || d->stride <= 0 ||
+      d->pad < 0 || !d->w || !d->gamma || !d->beta)
+    return false;
+  s->Ho = (d->H + 2 * d->pad - d->k) / d->stride + 1;
+  s->Wo = (d->W + 2 * d->pad - d->k) / d->stride + 1;
+  if (s->Ho <= 0 || s->Wo <= 0) return false;
+  s->P = (long long)d->N * s->Ho * s->Wo;
+  s->K = (long long)d->k * d->k * d->Cin;
+  s->direct = d->k == 1 && d->stride == 1;
+  s->bn_bytes = bb_bn_workspace_bytes(s->P, d->Cout);
+  if (s->bn_bytes < 0) return false;
+  s->col_bytes = s->direct ? 0 : up256(s->P * s->K * 2);
+  s->dy_bytes = up256(s->P * d->Cout * 2);
+  s->dcol_bytes = s->direct ? 0 : up256(s->P * s->K * 2);
+  s->bn_bytes = up256(s->bn_bytes);
+  return true;
+}
+
+int conv_gemm(const bb_conv_desc* d, int M, int N, int K, const void* A, long long lda, int a_mn, const void* B, long long ldb,
+              int b_mn, void* D, long long ldd, int epi, void* stream) {
+  bb_gemm_desc g = {};
+  g.M = M; g.N = N; g.K = K; g.A = A; g.lda = lda; g.a_mn_major = a_mn; g.B = B; g.ldb = ldb; g.b_mn_major = b_mn;
+  g.D = D; g.ldd = ldd; g.epilogue = epi; g.max_ctas = d->max_ctas;
+  return bb_gemm_bf16(&g, stream);
+}
+
+#define BB_TRY(expr) do { int _rc = (expr); if (_rc != BB_OK) return _rc; } while (0)
+
+}  // namespace
+
+extern "C" long long bb_conv_bn_scratch_bytes(const bb_conv_desc* d, int backward, int need_dx) {
+  ConvSizes s;
+  if (!conv_sizes(d, &s)) return -1;
+  if (!backward) return s.col_bytes + s.bn_bytes;
+  return s.dy_bytes + s.col_bytes + (need_dx ? s.dcol_bytes : 0) + s.bn_bytes;
+}
+
+extern "C" int bb_conv_bn_fwd(const bb_conv_desc* d, const void* x, const void* residual, void* y, void* z, float* mean,
+                              float* rstd, void* scratch, long long scratch_bytes, void* stream) {
+  ConvSizes s;
+  if (!conv_sizes(d, &s) || !x || !y || !z || !mean || !rstd || !scratch || scratch_bytes < s.col_bytes + s.bn_bytes) {
+    bb_set_last_error_msg("bb_conv_bn_fwd: bad descriptor, null buffer or scratch smaller than bb_conv_bn_scratch_bytes");
+    return BB_ERR_INVALID_ARG;
+  }
+  uint8_t* sc = static_cast<uint8_t*>(scratch);
+  const void* col = x;
+  if (!s.direct) {
+    BB_TRY(bb_im2col_nhwc(x, sc, d->N, d->H, d->W, d->Cin, d->k, d->stride, d->pad, s.Ho, s.Wo, s.K, stream));
+    col = sc;
+  }
+  BB_TRY(conv_gemm(d, (int)s.P, d->Cout, (int)s.K, col, s.K, 0, d->w, s.K, 0, y, d->Cout, BB_EPI_STORE, stream));
+  BB_TRY(bb_bn_stats(y, s.P, d->Cout, d->eps, mean, rstd, sc + s.col_bytes, s.bn_bytes, stream));
+  BB_TRY(bb_bn_apply(y, mean, rstd, d->gamma, d->beta, residual, z, s.P, d->Cout, d->relu, stream));
+  return BB_OK;
+}
+
+extern "C" int bb_conv_bn_bwd(const bb_conv_desc* d, const void* x, const void* y, const void* z, const float* mean,
+                              const float* rstd, const void* dz, void* dx, void* dres, void* scratch, long long scratch_bytes,
+                              void* stream) {
+  ConvSizes s;
+  if (!conv_sizes(d, &s) || !x || !y || !z || !mean || !rstd || !dz || !scratch || !d->g_w || !d->g_gamma || !d->g_beta ||
+      scratch_bytes < bb_conv_bn_scratch_bytes(d, 1, dx != nullptr)) {
+    bb_set_last_error_msg("bb_conv_bn_bwd: bad descriptor, null buffer, missing gradient pointer or scratch too small");
+    return BB_ERR_INVALID_ARG;
+  }
+  uint8_t* sc = static_cast<uint8_t*>(scratch);
+  void* dy = sc;
+  uint8_t* colbuf = sc + s.dy_bytes;
+  uint8_t* dcolbuf = colbuf + s.col_bytes;
+  uint8_t* bnws = dcolbuf + (dx ? s.dcol_bytes : 0);
+  BB_TRY(bb_bn_bwd(dz, z, y, mean, rstd, d->gamma, dy, dres, d->g_gamma, d->g_beta, s.P, d->Cout, d->relu, bnws, s.bn_bytes, stream));
+  const void* col = x;
+  if (!s.direct) {
+    BB_TRY(bb_im2col_nhwc(x, colbuf, d->N, d->H, d->W, d->Cin, d->k, d->stride, d->pad, s.Ho, s.Wo, s.K, stream));
+    col = colbuf;
+  }
+  // dW[Cout, K] += dy^T patches
+  BB_TRY(conv_gemm(d, d->Cout, (int)s.K, (int)s.P, dy, d->Cout, 1, col, s.K, 1, d->g_w, s.K, BB_EPI_ACCUM_F32, stream));
+  if (dx) {
+    void* dcol = s.direct ? dx : (void*)dcolbuf;
+    BB_TRY(conv_gemm(d, (int)s.P, (int)s.K, d->Cout, dy, d->Cout, 0, d->w, s.K, 1, dcol, s.K, BB_EPI_STORE, stream));
+    if (!s.direct)
+      BB_TRY(bb_col2im_nhwc(dcol, dx, d->N, d->H, d->W, d->Cin, d->k, d->stride, d->pad, s.Ho, s.Wo, s.K, stream));
+  }
+  return BB_OK;
+}

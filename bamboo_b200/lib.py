@@ -49,6 +49,17 @@ class BlockDesc(ctypes.Structure):
     ]
 
 
+class ConvDesc(ctypes.Structure):
+    """bb_conv_desc: convolution + batch norm layer (see include/bamboo_b200.h)."""
+    _fields_ = [
+        ("N", ctypes.c_int), ("H", ctypes.c_int), ("W", ctypes.c_int), ("Cin", ctypes.c_int), ("Cout", ctypes.c_int),
+        ("k", ctypes.c_int), ("stride", ctypes.c_int), ("pad", ctypes.c_int), ("relu", ctypes.c_int),
+        ("eps", ctypes.c_float), ("max_ctas", ctypes.c_int),
+        ("w", ctypes.c_void_p), ("gamma", ctypes.c_void_p), ("beta", ctypes.c_void_p),
+        ("g_w", ctypes.c_void_p), ("g_gamma", ctypes.c_void_p), ("g_beta", ctypes.c_void_p),
+    ]
+
+
 HALF_ATTENTION, HALF_MLP = 0, 1
 # kernels behind one call of bb_block_half_fwd / bb_block_half_bwd, per half (launch accounting)
 HALF_FWD_LAUNCHES = {HALF_ATTENTION: 4, HALF_MLP: 3}
@@ -79,6 +90,7 @@ def load():
         lib.bb_version.restype = ctypes.c_int
         lib.bb_block_saved_bytes.restype = ctypes.c_longlong
         lib.bb_block_scratch_bytes.restype = ctypes.c_longlong
+        lib.bb_conv_bn_scratch_bytes.restype = ctypes.c_longlong
         _lib = lib
     return _lib
 
@@ -437,4 +449,21 @@ def avgpool_bwd(dy, dx):
     LAUNCHES += 1
     N, H, W, C = dx.shape
     check(load().bb_avgpool_bwd(_ptr(dy), _ptr(dx), _I(N), _I(H * W), _I(C), _stream()), "bb_avgpool_bwd")
+    return dx
+
+
+def conv_bn_fwd(desc, x, residual, y, z, mean, rstd, scratch):
+    global LAUNCHES
+    LAUNCHES += 4 + (0 if (desc.k == 1 and desc.stride == 1) else 1)
+    check(load().bb_conv_bn_fwd(ctypes.byref(desc), _ptr(x), _ptr(residual), _ptr(y), _ptr(z), _ptr(mean), _ptr(rstd),
+                                _ptr(scratch), _LL(scratch.numel()), _stream()), "bb_conv_bn_fwd")
+    return z
+
+
+def conv_bn_bwd(desc, x, y, z, mean, rstd, dz, dx, dres, scratch):
+    global LAUNCHES
+    direct = desc.k == 1 and desc.stride == 1
+    LAUNCHES += 4 + (0 if direct else 1) + (0 if dx is None else (1 if direct else 2))
+    check(load().bb_conv_bn_bwd(ctypes.byref(desc), _ptr(x), _ptr(y), _ptr(z), _ptr(mean), _ptr(rstd), _ptr(dz), _ptr(dx),
+                                _ptr(dres), _ptr(scratch), _LL(scratch.numel()), _stream()), "bb_conv_bn_bwd")
     return dx

@@ -17,6 +17,7 @@ training step.
 
 There is no fallback: these modules raise on CPU tensors.
 """
+import ctypes
 import math
 
 import torch
@@ -27,6 +28,75 @@ from .layers import CrossEntropyLoss, Linear, _main_grad, _require_cuda
 from .module import LayerSpec
 
 IN_CHANNELS = 8            # 3 image channels + 5 zero planes (16-byte channel vectors)
+
+
+def _conv_desc(mod, N, H, W, Cin, need_grads):
+    """The layer's cached bb_conv_desc for this input geometry (rebuilt when its parameters moved)."""
+    key = (N, H, W, L.GEMM_MAX_CTAS, mod.weight.data_ptr(), need_grads)
+    cache = mod.__dict__.setdefault("_desc_cache", {})
+    d = cache.get(key)
+    if d is not None:
+        return d
+    d = L.ConvDesc(N=N, H=H, W=W, Cin=Cin, Cout=mod.weight.shape[0], k=mod.k, stride=mod.stride, pad=mod.pad,
+                   relu=int(mod.relu), eps=mod.eps, max_ctas=L.GEMM_MAX_CTAS,
+                   w=mod.weight.data_ptr(), gamma=mod.bn_weight.data_ptr(), beta=mod.bn_bias.data_ptr())
+    if need_grads:
+        d.g_w, d.g_gamma, d.g_beta = (_main_grad(p).data_ptr() for p in (mod.weight, mod.bn_weight, mod.bn_bias))
+    lib = L.load()
+    d._fwd_scratch = lib.bb_conv_bn_scratch_bytes(ctypes.byref(d), 0, 0)
+    d._bwd_scratch = (lib.bb_conv_bn_scratch_bytes(ctypes.byref(d), 1, 0), lib.bb_conv_bn_scratch_bytes(ctypes.byref(d), 1, 1))
+    if d._fwd_scratch < 0:
+        raise L.BambooNativeError("bb_conv_bn_scratch_bytes rejected the layer geometry "
+                                  "(channels: multiples of 8; batch norm: 8 x a power of two <= 2048)")
+    if len(cache) > 8:
+        cache.clear()
+    cache[key] = d
+    return d
+
+
+class _ConvBNNativeFn(torch.autograd.Function):
+    """z = [relu]( batchnorm(conv(x)) [+ residual] ) through one native call each way."""
+
+    @staticmethod
+    def forward(ctx, x, residual, mod, w, gamma, beta):
+        _require_cuda(x, "ConvBN")
+        if not x.is_contiguous():
+            x = x.contiguous()
+        N, H, W, Cin = x.shape
+        Ho, Wo = (H + 2 * mod.pad - mod.k) // mod.stride + 1, (W + 2 * mod.pad - mod.k) // mod.stride + 1
+        P, Cout = N * Ho * Wo, w.shape[0]
+        dev = x.device
+        d = _conv_desc(mod, N, H, W, Cin, False)
+        y = torch.empty(P, Cout, dtype=torch.bfloat16, device=dev)
+        z = torch.empty(N, Ho, Wo, Cout, dtype=torch.bfloat16, device=dev)
+        stats = torch.empty(2, Cout, dtype=torch.float32, device=dev)
+        scratch = torch.empty(max(d._fwd_scratch, 16), dtype=torch.uint8, device=dev)
+        if residual is not None and not residual.is_contiguous():
+            residual = residual.contiguous()
+        L.conv_bn_fwd(d, x, residual, y, z, stats[0], stats[1], scratch)
+        ctx.mod, ctx.geom, ctx.has_res = mod, (N, H, W, Cin), residual is not None
+        ctx.save_for_backward(x, y, z, stats)
+        return z
+
+    @staticmethod
+    def backward(ctx, dz):
+        x, y, z, stats = ctx.saved_tensors
+        mod = ctx.mod
+        N, H, W, Cin = ctx.geom
+        dev = x.device
+        if not dz.is_contiguous():
+            dz = dz.contiguous()
+        need_dx = ctx.needs_input_grad[0]
+        d = _conv_desc(mod, N, H, W, Cin, True)
+        dx = torch.empty(N, H, W, Cin, dtype=torch.bfloat16, device=dev) if need_dx else None
+        dres = torch.empty_like(z) if ctx.has_res else None
+        scratch = torch.empty(d._bwd_scratch[1 if need_dx else 0], dtype=torch.uint8, device=dev)
+        L.conv_bn_bwd(d, x, y, z, stats[0], stats[1], dz, dx, dres, scratch)
+        return dx, dres, None, None, None, None
+
+
+# One foreign call per layer and direction (False, or an active lib.gemm_hook: one call per kernel)
+NATIVE_LAYERS = True
 
 
 class _ConvBNFn(torch.autograd.Function):
@@ -110,7 +180,8 @@ class ConvBN(nn.Module):
         return L.im2col(x, col, self.k, self.stride, self.pad, Ho, Wo)
 
     def forward(self, x, residual=None):
-        return _ConvBNFn.apply(x, residual, self, self.weight, self.bn_weight, self.bn_bias)
+        fn = _ConvBNNativeFn if (NATIVE_LAYERS and L.gemm_hook is None) else _ConvBNFn
+        return fn.apply(x, residual, self, self.weight, self.bn_weight, self.bn_bias)
 
 
 class _MaxPoolFn(torch.autograd.Function):

@@ -222,6 +222,24 @@ int bb_bn_apply(const void* y, const float* mean, const float* rstd, const void*
 int bb_bn_bwd(const void* dz, const void* z, const void* y, const float* mean, const float* rstd, const void* gamma,
               void* dy, void* dres, float* dgamma, float* dbeta, long long rows, int C, int relu, void* workspace,
               long long workspace_bytes, void* stream);
+/* One call per layer: convolution + batch norm (+ residual, + ReLU), forward and backward, issuing
+ * the kernels above in order (patch gather, GEMM, statistics, normalise / batch-norm backward,
+ * patch gather, weight-gradient GEMM, input-gradient GEMM, adjoint gather).  y is the
+ * convolution output kept for the backward pass, z the layer output; dx / dres may be NULL.
+ * `scratch`: bb_conv_bn_scratch_bytes(desc, backward, need_dx).  Replaces one Conv2d + BatchNorm2d
+ * (+ add + ReLU) of a bottleneck block and their share of loss.backward(). */
+typedef struct bb_conv_desc {
+  int N, H, W, Cin, Cout, k, stride, pad, relu;
+  float eps;
+  int max_ctas;                       /* forwarded to every GEMM (see bb_gemm_desc.max_ctas) */
+  const void *w, *gamma, *beta;       /* bf16: weight [Cout, k, k, Cin], batch-norm gain and bias */
+  float *g_w, *g_gamma, *g_beta;      /* fp32 gradient accumulators (backward only) */
+} bb_conv_desc;
+long long bb_conv_bn_scratch_bytes(const bb_conv_desc* d, int backward, int need_dx);
+int bb_conv_bn_fwd(const bb_conv_desc* d, const void* x, const void* residual, void* y, void* z, float* mean, float* rstd,
+                   void* scratch, long long scratch_bytes, void* stream);
+int bb_conv_bn_bwd(const bb_conv_desc* d, const void* x, const void* y, const void* z, const float* mean, const float* rstd,
+                   const void* dz, void* dx, void* dres, void* scratch, long long scratch_bytes, void* stream);
 /* 3 x 3 / stride 2 / padding 1 max pooling (argmax: 1 byte per output element, position 0..8 in
  * the window, first maximum wins) and global average pooling over HW pixels.
  * Replaces: model.maxpool / model.avgpool of the same layer list. */
