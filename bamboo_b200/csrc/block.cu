@@ -33,7 +33,7 @@ AttnLayout attn_layout(const bb_block_desc* d) {
   L.datt = o; o += align256(T * h * 2);
   L.dqkv = o; o += align256(T * 3 * h * 2);
   L.dh1 = o;  o += align256(T * h * 2);
-  L.ws_ln = o;     o += align256(bb_layernorm_bwd_workspace_bytes((int)T, (int)h));
+  L.ws_ln = o;     o += align256(bb_layernorm_bwd_res_workspace_bytes((int)T, (int)h));
   L.ws_attn = o;   o += align256(bb_attention_bwd_workspace_bytes(d->batch, d->heads, d->seq));
   L.ws_colsum = o; o += align256(bb_colsum_workspace_bytes((int)T, (int)(3 * h)));
   L.scratch_total = o;
@@ -53,8 +53,8 @@ MlpLayout mlp_layout(const bb_block_desc* d) {
   o = 0;
   L.dpre = o; o += align256(T * f * 2);
   L.dh2 = o;  o += align256(T * h * 2);
-  L.ws_ln = o;     o += align256(bb_layernorm_bwd_workspace_bytes((int)T, (int)h));
-  L.ws_colsum = o; o += align256(bb_colsum_workspace_bytes((int)T, (int)(f > h ? f : h)));
+  L.ws_ln = o;     o += align256(bb_layernorm_bwd_res_workspace_bytes((int)T, (int)h));
+  L.ws_colsum = o; o += align256(bb_colsum_workspace_bytes((int)T, (int)f));
   L.scratch_total = o;
   return L;
 }
@@ -162,11 +162,12 @@ extern "C" int bb_block_half_bwd(const bb_block_desc* d, int half, const void* x
     // weight and bias gradients beside the chain
     BB_TRY(fork_to(stream, side_stream));
     BB_TRY(gemm(d, h, h, T, dout, h, 1, att, h, 1, d->g_w2, h, BB_EPI_ACCUM_F32, nullptr, nullptr, nullptr, 0, side_stream));
-    BB_TRY(bb_colsum_accum(dout, h, d->g_b2, sc + L.ws_colsum, bb_colsum_workspace_bytes(T, h), T, h, side_stream));
     BB_TRY(gemm(d, 3 * h, h, T, dqkv, 3LL * h, 1, h1, h, 1, d->g_w1, h, BB_EPI_ACCUM_F32, nullptr, nullptr, nullptr, 0, side_stream));
     BB_TRY(bb_colsum_accum(dqkv, 3LL * h, d->g_b1, sc + L.ws_colsum, bb_colsum_workspace_bytes(T, 3 * h), T, 3 * h, side_stream));
-    BB_TRY(bb_layernorm_bwd(dh1, x, d->ln_w, mean, rstd, dout, dx, d->g_ln_w, d->g_ln_b, sc + L.ws_ln,
-                            bb_layernorm_bwd_workspace_bytes(T, h), T, h, stream));
+    // the LayerNorm backward reads dout as the residual gradient: the projection's bias gradient
+    // (dout's column sums) comes out of the same pass
+    BB_TRY(bb_layernorm_bwd_res(dh1, x, d->ln_w, mean, rstd, dout, dx, d->g_ln_w, d->g_ln_b, d->g_b2, sc + L.ws_ln,
+                                bb_layernorm_bwd_res_workspace_bytes(T, h), T, h, stream));
     return BB_OK;
   }
   const MlpLayout L = mlp_layout(d);
@@ -180,10 +181,9 @@ extern "C" int bb_block_half_bwd(const bb_block_desc* d, int half, const void* x
   BB_TRY(gemm(d, T, h, f, dpre, f, 0, d->w1, h, 1, dh2, h, BB_EPI_STORE, nullptr, nullptr, nullptr, 0, stream));
   BB_TRY(fork_to(stream, side_stream));
   BB_TRY(gemm(d, h, f, T, dout, h, 1, act, f, 1, d->g_w2, f, BB_EPI_ACCUM_F32, nullptr, nullptr, nullptr, 0, side_stream));
-  BB_TRY(bb_colsum_accum(dout, h, d->g_b2, sc + L.ws_colsum, bb_colsum_workspace_bytes(T, h), T, h, side_stream));
   BB_TRY(gemm(d, f, h, T, dpre, f, 1, h2, h, 1, d->g_w1, h, BB_EPI_ACCUM_F32, nullptr, nullptr, nullptr, 0, side_stream));
   BB_TRY(bb_colsum_accum(dpre, f, d->g_b1, sc + L.ws_colsum, bb_colsum_workspace_bytes(T, f), T, f, side_stream));
-  BB_TRY(bb_layernorm_bwd(dh2, x, d->ln_w, mean, rstd, dout, dx, d->g_ln_w, d->g_ln_b, sc + L.ws_ln,
-                          bb_layernorm_bwd_workspace_bytes(T, h), T, h, stream));
+  BB_TRY(bb_layernorm_bwd_res(dh2, x, d->ln_w, mean, rstd, dout, dx, d->g_ln_w, d->g_ln_b, d->g_b2, sc + L.ws_ln,
+                              bb_layernorm_bwd_res_workspace_bytes(T, h), T, h, stream));
   return BB_OK;
 }

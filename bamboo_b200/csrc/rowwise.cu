@@ -6,6 +6,7 @@
 #include "common.cuh"
 #include <stdio.h>
 #include <stdlib.h>
+#include <atomic>
 
 namespace {
 
@@ -199,97 +200,129 @@ layernorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat
 
 // Column-owner variant (hidden sizes that are a multiple of 256, up to 8192): a thread owns 8
 // columns of one of `slots` row slots; its dgamma/dbeta partial sums are 16 registers, so several
-// CTAs fit on an SM and every thread keeps 2 x LNB_R 16-byte loads in flight (the warp-per-row
-// kernels hold a whole row's partial sums per warp, run one CTA per SM and are latency-bound at
-// about a third of the HBM rate).  The two row sums of LNB_R rows per slot are combined across
-// the slot's warps through double-buffered shared memory: one block barrier per 8 rows.
-constexpr int LNB_R = 4;
-template <int MAXT>
-__global__ void __launch_bounds__(MAXT, MAXT <= 256 ? 2 : 1)
+// CTAs fit on an SM (the warp-per-row kernels hold a whole row's partial sums per warp, run one
+// CTA per SM and are latency-bound at about a third of the HBM rate).  Every operand of the R rows
+// a thread handles per iteration - dy, x and the residual gradient - is requested before the first
+// use, so a thread keeps 3 x R 16-byte loads in flight and an iteration pays one memory latency.
+// The two row sums of R rows per slot are combined across the slot's warps through
+// double-buffered shared memory: one block barrier per iteration.
+// SUMRES: the thread also keeps the column sums of the residual gradient (a third partial row).
+template <int CW> struct ColVec;
+template <> struct ColVec<8> {
+  using T = uint4;
+  static __device__ __forceinline__ T zero() { return make_uint4(0, 0, 0, 0); }
+  static __device__ __forceinline__ void unpack(const T& q, float* f) { unpack8(q, f); }
+  static __device__ __forceinline__ T pack(const float* f) { return pack8(f); }
+  static __device__ __forceinline__ void opaque(T& q) { asm volatile("" : "+r"(q.x), "+r"(q.y), "+r"(q.z), "+r"(q.w)); }
+};
+template <> struct ColVec<4> {
+  using T = uint2;
+  static __device__ __forceinline__ T zero() { return make_uint2(0, 0); }
+  static __device__ __forceinline__ void unpack(const T& q, float* f) {
+    f[0] = bb::bf16_lo(q.x); f[1] = bb::bf16_hi(q.x); f[2] = bb::bf16_lo(q.y); f[3] = bb::bf16_hi(q.y);
+  }
+  static __device__ __forceinline__ T pack(const float* f) { return make_uint2(bb::pack_bf16x2(f[0], f[1]), bb::pack_bf16x2(f[2], f[3])); }
+  static __device__ __forceinline__ void opaque(T& q) { asm volatile("" : "+r"(q.x), "+r"(q.y)); }
+};
+
+// CW: columns per thread (8: 16-byte accesses; 4: 8-byte accesses and half the registers, for
+// hidden sizes up to 1024 where more resident warps matter more than the access width).
+template <int MAXT, int CW, int R, int MINB, bool SUMRES>
+__global__ void __launch_bounds__(MAXT, MINB)
 layernorm_bwd_cols_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                           const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
                           const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
                           __nv_bfloat16* __restrict__ dx, float* __restrict__ partials, int rows, int h, int slots) {
   extern __shared__ float sm[];
-  const int tpr = h >> 3;                          // threads per row
+  using V = ColVec<CW>;
+  using VT = typename V::T;
+  constexpr int NS = SUMRES ? 3 : 2;               // partial rows per CTA: dgamma, dbeta (, residual sums)
+  const int tpr = h / CW;                          // threads per row
   const int wps = tpr >> 5;                        // warps per slot
-  const int slot = threadIdx.x / tpr, tc = threadIdx.x - slot * tpr;   // my slot, my 8-column group
+  const int slot = threadIdx.x / tpr, tc = threadIdx.x - slot * tpr;   // my slot, my column group
   const int lane = threadIdx.x & 31, wis = tc >> 5;
-  float* red = sm;                                 // [2][slots][wps][2 * LNB_R]
-  float* fin = sm + 2 * slots * wps * 2 * LNB_R;   // [slots][2][h] final combination
-  float g[8], ag[8], ab[8];
-  unpack8(__ldg(reinterpret_cast<const uint4*>(gamma) + tc), g);
+  float* red = sm;                                 // [2][slots][wps][2 * R]
+  float* fin = sm + 2 * slots * wps * 2 * R;       // [slots][NS][h] final combination
+  float g[CW], ag[CW], ab[CW], ar[CW];
+  V::unpack(__ldg(reinterpret_cast<const VT*>(gamma) + tc), g);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) { ag[i] = 0.f; ab[i] = 0.f; }
+  for (int i = 0; i < CW; ++i) { ag[i] = 0.f; ab[i] = 0.f; ar[i] = 0.f; }
   const float inv_h = 1.f / h;
   int buf = 0;
-  for (int base = blockIdx.x * slots * LNB_R; base < rows; base += gridDim.x * slots * LNB_R) {
-    const int r0 = base + slot * LNB_R;
-    uint4 qd[LNB_R], qx[LNB_R];
-    float mean[LNB_R], rstd[LNB_R];
+  for (int base = blockIdx.x * slots * R; base < rows; base += gridDim.x * slots * R) {
+    const int r0 = base + slot * R;
+    VT qd[R], qx[R], qr[R];
+    float mean[R], rstd[R];
 #pragma unroll
-    for (int r = 0; r < LNB_R; ++r) {
+    for (int r = 0; r < R; ++r) {
       const int row = r0 + r;
+      qd[r] = V::zero(); qx[r] = qd[r]; qr[r] = qd[r]; mean[r] = 0.f; rstd[r] = 0.f;
       if (row < rows) {
-        qd[r] = reinterpret_cast<const uint4*>(dy + (size_t)row * h)[tc];
-        qx[r] = reinterpret_cast<const uint4*>(x + (size_t)row * h)[tc];
+        qd[r] = reinterpret_cast<const VT*>(dy + (size_t)row * h)[tc];
+        qx[r] = reinterpret_cast<const VT*>(x + (size_t)row * h)[tc];
+        if (dres) qr[r] = reinterpret_cast<const VT*>(dres + (size_t)row * h)[tc];
         mean[r] = mean_in[row]; rstd[r] = rstd_in[row];
-      } else {
-        qd[r] = make_uint4(0, 0, 0, 0); qx[r] = qd[r]; mean[r] = 0.f; rstd[r] = 0.f;
       }
     }
-    float s[2 * LNB_R];
+    float s[2 * R];
 #pragma unroll
-    for (int r = 0; r < LNB_R; ++r) {
-      float d[8], f[8];
-      unpack8(qd[r], d); unpack8(qx[r], f);
+    for (int r = 0; r < R; ++r) {
+      float d[CW], f[CW];
+      V::unpack(qd[r], d); V::unpack(qx[r], f);
       float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) { const float t = d[i] * g[i]; s1 += t; s2 += t * (f[i] - mean[r]) * rstd[r]; }
+      for (int i = 0; i < CW; ++i) { const float t = d[i] * g[i]; s1 += t; s2 += t * (f[i] - mean[r]) * rstd[r]; }
       s[2 * r] = s1; s[2 * r + 1] = s2;
     }
 #pragma unroll
-    for (int k = 0; k < 2 * LNB_R; ++k) s[k] = warp_sum(s[k]);
-    float* my = red + ((buf * slots + slot) * wps + wis) * 2 * LNB_R;
+    for (int k = 0; k < 2 * R; ++k) s[k] = warp_sum(s[k]);
+    float* my = red + ((buf * slots + slot) * wps + wis) * 2 * R;
     if (lane == 0) {
 #pragma unroll
-      for (int k = 0; k < 2 * LNB_R; ++k) my[k] = s[k];
+      for (int k = 0; k < 2 * R; ++k) my[k] = s[k];
     }
     __syncthreads();
-    const float* all = red + (buf * slots + slot) * wps * 2 * LNB_R;
+    // the operands stay packed across the barrier (the compiler would otherwise keep the unpacked
+    // floats of the first pass alive: twice the registers)
 #pragma unroll
-    for (int k = 0; k < 2 * LNB_R; ++k) {
+    for (int r = 0; r < R; ++r) { V::opaque(qd[r]); V::opaque(qx[r]); }
+    const float* all = red + (buf * slots + slot) * wps * 2 * R;
+#pragma unroll
+    for (int k = 0; k < 2 * R; ++k) {
       float t = 0.f;
-      for (int w = 0; w < wps; ++w) t += all[w * 2 * LNB_R + k];    // fixed order
+      for (int w = 0; w < wps; ++w) t += all[w * 2 * R + k];    // fixed order
       s[k] = t * inv_h;
     }
     buf ^= 1;
 #pragma unroll
-    for (int r = 0; r < LNB_R; ++r) {
+    for (int r = 0; r < R; ++r) {
       const int row = r0 + r;
       if (row >= rows) continue;
-      float d[8], f[8], o[8], rr[8];
-      unpack8(qd[r], d); unpack8(qx[r], f);
-      if (dres) unpack8(reinterpret_cast<const uint4*>(dres + (size_t)row * h)[tc], rr);
+      float d[CW], f[CW], o[CW], rr[CW];
+      V::unpack(qd[r], d); V::unpack(qx[r], f); V::unpack(qr[r], rr);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < CW; ++i) {
         const float xh = (f[i] - mean[r]) * rstd[r];
-        o[i] = rstd[r] * (d[i] * g[i] - s[2 * r] - xh * s[2 * r + 1]) + (dres ? rr[i] : 0.f);
+        o[i] = rstd[r] * (d[i] * g[i] - s[2 * r] - xh * s[2 * r + 1]) + rr[i];
         ag[i] += d[i] * xh;
         ab[i] += d[i];
+        if (SUMRES) ar[i] += rr[i];
       }
-      reinterpret_cast<uint4*>(dx + (size_t)row * h)[tc] = pack8(o);
+      reinterpret_cast<VT*>(dx + (size_t)row * h)[tc] = V::pack(o);
     }
   }
-  // combine the slots' column sums (fixed order) and write this CTA's partial row
-  float* mine = fin + (size_t)slot * 2 * h;
+  // combine the slots' column sums (fixed order) and write this CTA's partial rows
+  float* mine = fin + (size_t)slot * NS * h;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) { mine[tc * 8 + i] = ag[i]; mine[h + tc * 8 + i] = ab[i]; }
+  for (int i = 0; i < CW; ++i) {
+    mine[tc * CW + i] = ag[i]; mine[h + tc * CW + i] = ab[i];
+    if (SUMRES) mine[2 * h + tc * CW + i] = ar[i];
+  }
   __syncthreads();
-  float* out = partials + (size_t)blockIdx.x * 2 * h;
-  for (int j = threadIdx.x; j < 2 * h; j += blockDim.x) {
+  float* out = partials + (size_t)blockIdx.x * NS * h;
+  for (int j = threadIdx.x; j < NS * h; j += blockDim.x) {
     float t = 0.f;
-    for (int q = 0; q < slots; ++q) t += fin[(size_t)q * 2 * h + j];
+    for (int q = 0; q < slots; ++q) t += fin[(size_t)q * NS * h + j];
     out[j] = t;
   }
 }
@@ -297,15 +330,15 @@ layernorm_bwd_cols_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloa
 // out[j] += sum_p partials[p * stride + j].  A 32-column x 8-way block: eight threads share
 // a column, each sums every eighth partial, shared memory combines them in a fixed order
 // (deterministic).
-// blockIdx.y selects one of two (partials, out) pairs, `pair_offset` floats apart in `partials`
-// (LayerNorm: dgamma and dbeta in one launch).
+// blockIdx.y selects one of up to three (partials, out) pairs, `pair_offset` floats apart in
+// `partials` (LayerNorm: dgamma, dbeta and the residual gradient's column sums in one launch).
 __global__ void __launch_bounds__(256)
 reduce_partials_kernel(const float* __restrict__ partials, float* __restrict__ out0, float* __restrict__ out1,
-                       long long pair_offset, int nparts, int n, long long stride) {
+                       float* __restrict__ out2, long long pair_offset, int nparts, int n, long long stride) {
   __shared__ float red[8][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int j = blockIdx.x * 32 + tx;
-  float* out = blockIdx.y ? out1 : out0;
+  float* out = blockIdx.y == 0 ? out0 : (blockIdx.y == 1 ? out1 : out2);
   partials += blockIdx.y * pair_offset;
   float s = 0.f;
   if (j < n)
@@ -321,19 +354,43 @@ reduce_partials_kernel(const float* __restrict__ partials, float* __restrict__ o
 }
 
 // ------------------------------------------------------------------ bias gradient
-// partials[split][n] = sum over this split's rows of dy[row][n]
+// out[n] += sum over rows of dy[row][n], one launch.  CTA (bx, by) sums the rows of split `by`
+// over 256 columns (a warp reads 512 contiguous bytes of a row, four rows in flight per warp)
+// and writes one partial row; the CTA that finishes last for its 256 columns (a ticket counter
+// per column block) adds the partial rows in split order, so the result does not depend on the
+// order in which CTAs ran.  The counter returns to zero for its next user.
+constexpr int COLSUM_TICKET_SLOTS = 1 << 16;
+__device__ unsigned int g_colsum_tickets[COLSUM_TICKET_SLOTS];
+
 __global__ void __launch_bounds__(256)
-colsum_kernel(const __nv_bfloat16* __restrict__ dy, float* __restrict__ partials, int rows, int n, long long ld, int rows_per_split) {
+colsum_kernel(const __nv_bfloat16* __restrict__ dy, float* __restrict__ partials, float* __restrict__ out, int rows, int n,
+              long long ld, int rows_per_split, unsigned int* __restrict__ tickets) {
   __shared__ float red[8][256];
+  __shared__ int s_last;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int col0 = blockIdx.x * 256 + lane * 8;
   const int r0 = blockIdx.y * rows_per_split;
   const int r1 = min(rows, r0 + rows_per_split);
+  const int splits = gridDim.y;
   float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (col0 < n) {
-    for (int r = r0 + warp; r < r1; r += 8) {
+    const __nv_bfloat16* src = dy + col0;
+    int r = r0 + warp;
+    for (; r + 24 < r1; r += 32) {
+      uint4 q[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) q[u] = *reinterpret_cast<const uint4*>(src + (size_t)(r + 8 * u) * ld);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float f[8];
+        unpack8(q[u], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s[i] += f[i];
+      }
+    }
+    for (; r < r1; r += 8) {
       float f[8];
-      unpack8(*reinterpret_cast<const uint4*>(dy + (size_t)r * ld + col0), f);
+      unpack8(*reinterpret_cast<const uint4*>(src + (size_t)r * ld), f);
 #pragma unroll
       for (int i = 0; i < 8; ++i) s[i] += f[i];
     }
@@ -342,12 +399,34 @@ colsum_kernel(const __nv_bfloat16* __restrict__ dy, float* __restrict__ partials
   for (int i = 0; i < 8; ++i) red[warp][lane * 8 + i] = s[i];
   __syncthreads();
   const int j = threadIdx.x, col = blockIdx.x * 256 + j;
-  if (col < n) {
-    float t = 0.f;
+  float t = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) t += red[w][j];
-    partials[(size_t)blockIdx.y * n + col] = t;
+  for (int w = 0; w < 8; ++w) t += red[w][j];
+  if (splits == 1) {
+    if (col < n) out[col] += t;
+    return;
   }
+  if (col < n) partials[(size_t)blockIdx.y * n + col] = t;
+  __threadfence();                                   // my partial is visible before my ticket
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(&tickets[blockIdx.x], 1u) == (unsigned)(splits - 1));
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (col < n) {
+    float acc = 0.f;
+    int p = 0;
+    for (; p + 8 <= splits; p += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldcg(partials + (size_t)(p + u) * n + col);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) acc += v[u];
+    }
+    for (; p < splits; ++p) acc += __ldcg(partials + (size_t)p * n + col);
+    out[col] += acc;
+  }
+  if (threadIdx.x == 0) tickets[blockIdx.x] = 0u;
 }
 
 // ------------------------------------------------------------------ GeLU backward (stand-alone)
@@ -443,11 +522,33 @@ bool ln_bwd_cols_ok(int h) {
   if (off < 0) { const char* e = getenv("BB_LN_BWD_ROWS"); off = (e && e[0] == '1') ? 1 : 0; }   // 1: warp-per-row kernels
   return !off && h % 256 == 0 && h <= 8192;
 }
-int ln_bwd_cols_slots(int h) { const int tpr = h / 8; return tpr >= 256 ? 1 : 256 / tpr; }
+// Shape of the column-owner kernel for a hidden size: columns per thread, rows per slot per
+// iteration, resident CTAs per SM (what the register count of that instantiation allows) and
+// the CTA size bound.  Every instantiation below compiles without register spills.
+struct LnColsCfg { int cw, r, ctas, maxt; };
+LnColsCfg ln_cols_cfg(int h) {
+  if (h <= 1024) {
+    // BB_LN_BWD_VARIANT=0..4 in the environment picks another instantiation (A/B measurements)
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("BB_LN_BWD_VARIANT"); v = (e && e[0] >= '0' && e[0] <= '4') ? e[0] - '0' : 0; }
+    switch (v) {
+      case 1: return {4, 2, 4, 256};
+      case 2: return {4, 8, 2, 256};
+      case 3: return {8, 3, 2, 256};
+      case 4: return {8, 2, 3, 256};
+      default: return {4, 4, 3, 256};
+    }
+  }
+  if (h <= 2048) return {8, 2, 3, 256};
+  if (h <= 4096) return {8, 4, 1, 512};
+  return {8, 1, 1, 1024};
+}
+int ln_bwd_cols_slots(int h) { const int tpr = h / ln_cols_cfg(h).cw; return tpr >= 256 ? 1 : 256 / tpr; }
 int ln_bwd_grid(int rows, int h) {
   if (ln_bwd_cols_ok(h)) {
-    const int per = ln_bwd_cols_slots(h) * LNB_R;
-    long long want = ((long long)rows + per - 1) / per, cap = 2LL * bb_num_sms();
+    const LnColsCfg c = ln_cols_cfg(h);
+    const int per = ln_bwd_cols_slots(h) * c.r;
+    long long want = ((long long)rows + per - 1) / per, cap = (long long)c.ctas * bb_num_sms();
     return (int)(want < cap ? (want > 0 ? want : 1) : cap);
   }
   const int w = ln_bwd_warps(h);
@@ -458,27 +559,41 @@ int ln_bwd_grid(int rows, int h) {
 }  // namespace
 
 namespace {
-// launches the backward main kernel (register variant when the hidden size allows it)
-int ln_bwd_main(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, const void* dres,
-                void* dx, float* ws, int rows, int h, int grid, int warps, cudaStream_t s) {
-  if (ln_bwd_cols_ok(h)) {
-    const int slots = ln_bwd_cols_slots(h), tpr = h / 8;
-    const size_t sm_bytes = ((size_t)2 * slots * (tpr / 32) * 2 * LNB_R + (size_t)slots * 2 * h) * sizeof(float);
-    BB_ONCE_PER_DEVICE({
-      BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_cols_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
-      BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_cols_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
-      BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_cols_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
-    });
-    const int threads = slots * tpr;
+template <int MAXT, int CW, int R, int MINB>
+int ln_bwd_cols_launch(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, const void* dres,
+                       void* dx, float* ws, bool sum_res, int rows, int h, int grid, cudaStream_t s) {
+  const int slots = ln_bwd_cols_slots(h), tpr = h / CW, threads = slots * tpr;
+  const size_t sm_bytes = ((size_t)2 * slots * (tpr / 32) * 2 * R + (size_t)slots * (sum_res ? 3 : 2) * h) * sizeof(float);
+  BB_ONCE_PER_DEVICE({
+    BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_cols_kernel<MAXT, CW, R, MINB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+    BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_cols_kernel<MAXT, CW, R, MINB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+  });
 #define BB_LNC_ARGS (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, mean, rstd, \
                     (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, ws, rows, h, slots
-    if (threads <= 256) layernorm_bwd_cols_kernel<256><<<grid, threads, sm_bytes, s>>>(BB_LNC_ARGS);
-    else if (threads <= 512) layernorm_bwd_cols_kernel<512><<<grid, threads, sm_bytes, s>>>(BB_LNC_ARGS);
-    else layernorm_bwd_cols_kernel<1024><<<grid, threads, sm_bytes, s>>>(BB_LNC_ARGS);
+  if (sum_res) layernorm_bwd_cols_kernel<MAXT, CW, R, MINB, true><<<grid, threads, sm_bytes, s>>>(BB_LNC_ARGS);
+  else layernorm_bwd_cols_kernel<MAXT, CW, R, MINB, false><<<grid, threads, sm_bytes, s>>>(BB_LNC_ARGS);
 #undef BB_LNC_ARGS
-    BB_CUDA_CHECK(cudaGetLastError());
-    return BB_OK;
+  BB_CUDA_CHECK(cudaGetLastError());
+  return BB_OK;
+}
+
+// launches the backward main kernel (column-owner variant when the hidden size allows it); with
+// `sum_res` (column-owner variant only) every CTA writes a third partial row: the residual
+// gradient's column sums
+int ln_bwd_main(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, const void* dres,
+                void* dx, float* ws, bool sum_res, int rows, int h, int grid, int warps, cudaStream_t s) {
+  if (ln_bwd_cols_ok(h)) {
+    const LnColsCfg c = ln_cols_cfg(h);
+#define BB_LNC_CASE(MAXT, CW, R, MINB) \
+    if (c.maxt == MAXT && c.cw == CW && c.r == R && c.ctas == MINB) \
+      return ln_bwd_cols_launch<MAXT, CW, R, MINB>(dy, x, gamma, mean, rstd, dres, dx, ws, sum_res, rows, h, grid, s);
+    BB_LNC_CASE(256, 4, 4, 3) BB_LNC_CASE(256, 4, 2, 4) BB_LNC_CASE(256, 4, 8, 2) BB_LNC_CASE(256, 8, 3, 2)
+    BB_LNC_CASE(256, 8, 2, 3) BB_LNC_CASE(512, 8, 4, 1) BB_LNC_CASE(1024, 8, 1, 1)
+#undef BB_LNC_CASE
+    bb_set_last_error_msg("layernorm backward: no column-owner instantiation for this shape");
+    return BB_ERR_INVALID_ARG;
   }
+  if (sum_res) { bb_set_last_error_msg("layernorm backward: residual sums need the column-owner kernel"); return BB_ERR_INVALID_ARG; }
   const size_t smem = (size_t)warps * 2 * h * sizeof(float);
   BB_ONCE_PER_DEVICE({
     BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
@@ -503,15 +618,28 @@ extern "C" long long bb_layernorm_bwd_workspace_bytes(int rows, int h) {
   return (long long)ln_bwd_grid(rows, h) * 2 * h * (long long)sizeof(float);
 }
 
+namespace {
+int ln_bwd_check(const char* who, const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
+                 const void* dx, const float* dgamma, const float* dbeta, const void* workspace, int rows, int h) {
+  char msg[160];
+  if (!dy || !x || !gamma || !mean || !rstd || !dx || !dgamma || !dbeta || !workspace || rows <= 0 || h <= 0 || (h & 7)) {
+    snprintf(msg, sizeof(msg), "%s: null pointer or hidden size not a multiple of 8", who);
+    bb_set_last_error_msg(msg);
+    return BB_ERR_INVALID_ARG;
+  }
+  if (ln_bwd_warps(h) < 1) {
+    snprintf(msg, sizeof(msg), "%s: hidden size too large (max 25600)", who);
+    bb_set_last_error_msg(msg);
+    return BB_ERR_TOO_LARGE;
+  }
+  return BB_OK;
+}
+}  // namespace
+
 extern "C" int bb_layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
                                 const void* dres, void* dx, float* dgamma, float* dbeta, void* workspace,
                                 long long workspace_bytes, int rows, int h, void* stream) {
-  if (!dy || !x || !gamma || !mean || !rstd || !dx || !dgamma || !dbeta || !workspace || rows <= 0 || h <= 0 || (h & 7)) {
-    bb_set_last_error_msg("bb_layernorm_bwd: null pointer or hidden size not a multiple of 8");
-    return BB_ERR_INVALID_ARG;
-  }
-  const int warps = ln_bwd_warps(h);
-  if (warps < 1) { bb_set_last_error_msg("bb_layernorm_bwd: hidden size too large (max 25600)"); return BB_ERR_TOO_LARGE; }
+  if (int rc = ln_bwd_check("bb_layernorm_bwd", dy, x, gamma, mean, rstd, dx, dgamma, dbeta, workspace, rows, h)) return rc;
   if (workspace_bytes < bb_layernorm_bwd_workspace_bytes(rows, h)) {
     bb_set_last_error_msg("bb_layernorm_bwd: workspace smaller than bb_layernorm_bwd_workspace_bytes()");
     return BB_ERR_INVALID_ARG;
@@ -519,8 +647,8 @@ extern "C" int bb_layernorm_bwd(const void* dy, const void* x, const void* gamma
   cudaStream_t s = (cudaStream_t)stream;
   const int grid = ln_bwd_grid(rows, h);
   float* ws = (float*)workspace;
-  if (int rc = ln_bwd_main(dy, x, gamma, mean, rstd, dres, dx, ws, rows, h, grid, warps, s)) return rc;
-  reduce_partials_kernel<<<dim3((h + 31) / 32, 2), 256, 0, s>>>(ws, dgamma, dbeta, (long long)h, grid, h, 2LL * h);
+  if (int rc = ln_bwd_main(dy, x, gamma, mean, rstd, dres, dx, ws, false, rows, h, grid, ln_bwd_warps(h), s)) return rc;
+  reduce_partials_kernel<<<dim3((h + 31) / 32, 2), 256, 0, s>>>(ws, dgamma, dbeta, nullptr, (long long)h, grid, h, 2LL * h);
   BB_CUDA_CHECK(cudaGetLastError());
   return BB_OK;
 }
@@ -577,16 +705,39 @@ extern "C" int bb_layernorm_bwd_static(const void* dy, const void* x, const void
   const int grid = ln_bwd_grid(rows, h);
   // every partial row that the reduction reads is rewritten by this launch, so the scratch
   // needs no clearing although it still holds the previous call's sums
-  if (int rc = ln_bwd_main(dy, x, gamma, mean, rstd, dres, dx, ws, rows, h, grid, warps, s)) return rc;
-  reduce_partials_kernel<<<dim3((h + 31) / 32, 2), 256, 0, s>>>(ws, dgamma, dbeta, (long long)h, grid, h, 2LL * h);
+  if (int rc = ln_bwd_main(dy, x, gamma, mean, rstd, dres, dx, ws, false, rows, h, grid, warps, s)) return rc;
+  reduce_partials_kernel<<<dim3((h + 31) / 32, 2), 256, 0, s>>>(ws, dgamma, dbeta, nullptr, (long long)h, grid, h, 2LL * h);
   BB_CUDA_CHECK(cudaGetLastError());
   return BB_OK;
 }
 
 namespace {
-int colsum_splits(int rows) {
-  int s = (rows + 255) / 256;
-  return s < 1 ? 1 : (s > 64 ? 64 : s);
+// enough splits for about four CTAs per SM, at least 32 rows each
+int colsum_splits(int rows, int n) {
+  const int col_blocks = (n + 255) / 256;
+  int s = (4 * bb_num_sms() + col_blocks - 1) / col_blocks;
+  const int by_rows = (rows + 31) / 32;
+  if (s > by_rows) s = by_rows;
+  return s < 1 ? 1 : (s > 256 ? 256 : s);
+}
+
+// ticket counters of one launch: `col_blocks` consecutive entries of the device table, handed out
+// round-robin so that launches in flight on different streams never share an entry
+unsigned int* colsum_tickets(int col_blocks) {
+  static unsigned int* table[64] = {nullptr};
+  static std::atomic<unsigned long long> next{0};
+  const int dev = bb_current_device();
+  if (dev < 0 || col_blocks > COLSUM_TICKET_SLOTS) return nullptr;
+  if (!table[dev]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_colsum_tickets) != cudaSuccess) return nullptr;
+    table[dev] = static_cast<unsigned int*>(ptr);
+  }
+  for (;;) {
+    const unsigned long long at = next.fetch_add((unsigned long long)col_blocks);
+    const unsigned first = (unsigned)(at % COLSUM_TICKET_SLOTS);
+    if (first + (unsigned)col_blocks <= (unsigned)COLSUM_TICKET_SLOTS) return table[dev] + first;   // else the range wraps: take the next one
+  }
 }
 }  // namespace
 
@@ -605,7 +756,7 @@ extern "C" int bb_gelu_bwd(const void* dy, const void* pre, void* dx, long long 
 
 extern "C" long long bb_colsum_workspace_bytes(int rows, int n) {
   if (rows <= 0 || n <= 0) return 0;
-  return (long long)colsum_splits(rows) * n * (long long)sizeof(float);
+  return (long long)colsum_splits(rows, n) * n * (long long)sizeof(float);
 }
 
 extern "C" int bb_colsum_accum(const void* dy, long long ld, float* out, void* workspace, long long workspace_bytes,
@@ -619,11 +770,45 @@ extern "C" int bb_colsum_accum(const void* dy, long long ld, float* out, void* w
     return BB_ERR_INVALID_ARG;
   }
   cudaStream_t s = (cudaStream_t)stream;
-  const int splits = colsum_splits(rows);
+  const int splits = colsum_splits(rows, n);
   const int rps = (rows + splits - 1) / splits;
   dim3 grid((n + 255) / 256, splits);
-  colsum_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)dy, (float*)workspace, rows, n, ld, rps);
-  reduce_partials_kernel<<<dim3((n + 31) / 32, 1), 256, 0, s>>>((const float*)workspace, out, nullptr, 0LL, splits, n, (long long)n);
+  unsigned int* tickets = colsum_tickets((int)grid.x);
+  if (!tickets) { bb_set_last_error_msg("bb_colsum_accum: ticket counters unavailable on this device"); return BB_ERR_CUDA; }
+  colsum_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)dy, (float*)workspace, out, rows, n, ld, rps, tickets);
+  BB_CUDA_CHECK(cudaGetLastError());
+  return BB_OK;
+}
+
+// ------------------------------------------------------------------ LayerNorm backward + residual column sums
+extern "C" long long bb_layernorm_bwd_res_workspace_bytes(int rows, int h) {
+  if (rows <= 0 || h <= 0 || ln_bwd_warps(h) < 1) return 0;
+  if (ln_bwd_cols_ok(h)) return (long long)ln_bwd_grid(rows, h) * 3 * h * (long long)sizeof(float);
+  // other hidden sizes: the plain backward, then a column-sum pass over the residual gradient
+  const long long a = (bb_layernorm_bwd_workspace_bytes(rows, h) + 255) & ~255LL;
+  return a + bb_colsum_workspace_bytes(rows, h);
+}
+
+extern "C" int bb_layernorm_bwd_res(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
+                                    const void* dres, void* dx, float* dgamma, float* dbeta, float* dres_sum, void* workspace,
+                                    long long workspace_bytes, int rows, int h, void* stream) {
+  if (int rc = ln_bwd_check("bb_layernorm_bwd_res", dy, x, gamma, mean, rstd, dx, dgamma, dbeta, workspace, rows, h)) return rc;
+  if (!dres || !dres_sum) { bb_set_last_error_msg("bb_layernorm_bwd_res: dres and dres_sum are required"); return BB_ERR_INVALID_ARG; }
+  if (workspace_bytes < bb_layernorm_bwd_res_workspace_bytes(rows, h)) {
+    bb_set_last_error_msg("bb_layernorm_bwd_res: workspace smaller than bb_layernorm_bwd_res_workspace_bytes()");
+    return BB_ERR_INVALID_ARG;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  float* ws = (float*)workspace;
+  if (!ln_bwd_cols_ok(h)) {
+    const long long a = (bb_layernorm_bwd_workspace_bytes(rows, h) + 255) & ~255LL;
+    // the column sums first: dx may alias dres
+    if (int rc = bb_colsum_accum(dres, h, dres_sum, (char*)workspace + a, workspace_bytes - a, rows, h, stream)) return rc;
+    return bb_layernorm_bwd(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, workspace, a, rows, h, stream);
+  }
+  const int grid = ln_bwd_grid(rows, h);
+  if (int rc = ln_bwd_main(dy, x, gamma, mean, rstd, dres, dx, ws, true, rows, h, grid, ln_bwd_warps(h), s)) return rc;
+  reduce_partials_kernel<<<dim3((h + 31) / 32, 3), 256, 0, s>>>(ws, dgamma, dbeta, dres_sum, (long long)h, grid, h, 3LL * h);
   BB_CUDA_CHECK(cudaGetLastError());
   return BB_OK;
 }

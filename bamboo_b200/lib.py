@@ -63,7 +63,7 @@ class ConvDesc(ctypes.Structure):
 HALF_ATTENTION, HALF_MLP = 0, 1
 # kernels behind one call of bb_block_half_fwd / bb_block_half_bwd, per half (launch accounting)
 HALF_FWD_LAUNCHES = {HALF_ATTENTION: 4, HALF_MLP: 3}
-HALF_BWD_LAUNCHES = {HALF_ATTENTION: 14, HALF_MLP: 11}
+HALF_BWD_LAUNCHES = {HALF_ATTENTION: 9, HALF_MLP: 7}   # + 1 for attention with a head dimension other than 64
 
 _lib = None
 _lock = threading.Lock()
@@ -208,7 +208,7 @@ def layernorm_fwd(x, gamma, beta, y, mean, rstd, eps=1e-5):
 
 def layernorm_bwd(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta):
     global LAUNCHES
-    LAUNCHES += 3
+    LAUNCHES += 2
     rows, h = x.numel() // x.shape[-1], x.shape[-1]
     lib = load()
     lib.bb_layernorm_bwd_workspace_bytes.restype = _LL
@@ -220,11 +220,26 @@ def layernorm_bwd(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta):
     return dx
 
 
+def layernorm_bwd_res(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, dres_sum):
+    """LayerNorm backward that also accumulates the column sums of ``dres`` into ``dres_sum`` (fp32)."""
+    global LAUNCHES
+    LAUNCHES += 2
+    lib = load()
+    rows, h = x.shape[0], x.shape[1]
+    lib.bb_layernorm_bwd_res_workspace_bytes.restype = _LL
+    need = lib.bb_layernorm_bwd_res_workspace_bytes(_I(rows), _I(h))
+    ws = workspace(need, "rowwise")
+    check(lib.bb_layernorm_bwd_res(_ptr(dy), _ptr(x), _ptr(gamma), _ptr(mean), _ptr(rstd), _ptr(dres), _ptr(dx),
+                                   _ptr(dgamma), _ptr(dbeta), _ptr(dres_sum), _ptr(ws), _LL(ws.numel()), _I(rows), _I(h),
+                                   _stream()), "bb_layernorm_bwd_res")
+    return dx
+
+
 def layernorm_bwd_static(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta):
     """LayerNorm backward through the entry point that allocates nothing: its scratch is an
     array inside the library (see bb_layernorm_bwd_static in the header for the limits)."""
     global LAUNCHES
-    LAUNCHES += 3
+    LAUNCHES += 2
     rows, h = x.numel() // x.shape[-1], x.shape[-1]
     check(load().bb_layernorm_bwd_static(_ptr(dy), _ptr(x), _ptr(gamma), _ptr(mean), _ptr(rstd), _ptr(dres), _ptr(dx),
                                          _ptr(dgamma), _ptr(dbeta), _I(rows), _I(h), _stream()),
@@ -236,7 +251,7 @@ def colsum_accum(dy, out, tag="rowwise", stream=None):
     """out(fp32)[n] += dy(bf16)[rows, n].sum(0); ``tag`` names the scratch buffer (calls that may
     overlap on the GPU, e.g. on different streams, need different ones)"""
     global LAUNCHES
-    LAUNCHES += 2
+    LAUNCHES += 1
     rows, n = dy.shape
     lib = load()
     lib.bb_colsum_workspace_bytes.restype = _LL
@@ -355,7 +370,7 @@ def block_half_fwd(desc, half, x, saved, out):
 def block_half_bwd(desc, half, x, saved, dout, dx, scratch, side_stream=None):
     """``side_stream``: raw handle of the stream for the weight gradients (None: the current stream)."""
     global LAUNCHES
-    LAUNCHES += HALF_BWD_LAUNCHES[half]
+    LAUNCHES += HALF_BWD_LAUNCHES[half] + (1 if half == HALF_ATTENTION and desc.head_dim != 64 else 0)
     main = _stream()
     side = main if side_stream is None else ctypes.c_void_p(side_stream)
     check(load().bb_block_half_bwd(ctypes.byref(desc), _I(half), _ptr(x), _ptr(saved), _ptr(dout), _ptr(dx), _ptr(scratch),

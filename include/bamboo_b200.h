@@ -89,6 +89,18 @@ long long bb_layernorm_bwd_workspace_bytes(int rows, int h);
 int bb_layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
                      const void* dres, void* dx, float* dgamma, float* dbeta, void* workspace,
                      long long workspace_bytes, int rows, int h, void* stream);
+/* The same, and dres_sum[h] (fp32) += the column sums of dres, from the same pass over dres.
+ * In a pre-LayerNorm block out = x + Linear(...), so the gradient of `out` is both the residual
+ * gradient of the block's LayerNorm and the row-wise gradient of that Linear's bias: its bias
+ * gradient comes out of this call instead of a separate pass over `dres` (bb_colsum_accum).
+ * dres and dres_sum are required; dx may alias dres.  Workspace:
+ * bb_layernorm_bwd_res_workspace_bytes.
+ * Replaces: the two autograd nodes above (LayerNorm backward and the bias-gradient reduction of
+ * nn.Linear, EX/pipeline_parallelism/gpt2.py:20-32,52-64 via DS/runtime/pipe/engine.py:1680-1727). */
+long long bb_layernorm_bwd_res_workspace_bytes(int rows, int h);
+int bb_layernorm_bwd_res(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
+                         const void* dres, void* dx, float* dgamma, float* dbeta, float* dres_sum, void* workspace,
+                         long long workspace_bytes, int rows, int h, void* stream);
 
 /* LayerNorm backward for callers that must not allocate device memory - code running inside
  * a memory-pool callback, a fixed-footprint serving process, or any host that is not allowed to
@@ -108,7 +120,9 @@ long long bb_layernorm_bwd_static_capacity_bytes(void);
 int bb_layernorm_bwd_static(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
                             const void* dres, void* dx, float* dgamma, float* dbeta, int rows, int h, void* stream);
 
-/* out[n] += sum_rows dy[row, n] : bias gradient of a linear layer (fp32 accumulate).
+/* out[n] += sum_rows dy[row, n] : bias gradient of a linear layer (fp32 accumulate).  One
+ * launch: per-CTA partial rows go to `workspace`, the CTA that finishes last for a block of 256
+ * columns adds them in a fixed order (the result does not depend on scheduling).
  * Replaces: the bias-gradient reduction autograd runs for nn.Linear
  * (EX/pipeline_parallelism/gpt2.py:52-64 via DS/runtime/pipe/engine.py:1680-1727). */
 long long bb_colsum_workspace_bytes(int rows, int n);

@@ -181,13 +181,62 @@ def test_layernorm(L, rows, h):
     close(db - 1, bf.grad)
 
 
-@pytest.mark.parametrize("rows,n", [(8192, 4096), (100, 264), (513, 1024), (1, 8)])
+@pytest.mark.parametrize("rows,h", [(8192, 1024), (777, 256), (300, 768), (1000, 2048), (515, 4096), (64, 8192), (100, 1000)])
+def test_layernorm_backward_with_residual_sums(L, rows, h):
+    """One pass gives dx, dgamma, dbeta and the column sums of the residual gradient; every
+    column-owner instantiation (hidden sizes up to 1024, 2048, 4096, 8192) and the fallback."""
+    torch.manual_seed(6)
+    x = torch.randn(rows, h, device="cuda").bfloat16()
+    g = (1 + 0.1 * torch.randn(h, device="cuda")).bfloat16()
+    b = torch.zeros(h, device="cuda").bfloat16()
+    y = torch.empty_like(x)
+    mean, rstd = torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda")
+    L.layernorm_fwd(x, g, b, y, mean, rstd, 1e-5)
+    dy, dres = torch.randn(rows, h, device="cuda").bfloat16(), torch.randn(rows, h, device="cuda").bfloat16()
+    dx0, dx1 = torch.empty_like(x), torch.empty_like(x)
+    dg0, db0 = torch.zeros(h, device="cuda"), torch.zeros(h, device="cuda")
+    dg1, db1, ds1 = torch.zeros(h, device="cuda"), torch.zeros(h, device="cuda"), torch.ones(h, device="cuda")
+    L.layernorm_bwd(dy, x, g, mean, rstd, dres, dx0, dg0, db0)
+    L.layernorm_bwd_res(dy, x, g, mean, rstd, dres, dx1, dg1, db1, ds1)
+    close(dx1, dx0, 1e-2)
+    close(dg1, dg0, 1e-4)
+    close(db1, db0, 1e-4)
+    close(ds1 - 1, dres.float().sum(0), 1e-3)
+    xf, gf = x.float().requires_grad_(True), g.float().requires_grad_(True)
+    F.layer_norm(xf, (h,), gf, b.float(), 1e-5).backward(dy.float())
+    close(dx1, xf.grad + dres.float())
+    close(dg1, gf.grad)
+    # in place over the residual gradient
+    alias = dres.clone()
+    ds2 = torch.zeros(h, device="cuda")
+    L.layernorm_bwd_res(dy, x, g, mean, rstd, alias, alias, dg1, db1, ds2)
+    close(alias, dx1, 1e-2)
+    close(ds2, dres.float().sum(0), 1e-3)
+    assert L.read_status() == 0
+
+
+@pytest.mark.parametrize("rows,n", [(8192, 4096), (8192, 1024), (100, 264), (513, 1024), (1, 8), (4096, 50304), (33, 3072)])
 def test_colsum(L, rows, n):
     torch.manual_seed(5)
     dy = torch.randn(rows, n, device="cuda").bfloat16()
     out = torch.ones(n, device="cuda")
     L.colsum_accum(dy, out)
     close(out - 1, dy.float().sum(0), 1e-3)
+    # the ticket counters return to zero: repeated calls (also back to back on two streams, each
+    # with its own scratch) give the same bits
+    again = torch.ones(n, device="cuda")
+    L.colsum_accum(dy, again)
+    assert torch.equal(out, again)
+    side = torch.cuda.Stream()
+    a, b = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    torch.cuda.synchronize()
+    for _ in range(3):
+        L.colsum_accum(dy, a)
+        with torch.cuda.stream(side):
+            L.colsum_accum(dy, b, tag="test-side", stream=side.cuda_stream)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)
+    close(a, 3 * dy.float().sum(0), 1e-3)
 
 
 def test_gelu_backward(L):
