@@ -227,7 +227,9 @@ template <> struct ColVec<4> {
 
 // CW: columns per thread (8: 16-byte accesses; 4: 8-byte accesses and half the registers, for
 // hidden sizes up to 1024 where more resident warps matter more than the access width).
-template <int MAXT, int CW, int R, int MINB, bool SUMRES>
+// PF: the operands of the next iteration are requested before the current one is processed
+// (twice the operand registers, memory requests in flight all the time).
+template <int MAXT, int CW, int R, int MINB, bool PF, bool SUMRES>
 __global__ void __launch_bounds__(MAXT, MINB)
 layernorm_bwd_cols_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                           const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
@@ -249,21 +251,29 @@ layernorm_bwd_cols_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloa
   for (int i = 0; i < CW; ++i) { ag[i] = 0.f; ab[i] = 0.f; ar[i] = 0.f; }
   const float inv_h = 1.f / h;
   int buf = 0;
-  for (int base = blockIdx.x * slots * R; base < rows; base += gridDim.x * slots * R) {
-    const int r0 = base + slot * R;
-    VT qd[R], qx[R], qr[R];
-    float mean[R], rstd[R];
+  // operands of R rows starting at `first` (zeros past the last row)
+  auto load_rows = [&](int first, VT* ld, VT* lx, VT* lr, float* lm, float* ls) {
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      const int row = r0 + r;
-      qd[r] = V::zero(); qx[r] = qd[r]; qr[r] = qd[r]; mean[r] = 0.f; rstd[r] = 0.f;
+      const int row = first + r;
+      ld[r] = V::zero(); lx[r] = ld[r]; lr[r] = ld[r]; lm[r] = 0.f; ls[r] = 0.f;
       if (row < rows) {
-        qd[r] = reinterpret_cast<const VT*>(dy + (size_t)row * h)[tc];
-        qx[r] = reinterpret_cast<const VT*>(x + (size_t)row * h)[tc];
-        if (dres) qr[r] = reinterpret_cast<const VT*>(dres + (size_t)row * h)[tc];
-        mean[r] = mean_in[row]; rstd[r] = rstd_in[row];
+        ld[r] = reinterpret_cast<const VT*>(dy + (size_t)row * h)[tc];
+        lx[r] = reinterpret_cast<const VT*>(x + (size_t)row * h)[tc];
+        if (dres) lr[r] = reinterpret_cast<const VT*>(dres + (size_t)row * h)[tc];
+        lm[r] = mean_in[row]; ls[r] = rstd_in[row];
       }
     }
+  };
+  const int step = gridDim.x * slots * R;
+  VT qd[R], qx[R], qr[R];
+  float mean[R], rstd[R];
+  if ((int)blockIdx.x * slots * R < rows) load_rows(blockIdx.x * slots * R + slot * R, qd, qx, qr, mean, rstd);
+  for (int base = blockIdx.x * slots * R; base < rows; base += step) {
+    const int r0 = base + slot * R;
+    VT nd[R], nx[R], nr[R];
+    float nm[R], ns[R];
+    if (PF && base + step < rows) load_rows(r0 + step, nd, nx, nr, nm, ns);
     float s[2 * R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -310,6 +320,14 @@ layernorm_bwd_cols_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloa
       }
       reinterpret_cast<VT*>(dx + (size_t)row * h)[tc] = V::pack(o);
     }
+    if (base + step < rows) {
+      if (PF) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) { qd[r] = nd[r]; qx[r] = nx[r]; qr[r] = nr[r]; mean[r] = nm[r]; rstd[r] = ns[r]; }
+      } else {
+        load_rows(r0 + step, qd, qx, qr, mean, rstd);
+      }
+    }
   }
   // combine the slots' column sums (fixed order) and write this CTA's partial rows
   float* mine = fin + (size_t)slot * NS * h;
@@ -327,28 +345,35 @@ layernorm_bwd_cols_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloa
   }
 }
 
-// out[j] += sum_p partials[p * stride + j].  A 32-column x 8-way block: eight threads share
-// a column, each sums every eighth partial, shared memory combines them in a fixed order
-// (deterministic).
+// out[j] += sum_p partials[p * stride + j].  A 32-column x 32-way block: 32 threads share a
+// column, each sums every 32nd partial (eight loads in flight), shared memory combines them in a
+// fixed order (deterministic).
 // blockIdx.y selects one of up to three (partials, out) pairs, `pair_offset` floats apart in
 // `partials` (LayerNorm: dgamma, dbeta and the residual gradient's column sums in one launch).
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 reduce_partials_kernel(const float* __restrict__ partials, float* __restrict__ out0, float* __restrict__ out1,
                        float* __restrict__ out2, long long pair_offset, int nparts, int n, long long stride) {
-  __shared__ float red[8][33];
+  __shared__ float red[32][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int j = blockIdx.x * 32 + tx;
   float* out = blockIdx.y == 0 ? out0 : (blockIdx.y == 1 ? out1 : out2);
   partials += blockIdx.y * pair_offset;
   float s = 0.f;
-  if (j < n)
-    for (int p = ty; p < nparts; p += 8) s += partials[(size_t)p * stride + j];
+  if (j < n) {
+    for (int p = ty; p < nparts; p += 32 * 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = (p + 32 * u < nparts) ? __ldcg(partials + (size_t)(p + 32 * u) * stride + j) : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) s += v[u];
+    }
+  }
   red[ty][tx] = s;
   __syncthreads();
   if (ty == 0 && j < n) {
     float t = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) t += red[w][tx];
+    for (int w = 0; w < 32; ++w) t += red[w][tx];
     out[j] += t;
   }
 }
@@ -375,24 +400,19 @@ colsum_kernel(const __nv_bfloat16* __restrict__ dy, float* __restrict__ partials
   float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (col0 < n) {
     const __nv_bfloat16* src = dy + col0;
-    int r = r0 + warp;
-    for (; r + 24 < r1; r += 32) {
-      uint4 q[4];
+    // eight rows in flight per warp; rows past the split's end load nothing and add zeros
+    for (int r = r0 + warp; r < r1; r += 64) {
+      uint4 q[8];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) q[u] = *reinterpret_cast<const uint4*>(src + (size_t)(r + 8 * u) * ld);
+      for (int u = 0; u < 8; ++u)
+        q[u] = (r + 8 * u < r1) ? *reinterpret_cast<const uint4*>(src + (size_t)(r + 8 * u) * ld) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 8; ++u) {
         float f[8];
         unpack8(q[u], f);
 #pragma unroll
         for (int i = 0; i < 8; ++i) s[i] += f[i];
       }
-    }
-    for (; r < r1; r += 8) {
-      float f[8];
-      unpack8(*reinterpret_cast<const uint4*>(src + (size_t)r * ld), f);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) s[i] += f[i];
     }
   }
 #pragma unroll
@@ -415,15 +435,13 @@ colsum_kernel(const __nv_bfloat16* __restrict__ dy, float* __restrict__ partials
   __threadfence();
   if (col < n) {
     float acc = 0.f;
-    int p = 0;
-    for (; p + 8 <= splits; p += 8) {
-      float v[8];
+    for (int p = 0; p < splits; p += 16) {
+      float v[16];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = __ldcg(partials + (size_t)(p + u) * n + col);
+      for (int u = 0; u < 16; ++u) v[u] = (p + u < splits) ? __ldcg(partials + (size_t)(p + u) * n + col) : 0.f;
 #pragma unroll
-      for (int u = 0; u < 8; ++u) acc += v[u];
+      for (int u = 0; u < 16; ++u) acc += v[u];
     }
-    for (; p < splits; ++p) acc += __ldcg(partials + (size_t)p * n + col);
     out[col] += acc;
   }
   if (threadIdx.x == 0) tickets[blockIdx.x] = 0u;
@@ -525,23 +543,23 @@ bool ln_bwd_cols_ok(int h) {
 // Shape of the column-owner kernel for a hidden size: columns per thread, rows per slot per
 // iteration, resident CTAs per SM (what the register count of that instantiation allows) and
 // the CTA size bound.  Every instantiation below compiles without register spills.
-struct LnColsCfg { int cw, r, ctas, maxt; };
+struct LnColsCfg { int cw, r, ctas, maxt, pf; };
 LnColsCfg ln_cols_cfg(int h) {
   if (h <= 1024) {
-    // BB_LN_BWD_VARIANT=0..4 in the environment picks another instantiation (A/B measurements)
+    // BB_LN_BWD_VARIANT=1|2 in the environment picks another instantiation (A/B measurements):
+    // measured on 8192 x 1024, both launches, less the fixed cost of two launches:
+    // 0: 16.2 us, 1: 21.1 us, 2: 14.8 us (but 20.2 us with the residual sums: it spills there)
     static int v = -1;
-    if (v < 0) { const char* e = getenv("BB_LN_BWD_VARIANT"); v = (e && e[0] >= '0' && e[0] <= '4') ? e[0] - '0' : 0; }
+    if (v < 0) { const char* e = getenv("BB_LN_BWD_VARIANT"); v = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 0; }
     switch (v) {
-      case 1: return {4, 2, 4, 256};
-      case 2: return {4, 8, 2, 256};
-      case 3: return {8, 3, 2, 256};
-      case 4: return {8, 2, 3, 256};
-      default: return {4, 4, 3, 256};
+      case 1: return {4, 4, 3, 256, 0};
+      case 2: return {8, 1, 3, 256, 1};
+      default: return {8, 3, 2, 256, 0};
     }
   }
-  if (h <= 2048) return {8, 2, 3, 256};
-  if (h <= 4096) return {8, 4, 1, 512};
-  return {8, 1, 1, 1024};
+  if (h <= 2048) return {8, 2, 3, 256, 0};
+  if (h <= 4096) return {8, 4, 1, 512, 0};
+  return {8, 1, 1, 1024, 0};
 }
 int ln_bwd_cols_slots(int h) { const int tpr = h / ln_cols_cfg(h).cw; return tpr >= 256 ? 1 : 256 / tpr; }
 int ln_bwd_grid(int rows, int h) {
@@ -559,19 +577,19 @@ int ln_bwd_grid(int rows, int h) {
 }  // namespace
 
 namespace {
-template <int MAXT, int CW, int R, int MINB>
+template <int MAXT, int CW, int R, int MINB, bool PF>
 int ln_bwd_cols_launch(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, const void* dres,
                        void* dx, float* ws, bool sum_res, int rows, int h, int grid, cudaStream_t s) {
   const int slots = ln_bwd_cols_slots(h), tpr = h / CW, threads = slots * tpr;
   const size_t sm_bytes = ((size_t)2 * slots * (tpr / 32) * 2 * R + (size_t)slots * (sum_res ? 3 : 2) * h) * sizeof(float);
   BB_ONCE_PER_DEVICE({
-    BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_cols_kernel<MAXT, CW, R, MINB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
-    BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_cols_kernel<MAXT, CW, R, MINB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+    BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_cols_kernel<MAXT, CW, R, MINB, PF, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+    BB_CUDA_CHECK(cudaFuncSetAttribute(layernorm_bwd_cols_kernel<MAXT, CW, R, MINB, PF, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
   });
 #define BB_LNC_ARGS (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, mean, rstd, \
                     (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, ws, rows, h, slots
-  if (sum_res) layernorm_bwd_cols_kernel<MAXT, CW, R, MINB, true><<<grid, threads, sm_bytes, s>>>(BB_LNC_ARGS);
-  else layernorm_bwd_cols_kernel<MAXT, CW, R, MINB, false><<<grid, threads, sm_bytes, s>>>(BB_LNC_ARGS);
+  if (sum_res) layernorm_bwd_cols_kernel<MAXT, CW, R, MINB, PF, true><<<grid, threads, sm_bytes, s>>>(BB_LNC_ARGS);
+  else layernorm_bwd_cols_kernel<MAXT, CW, R, MINB, PF, false><<<grid, threads, sm_bytes, s>>>(BB_LNC_ARGS);
 #undef BB_LNC_ARGS
   BB_CUDA_CHECK(cudaGetLastError());
   return BB_OK;
@@ -584,11 +602,11 @@ int ln_bwd_main(const void* dy, const void* x, const void* gamma, const float* m
                 void* dx, float* ws, bool sum_res, int rows, int h, int grid, int warps, cudaStream_t s) {
   if (ln_bwd_cols_ok(h)) {
     const LnColsCfg c = ln_cols_cfg(h);
-#define BB_LNC_CASE(MAXT, CW, R, MINB) \
-    if (c.maxt == MAXT && c.cw == CW && c.r == R && c.ctas == MINB) \
-      return ln_bwd_cols_launch<MAXT, CW, R, MINB>(dy, x, gamma, mean, rstd, dres, dx, ws, sum_res, rows, h, grid, s);
-    BB_LNC_CASE(256, 4, 4, 3) BB_LNC_CASE(256, 4, 2, 4) BB_LNC_CASE(256, 4, 8, 2) BB_LNC_CASE(256, 8, 3, 2)
-    BB_LNC_CASE(256, 8, 2, 3) BB_LNC_CASE(512, 8, 4, 1) BB_LNC_CASE(1024, 8, 1, 1)
+#define BB_LNC_CASE(MAXT, CW, R, MINB, PF) \
+    if (c.maxt == MAXT && c.cw == CW && c.r == R && c.ctas == MINB && c.pf == PF) \
+      return ln_bwd_cols_launch<MAXT, CW, R, MINB, PF != 0>(dy, x, gamma, mean, rstd, dres, dx, ws, sum_res, rows, h, grid, s);
+    BB_LNC_CASE(256, 8, 3, 2, 0) BB_LNC_CASE(256, 4, 4, 3, 0) BB_LNC_CASE(256, 8, 1, 3, 1)
+    BB_LNC_CASE(256, 8, 2, 3, 0) BB_LNC_CASE(512, 8, 4, 1, 0) BB_LNC_CASE(1024, 8, 1, 1, 0)
 #undef BB_LNC_CASE
     bb_set_last_error_msg("layernorm backward: no column-owner instantiation for this shape");
     return BB_ERR_INVALID_ARG;
@@ -648,7 +666,7 @@ extern "C" int bb_layernorm_bwd(const void* dy, const void* x, const void* gamma
   const int grid = ln_bwd_grid(rows, h);
   float* ws = (float*)workspace;
   if (int rc = ln_bwd_main(dy, x, gamma, mean, rstd, dres, dx, ws, false, rows, h, grid, ln_bwd_warps(h), s)) return rc;
-  reduce_partials_kernel<<<dim3((h + 31) / 32, 2), 256, 0, s>>>(ws, dgamma, dbeta, nullptr, (long long)h, grid, h, 2LL * h);
+  reduce_partials_kernel<<<dim3((h + 31) / 32, 2), 1024, 0, s>>>(ws, dgamma, dbeta, nullptr, (long long)h, grid, h, 2LL * h);
   BB_CUDA_CHECK(cudaGetLastError());
   return BB_OK;
 }
@@ -706,19 +724,20 @@ extern "C" int bb_layernorm_bwd_static(const void* dy, const void* x, const void
   // every partial row that the reduction reads is rewritten by this launch, so the scratch
   // needs no clearing although it still holds the previous call's sums
   if (int rc = ln_bwd_main(dy, x, gamma, mean, rstd, dres, dx, ws, false, rows, h, grid, warps, s)) return rc;
-  reduce_partials_kernel<<<dim3((h + 31) / 32, 2), 256, 0, s>>>(ws, dgamma, dbeta, nullptr, (long long)h, grid, h, 2LL * h);
+  reduce_partials_kernel<<<dim3((h + 31) / 32, 2), 1024, 0, s>>>(ws, dgamma, dbeta, nullptr, (long long)h, grid, h, 2LL * h);
   BB_CUDA_CHECK(cudaGetLastError());
   return BB_OK;
 }
 
 namespace {
-// enough splits for about four CTAs per SM, at least 32 rows each
+// enough splits for about four CTAs per SM, at least 64 rows each (eight per warp: one batch of
+// loads), at most 64 (the last CTA of a column block adds the partial rows)
 int colsum_splits(int rows, int n) {
   const int col_blocks = (n + 255) / 256;
   int s = (4 * bb_num_sms() + col_blocks - 1) / col_blocks;
-  const int by_rows = (rows + 31) / 32;
+  const int by_rows = (rows + 63) / 64;
   if (s > by_rows) s = by_rows;
-  return s < 1 ? 1 : (s > 256 ? 256 : s);
+  return s < 1 ? 1 : (s > 64 ? 64 : s);
 }
 
 // ticket counters of one launch: `col_blocks` consecutive entries of the device table, handed out
@@ -808,7 +827,7 @@ extern "C" int bb_layernorm_bwd_res(const void* dy, const void* x, const void* g
   }
   const int grid = ln_bwd_grid(rows, h);
   if (int rc = ln_bwd_main(dy, x, gamma, mean, rstd, dres, dx, ws, true, rows, h, grid, ln_bwd_warps(h), s)) return rc;
-  reduce_partials_kernel<<<dim3((h + 31) / 32, 3), 256, 0, s>>>(ws, dgamma, dbeta, dres_sum, (long long)h, grid, h, 3LL * h);
+  reduce_partials_kernel<<<dim3((h + 31) / 32, 3), 1024, 0, s>>>(ws, dgamma, dbeta, dres_sum, (long long)h, grid, h, 3LL * h);
   BB_CUDA_CHECK(cudaGetLastError());
   return BB_OK;
 }
