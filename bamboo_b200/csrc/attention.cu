@@ -472,8 +472,8 @@ bool bad_layout(long long stride, int D, const void* a, const void* b, const voi
 int bb_attention_tc_fwd(const void* qkv_q, void* out, float* lse, int B, int H, int S, long long stride_qkv, long long stride_o,
                         int causal, float scale, cudaStream_t stream);
 int bb_attention_tc_bwd(const void* qkv_q, const void* out, const void* d_out, const float* lse, void* dq, void* dk, void* dv,
-                        float* delta, int B, int H, int S, long long stride_qkv, long long stride_o, long long stride_dqkv,
-                        int causal, float scale, cudaStream_t stream);
+                        float* delta, float* dq_acc, int B, int H, int S, long long stride_qkv, long long stride_o,
+                        long long stride_dqkv, int causal, float scale, cudaStream_t stream);
 
 namespace {
 // The tcgen05 kernels (attention_tc.cu) read q, k, v through one tensor map over the packed
@@ -514,9 +514,16 @@ extern "C" int bb_attention_fwd(const void* q, const void* k, const void* v, voi
   return BB_ERR_UNSUPPORTED;
 }
 
+namespace {
+// workspace: delta [B, H, S] fp32, then (256-byte aligned) the fp32 dQ accumulator [B, H, S, 64] of
+// the fused tcgen05 backward (head dimension 64; the size does not depend on the head dimension
+// because this query has none)
+long long attn_ws_delta_bytes(int B, int H, int S) { return (((long long)B * H * S * (long long)sizeof(float)) + 255) & ~255LL; }
+}  // namespace
+
 extern "C" long long bb_attention_bwd_workspace_bytes(int B, int H, int S) {
   if (B <= 0 || H <= 0 || S <= 0) return 0;
-  return (long long)B * H * S * (long long)sizeof(float);
+  return attn_ws_delta_bytes(B, H, S) + (long long)B * H * S * 64 * (long long)sizeof(float);
 }
 
 extern "C" int bb_attention_bwd(const void* q, const void* k, const void* v, const void* out, const void* d_out, const float* lse,
@@ -540,8 +547,9 @@ extern "C" int bb_attention_bwd(const void* q, const void* k, const void* v, con
   p.stride_qkv = stride_qkv; p.stride_o = stride_o; p.stride_dqkv = stride_dqkv;
   p.B = B; p.H = H; p.S = S; p.causal = causal; p.scale = scale;
   if (use_tc_path(q, k, v, H, D, stride_qkv))
-    return bb_attention_tc_bwd(q, out, d_out, lse, dq, dk, dv, (float*)workspace, B, H, S, stride_qkv, stride_o, stride_dqkv,
-                               causal, scale, (cudaStream_t)stream);
+    return bb_attention_tc_bwd(q, out, d_out, lse, dq, dk, dv, (float*)workspace,
+                               (float*)((char*)workspace + attn_ws_delta_bytes(B, H, S)), B, H, S, stride_qkv, stride_o,
+                               stride_dqkv, causal, scale, (cudaStream_t)stream);
   if (D == 64) return launch_bwd<64>(p, (cudaStream_t)stream);
   if (D == 128) return launch_bwd<128>(p, (cudaStream_t)stream);
   bb_set_last_error_msg("bb_attention_bwd: head dimension must be 64 or 128");

@@ -15,6 +15,7 @@
 // the backward split keeps every sum in a fixed order (no atomics).
 #include "tma_host.cuh"
 #include <math.h>
+#include <stdlib.h>
 
 namespace {
 
@@ -28,6 +29,7 @@ struct TcParams {
   __nv_bfloat16 *out, *dq, *dk, *dv;
   float* lse;                   // [B, H, S]
   float* delta;                 // [B, H, S]
+  float* dq_acc;                // [B, H, S, 64] fp32 sums of dQ (fused backward), or null
   long long stride_o, stride_dqkv;
   int B, H, S;
   int hidden;                   // H * 64: column offset between q, k and v in the packed projection
@@ -116,12 +118,18 @@ struct Ctl {
 
 // delta[b, h, s] = sum_d dO * O.  Eight lanes per (token, head): each loads 16 bytes of O and dO
 // (a warp reads four consecutive heads of a token: 512 contiguous bytes per operand), two
-// independent units per thread for memory-level parallelism.
+// independent units per thread for memory-level parallelism.  The same pass clears the fp32
+// accumulator of the fused backward kernel, when there is one.
 __global__ void __launch_bounds__(256)
 attn_tc_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, const TcParams p) {
   const int per_tok = p.H * 8;                                 // 16-byte chunks per token row
   const long long total = (long long)p.B * p.S * per_tok;
   const long long stride = (long long)gridDim.x * blockDim.x;
+  if (p.dq_acc) {
+    float4* z = reinterpret_cast<float4*>(p.dq_acc);
+    const long long n4 = (long long)p.B * p.H * p.S * (HD / 4);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   // the trip count is uniform within a warp (the shuffles below need every lane)
   for (long long w = (long long)blockIdx.x * blockDim.x + (threadIdx.x & ~31); w < total; w += 2 * stride) {
     const long long c = w + (threadIdx.x & 31);
@@ -229,7 +237,7 @@ attn_tc_dq2_body(const CUtensorMap& tm_q, const CUtensorMap& tm_kv, const CUtens
       bb::tma_load_2d(sDO, &tm_do, q_full, colq, row_base + q0);
       for (int j = 0; j < nblk; ++j) {
         const int s = j % NST;
-        if (!bb::mbar_wait_spin(&kv_empty[s], ((j / NST) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        if (!bb::mbar_wait(&kv_empty[s], ((j / NST) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
         bb::mbar_arrive_expect_tx(&kv_full[s], 2 * SUB_BYTES);
         bb::tma_load_2d(sK + s * SUB_BYTES, &tm_kv, &kv_full[s], colk, row_base + j * SUB);
         bb::tma_load_2d(sV + s * SUB_BYTES, &tm_kv, &kv_full[s], colv, row_base + j * SUB);
@@ -240,13 +248,13 @@ attn_tc_dq2_body(const CUtensorMap& tm_q, const CUtensorMap& tm_kv, const CUtens
     const uint64_t dK0 = desc_k0(bb::smem_u32(sK)), dV0 = desc_k0(bb::smem_u32(sV));     // stage 0; stage s: + s * SUB_BYTES / 16
     const uint64_t dKm0 = desc_mn0(bb::smem_u32(sK)), dDS0 = desc_k0(bb::smem_u32(sDS));
     const uint32_t i_s = idesc(64, 0, 0), i_dq = idesc(64, 0, 1);
-    bool alive = bb::mbar_wait_spin(q_full, 0, &ctl->abort_flag, p.status);
+    bool alive = bb::mbar_wait(q_full, 0, &ctl->abort_flag, p.status);
     // software pipeline: the scores run two sub-blocks ahead of the dQ updates
     for (int j = 0; j < nblk + 2 && alive; ++j) {
       if (j < nblk) {
         const int s = j % NST, b = j % NSB;
-        if (!bb::mbar_wait_spin(&kv_full[s], (j / NST) & 1, &ctl->abort_flag, p.status)) break;
-        if (!bb::mbar_wait_spin(&s_empty[b], ((j / NSB) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        if (!bb::mbar_wait(&kv_full[s], (j / NST) & 1, &ctl->abort_flag, p.status)) break;
+        if (!bb::mbar_wait(&s_empty[b], ((j / NSB) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
         bb::tc_fence_after_sync();
         if (lane == 0) {
           const uint64_t dK = dK0 + (uint64_t)(s * (SUB_BYTES >> 4)), dV = dV0 + (uint64_t)(s * (SUB_BYTES >> 4));
@@ -261,7 +269,7 @@ attn_tc_dq2_body(const CUtensorMap& tm_q, const CUtensorMap& tm_kv, const CUtens
       }
       if (j >= 2) {
         const int jj = j - 2, s2 = jj % NST, b2 = jj & 1;
-        if (!bb::mbar_wait_spin(&ds_full[b2], (jj >> 1) & 1, &ctl->abort_flag, p.status)) break;
+        if (!bb::mbar_wait(&ds_full[b2], (jj >> 1) & 1, &ctl->abort_flag, p.status)) break;
         bb::tc_fence_after_sync();
         if (lane == 0) {
           const uint64_t dK2 = dKm0 + (uint64_t)(s2 * (SUB_BYTES >> 4)), dDS = dDS0 + (uint64_t)(b2 * (TILE_BYTES >> 4));
@@ -292,7 +300,7 @@ attn_tc_dq2_body(const CUtensorMap& tm_q, const CUtensorMap& tm_kv, const CUtens
     for (int j = g; j < nblk && alive; j += 2, ++n) {
       const int sb = j % NSB;
       const uint32_t tS = tmem + 64 * sb, tDP = tmem + 192 + 64 * sb;
-      const bool ok = bb::mbar_wait_spin(&s_full[sb], (j / NSB) & 1, &ctl->abort_flag, p.status);
+      const bool ok = bb::mbar_wait(&s_full[sb], (j / NSB) & 1, &ctl->abort_flag, p.status);
       if (!bb::named_bar_all(3 + g, GROUP_THREADS, ok)) { alive = false; break; }
       bb::tc_fence_after_sync();
       const int c0 = j * SUB + hf * 32;
@@ -321,14 +329,14 @@ attn_tc_dq2_body(const CUtensorMap& tm_q, const CUtensorMap& tm_kv, const CUtens
       __syncwarp();
       if (lane == 0) bb::mbar_arrive(&s_empty[sb]);          // scores consumed: the MMA warp may refill
       // the staging buffer is free once the dQ update that read it two sub-blocks ago retired
-      const bool ok2 = bb::mbar_wait_spin(&ds_empty[g], (n & 1) ^ 1, &ctl->abort_flag, p.status);
+      const bool ok2 = bb::mbar_wait(&ds_empty[g], (n & 1) ^ 1, &ctl->abort_flag, p.status);
       if (!bb::named_bar_all(3 + g, GROUP_THREADS, ok2)) { alive = false; break; }
       atom_store_half_row(myDS, row, hf, pk);
       bb::fence_proxy_async();
       __syncwarp();
       if (lane == 0) bb::mbar_arrive(&ds_full[g]);
     }
-    const bool fin = alive && bb::mbar_wait_spin(acc_full, 0, &ctl->abort_flag, p.status);
+    const bool fin = alive && bb::mbar_wait(acc_full, 0, &ctl->abort_flag, p.status);
     if (bb::named_bar_all(3 + g, GROUP_THREADS, fin) && g == 0) {
       bb::tc_fence_after_sync();
       float v[32];
@@ -402,7 +410,7 @@ attn_tc_dkv2_body(const CUtensorMap& tm128, const CUtensorMap& tm64, const CUten
       bb::tma_load_2d(sV, &tm128, kv_full, colv, row_base + k0);
       for (int i = 0; i < nblk; ++i) {
         const int s = i % NST;
-        if (!bb::mbar_wait_spin(&q_empty[s], ((i / NST) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        if (!bb::mbar_wait(&q_empty[s], ((i / NST) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
         bb::mbar_arrive_expect_tx(&q_full[s], 2 * SUB_BYTES);
         bb::tma_load_2d(sQ + s * SUB_BYTES, &tm64, &q_full[s], colq, row_base + (qstart + i) * SUB);
         bb::tma_load_2d(sDO + s * SUB_BYTES, &tm_do64, &q_full[s], colq, row_base + (qstart + i) * SUB);
@@ -414,13 +422,13 @@ attn_tc_dkv2_body(const CUtensorMap& tm128, const CUtensorMap& tm64, const CUten
     const uint64_t dQm0 = desc_mn0(bb::smem_u32(sQ)), dDOm0 = desc_mn0(bb::smem_u32(sDO));
     const uint64_t dP0 = desc_k0(bb::smem_u32(sP)), dDS0 = desc_k0(bb::smem_u32(sDS));
     const uint32_t i_s = idesc(64, 0, 0), i_acc = idesc(64, 0, 1);
-    bool alive = bb::mbar_wait_spin(kv_full, 0, &ctl->abort_flag, p.status);
+    bool alive = bb::mbar_wait(kv_full, 0, &ctl->abort_flag, p.status);
     // the score products run two sub-blocks ahead of the dV / dK updates
     for (int i = 0; i < nblk + 2 && alive; ++i) {
       if (i < nblk) {
         const int s = i % NST, b = i % NSB;
-        if (!bb::mbar_wait_spin(&q_full[s], (i / NST) & 1, &ctl->abort_flag, p.status)) break;
-        if (!bb::mbar_wait_spin(&s_empty[b], ((i / NSB) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        if (!bb::mbar_wait(&q_full[s], (i / NST) & 1, &ctl->abort_flag, p.status)) break;
+        if (!bb::mbar_wait(&s_empty[b], ((i / NSB) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
         bb::tc_fence_after_sync();
         if (lane == 0) {
           const uint64_t dQ = dQ0 + (uint64_t)(s * (SUB_BYTES >> 4)), dDO = dDO0 + (uint64_t)(s * (SUB_BYTES >> 4));
@@ -435,7 +443,7 @@ attn_tc_dkv2_body(const CUtensorMap& tm128, const CUtensorMap& tm64, const CUten
       }
       if (i >= 2) {
         const int ii = i - 2, s2 = ii % NST, b2 = ii & 1;
-        if (!bb::mbar_wait_spin(&p_full[b2], (ii >> 1) & 1, &ctl->abort_flag, p.status)) break;
+        if (!bb::mbar_wait(&p_full[b2], (ii >> 1) & 1, &ctl->abort_flag, p.status)) break;
         bb::tc_fence_after_sync();
         if (lane == 0) {
           const uint64_t dQ2 = dQm0 + (uint64_t)(s2 * (SUB_BYTES >> 4)), dDO2 = dDOm0 + (uint64_t)(s2 * (SUB_BYTES >> 4));
@@ -488,7 +496,7 @@ attn_tc_dkv2_body(const CUtensorMap& tm128, const CUtensorMap& tm64, const CUten
       }
       const int sb = i % NSB;
       const uint32_t tS = tmem + 64 * sb, tDP = tmem + 192 + 64 * sb;
-      const bool ok = bb::mbar_wait_spin(&s_full[sb], (i / NSB) & 1, &ctl->abort_flag, p.status);
+      const bool ok = bb::mbar_wait(&s_full[sb], (i / NSB) & 1, &ctl->abort_flag, p.status);
       if (!bb::named_bar_all(3 + g, GROUP_THREADS, ok)) { alive = false; break; }
       bb::tc_fence_after_sync();
       const bool need_mask = (qc0 + SUB > p.S) || (p.causal && k0 + TQ - 1 > qc0);
@@ -520,7 +528,7 @@ attn_tc_dkv2_body(const CUtensorMap& tm128, const CUtensorMap& tm64, const CUten
       __syncwarp();
       if (lane == 0) bb::mbar_arrive(&s_empty[sb]);
       // the staging buffers are free once the dV / dK update that read them retired
-      const bool ok2 = bb::mbar_wait_spin(&p_empty[g], (n & 1) ^ 1, &ctl->abort_flag, p.status);
+      const bool ok2 = bb::mbar_wait(&p_empty[g], (n & 1) ^ 1, &ctl->abort_flag, p.status);
       if (!bb::named_bar_all(3 + g, GROUP_THREADS, ok2)) { alive = false; break; }
       atom_store_half_row(myP, row, hf, pkP);
       atom_store_half_row(myDS, row, hf, pkDS);
@@ -528,7 +536,7 @@ attn_tc_dkv2_body(const CUtensorMap& tm128, const CUtensorMap& tm64, const CUten
       __syncwarp();
       if (lane == 0) bb::mbar_arrive(&p_full[g]);
     }
-    const bool fin = alive && nblk > 0 && bb::mbar_wait_spin(acc_full, 0, &ctl->abort_flag, p.status);
+    const bool fin = alive && nblk > 0 && bb::mbar_wait(acc_full, 0, &ctl->abort_flag, p.status);
     if (bb::named_bar_all(3 + g, GROUP_THREADS, fin)) {
       bb::tc_fence_after_sync();
       float v[32];
@@ -556,6 +564,301 @@ attn_tc_bwd2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
   const int nbx = gridDim.x >> 1;
   if ((int)blockIdx.x < nbx) attn_tc_dkv2_body(tm128, tm64, tm_do64, p, blockIdx.x);
   else attn_tc_dq2_body(tm128, tm64, tm_do128, p, blockIdx.x - nbx, nbx);
+}
+
+// ------------------------------------------------------------------ fused backward: dK, dV and dQ from one pass
+// A CTA owns 128 key rows and streams the 64-row query / dO sub-tiles like the dK/dV role above,
+// but S^T and dP^T are computed once: the staged dS^T tiles of two consecutive sub-blocks
+// ([128 keys x 64 queries] each, adjacent in shared memory) also serve, read with the queries as
+// the M dimension, as the A operand of dQ[128 queries x 64] = dS . K for that pair of sub-blocks.
+// The pair's dQ leaves tensor memory as fp32 vector reductions into a [B, H, S, 64] accumulator
+// (each query row receives one contribution per key tile; their order is not fixed), which a small
+// kernel scales and converts once all CTAs are done.  Five contractions instead of seven, one
+// exponential pass instead of two, half the CTAs.
+// smem: K, V [128 x 64] | Q, dO sub-tiles x NST3 | P^T x 2 | dS^T x 2 pair slots x 2 groups | lse / delta
+// TMEM: S^T 2 x 64 | dP^T 2 x 64 | dV 64 | dK 64 | dQ 2 x 64
+constexpr int NST3 = 5;
+__device__ __forceinline__ void red_add_f32x4(float* dst, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" :: "l"(dst), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__global__ void __launch_bounds__(NT2, 1)
+attn_tc_bwd3_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_constant__ CUtensorMap tm64,
+                    const __grid_constant__ CUtensorMap tm_do64, const TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TILE_BYTES;
+  uint8_t* sQ = sV + TILE_BYTES;               // NST3 stages x 8 KiB
+  uint8_t* sDO = sQ + NST3 * SUB_BYTES;        // NST3 stages x 8 KiB
+  uint8_t* sP = sDO + NST3 * SUB_BYTES;        // [group] x 16 KiB
+  uint8_t* sDS = sP + 2 * TILE_BYTES;          // [pair slot][group] x 16 KiB
+  float* s_lse = reinterpret_cast<float*>(sDS + 4 * TILE_BYTES);   // [2][64]
+  float* s_delta = s_lse + 2 * SUB;                                // [2][64]
+  Ctl* ctl = reinterpret_cast<Ctl*>(s_delta + 2 * SUB);
+  uint64_t* kv_full = &ctl->bars[0];
+  uint64_t* q_full = &ctl->bars[1];            // [NST3]
+  uint64_t* q_empty = q_full + NST3;           // [NST3]
+  uint64_t* s_full = q_empty + NST3;           // [2]
+  uint64_t* s_empty = s_full + 2;              // [2]
+  uint64_t* p_full = s_empty + 2;              // [2]  P^T and dS^T of a sub-block staged
+  uint64_t* p_empty = p_full + 2;              // [2]  P^T buffer of a group read by its dV update
+  uint64_t* ds_empty = p_empty + 2;            // [2]  both dS^T buffers of a pair slot read by dK and dQ
+  uint64_t* dq_full = ds_empty + 2;            // [2]  a pair's dQ complete in tensor memory
+  uint64_t* dq_empty = dq_full + 2;            // [2]  ... and drained
+  uint64_t* acc_full = dq_empty + 2;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+  const int k0 = kb * TQ;
+  const int row_base = batch * p.S;
+  const int colq = head * HD, colk = p.hidden + head * HD, colv = 2 * p.hidden + head * HD;
+  const int nq = (p.S + SUB - 1) / SUB;
+  const int qstart = p.causal ? (k0 / SUB) : 0;
+  // an even number of sub-blocks (they pair up for dQ); a padding sub-block lies past the
+  // sequence end and is masked to zero
+  const int nblk = (nq - qstart + 1) & ~1;
+  const int npairs = nblk >> 1;
+
+  if (threadIdx.x == 0) {
+    ctl->abort_flag = 0;
+    bb::mbar_init(kv_full, 1);
+    for (int i = 0; i < NST3; ++i) { bb::mbar_init(&q_full[i], 1); bb::mbar_init(&q_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) {
+      bb::mbar_init(&s_full[i], 1); bb::mbar_init(&s_empty[i], GROUP_THREADS / 32);
+      bb::mbar_init(&p_full[i], GROUP_THREADS / 32); bb::mbar_init(&p_empty[i], 1);
+      bb::mbar_init(&ds_empty[i], 1);
+      bb::mbar_init(&dq_full[i], 1); bb::mbar_init(&dq_empty[i], GROUP_THREADS / 32);
+    }
+    bb::mbar_init(acc_full, 1);
+    bb::fence_barrier_init();
+    bb::tma_prefetch_desc(&tm128); bb::tma_prefetch_desc(&tm64); bb::tma_prefetch_desc(&tm_do64);
+  }
+  if (warp == 1) { bb::tmem_alloc(&ctl->tmem_slot, 512); bb::tmem_relinquish(); }
+  bb::tc_fence_before_sync();
+  __syncthreads();
+  bb::tc_fence_after_sync();
+  const uint32_t tmem = ctl->tmem_slot;
+  // S^T[b] at tmem + 64 b, dP^T[b] at tmem + 128 + 64 b (b < 2)
+  const uint32_t tDV = tmem + 256, tDK = tmem + 320, tDQ = tmem + 384;    // dQ[b] at tDQ + 64 b
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bb::mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
+      bb::tma_load_2d(sK, &tm128, kv_full, colk, row_base + k0);
+      bb::tma_load_2d(sV, &tm128, kv_full, colv, row_base + k0);
+      for (int i = 0; i < nblk; ++i) {
+        const int s = i % NST3;
+        if (!bb::mbar_wait(&q_empty[s], ((i / NST3) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        bb::mbar_arrive_expect_tx(&q_full[s], 2 * SUB_BYTES);
+        bb::tma_load_2d(sQ + s * SUB_BYTES, &tm64, &q_full[s], colq, row_base + (qstart + i) * SUB);
+        bb::tma_load_2d(sDO + s * SUB_BYTES, &tm_do64, &q_full[s], colq, row_base + (qstart + i) * SUB);
+      }
+    }
+  } else if (warp == 1) {
+    const uint64_t dK0 = desc_k0(bb::smem_u32(sK)), dV0 = desc_k0(bb::smem_u32(sV));
+    const uint64_t dQ0 = desc_k0(bb::smem_u32(sQ)), dDO0 = desc_k0(bb::smem_u32(sDO));   // stage 0; stage s: + s * SUB_BYTES / 16
+    const uint64_t dQm0 = desc_mn0(bb::smem_u32(sQ)), dDOm0 = desc_mn0(bb::smem_u32(sDO));
+    const uint64_t dP0 = desc_k0(bb::smem_u32(sP)), dDS0 = desc_k0(bb::smem_u32(sDS));
+    // dS^T of a pair slot read with the queries as M: two 64-query blocks one tile apart, 8-key groups 1 KiB apart
+    const uint64_t dDSm0 = bb::make_smem_desc_sw128(bb::smem_u32(sDS), TILE_BYTES, 1024);
+    const uint64_t dKm0 = desc_mn0(bb::smem_u32(sK));
+    const uint32_t i_s = idesc(64, 0, 0), i_acc = idesc(64, 0, 1), i_dq = idesc(64, 1, 1);
+    bool alive = bb::mbar_wait(kv_full, 0, &ctl->abort_flag, p.status);
+    // the score products run two sub-blocks ahead of the dV / dK updates
+    for (int i = 0; i < nblk + 2 && alive; ++i) {
+      if (i < nblk) {
+        const int s = i % NST3, b = i & 1;
+        if (!bb::mbar_wait(&q_full[s], (i / NST3) & 1, &ctl->abort_flag, p.status)) break;
+        if (!bb::mbar_wait(&s_empty[b], ((i >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        bb::tc_fence_after_sync();
+        if (lane == 0) {
+          const uint64_t dQ = dQ0 + (uint64_t)(s * (SUB_BYTES >> 4)), dDO = dDO0 + (uint64_t)(s * (SUB_BYTES >> 4));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            bb::umma_f16(tmem + 64 * b, desc_kmajor(dK0, k), desc_kmajor(dQ, k), i_s, k > 0);
+            bb::umma_f16(tmem + 128 + 64 * b, desc_kmajor(dV0, k), desc_kmajor(dDO, k), i_s, k > 0);
+          }
+          bb::umma_commit(&s_full[b]);
+        }
+        __syncwarp();
+      }
+      if (i >= 2) {
+        const int ii = i - 2, s2 = ii % NST3, g2 = ii & 1, pair = ii >> 1, ps = pair & 1;
+        if (!bb::mbar_wait(&p_full[g2], pair & 1, &ctl->abort_flag, p.status)) break;
+        bb::tc_fence_after_sync();
+        if (lane == 0) {
+          const uint64_t dQ2 = dQm0 + (uint64_t)(s2 * (SUB_BYTES >> 4)), dDO2 = dDOm0 + (uint64_t)(s2 * (SUB_BYTES >> 4));
+          const uint64_t dP = dP0 + (uint64_t)(g2 * (TILE_BYTES >> 4));
+          const uint64_t dDS = dDS0 + (uint64_t)((ps * 2 + g2) * (TILE_BYTES >> 4));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            bb::umma_f16(tDV, desc_kmajor(dP, k), desc_mnmajor64(dDO2, k), i_acc, (ii > 0 || k > 0));
+            bb::umma_f16(tDK, desc_kmajor(dDS, k), desc_mnmajor64(dQ2, k), i_acc, (ii > 0 || k > 0));
+          }
+          bb::umma_commit(&p_empty[g2]);
+          bb::umma_commit(&q_empty[s2]);
+        }
+        __syncwarp();
+        if (g2 == 1) {
+          // both halves of the pair are staged: dQ[pair] = dS . K over the tile's 128 keys
+          if (!bb::mbar_wait(&dq_empty[pair & 1], ((pair >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+          bb::tc_fence_after_sync();
+          if (lane == 0) {
+            const uint64_t dA = dDSm0 + (uint64_t)(ps * 2 * (TILE_BYTES >> 4));
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              bb::umma_f16(tDQ + 64 * (pair & 1), desc_mnmajor64(dA, k), desc_mnmajor64(dKm0, k), i_dq, k > 0);
+            bb::umma_commit(&ds_empty[ps]);
+            bb::umma_commit(&dq_full[pair & 1]);
+            if (ii == nblk - 1) bb::umma_commit(acc_full);
+          }
+          __syncwarp();
+        }
+      }
+    }
+  } else {
+    const int g = (warp - 2) >> 3;
+    const int hf = ((warp - 2) >> 2) & 1;                  // which 32 of the sub-block's 64 query columns
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;                   // key row inside the tile / query row inside a pair
+    const int gt = threadIdx.x - 64 - GROUP_THREADS * g;   // thread index inside the group
+    const int krow = k0 + row;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const float* lse_g = p.lse + ((long long)batch * p.H + head) * p.S;
+    const float* delta_g = p.delta + ((long long)batch * p.H + head) * p.S;
+    float* acc_g = p.dq_acc + ((long long)batch * p.H + head) * p.S * HD;
+    const float sl = p.scale * LOG2E;
+    uint8_t* myP = sP + g * TILE_BYTES;
+    float* my_lse = s_lse + g * SUB;
+    float* my_delta = s_delta + g * SUB;
+    bool alive = true;
+    int n = 0;
+    int next_drain = g;                                     // group g drains the pairs of its parity
+    // one pair's dQ: tensor memory -> fp32 reductions into the accumulator rows of its 128 queries
+    auto drain = [&](int pair) -> bool {
+      const bool ok = bb::mbar_wait(&dq_full[pair & 1], (pair >> 1) & 1, &ctl->abort_flag, p.status);
+      if (!bb::named_bar_all(3 + g, GROUP_THREADS, ok)) return false;
+      bb::tc_fence_after_sync();
+      float v[32];
+      ld32(tDQ + 64 * (pair & 1) + lane_addr + hf * 32, v);
+      bb::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) bb::mbar_arrive(&dq_empty[pair & 1]);
+      const int q = (qstart + 2 * pair) * SUB + row;
+      if (q < p.S) {
+        float* dst = acc_g + (long long)q * HD + hf * 32;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) red_add_f32x4(dst + 4 * c, v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+      }
+      return true;
+    };
+    // per-column statistics are fetched one sub-block ahead so their latency is off the critical path
+    float nx_lse = 0.f, nx_delta = 0.f;
+    if (gt < SUB && g < nblk) {
+      const int q = (qstart + g) * SUB + gt;
+      if (q < p.S) { nx_lse = lse_g[q] * LOG2E; nx_delta = delta_g[q]; }
+    }
+    for (int i = g; i < nblk && alive; i += 2, ++n) {
+      const int qc0 = (qstart + i) * SUB;
+      const int ps = n & 1;                                  // sub-block i belongs to pair n
+      // (the group's previous readers are past their last use once everybody is through this barrier)
+      bb::named_bar_sync(1 + g, GROUP_THREADS);
+      if (gt < SUB) { my_lse[gt] = nx_lse; my_delta[gt] = nx_delta; }
+      bb::named_bar_sync(1 + g, GROUP_THREADS);
+      if (gt < SUB && i + 2 < nblk) {
+        const int q = (qstart + i + 2) * SUB + gt;
+        nx_lse = (q < p.S) ? lse_g[q] * LOG2E : 0.f;
+        nx_delta = (q < p.S) ? delta_g[q] : 0.f;
+      }
+      const uint32_t tS = tmem + 64 * g, tDP = tmem + 128 + 64 * g;
+      const bool ok = bb::mbar_wait(&s_full[g], n & 1, &ctl->abort_flag, p.status);
+      if (!bb::named_bar_all(3 + g, GROUP_THREADS, ok)) { alive = false; break; }
+      bb::tc_fence_after_sync();
+      // (keys past the sequence end must not reach dQ: their rows of dK / dV are simply not stored)
+      const bool need_mask = (qc0 + SUB > p.S) || (k0 + TQ > p.S) || (p.causal && k0 + TQ - 1 > qc0);
+      uint32_t pkP[16], pkDS[16];                            // this thread's 32 P^T and dS^T values as bf16 pairs
+      {
+        float sv[32], dp[32];
+        ld32x2(tS + lane_addr + hf * 32, tDP + lane_addr + hf * 32, sv, dp);
+#pragma unroll
+        for (int e4 = 0; e4 < 32; e4 += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(my_lse + hf * 32 + e4);
+          const float4 d4 = *reinterpret_cast<const float4*>(my_delta + hf * 32 + e4);
+          const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, ds[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int e = e4 + u;
+            float pv = ex2(fmaf(sv[e], sl, -ls[u]));
+            if (need_mask) {
+              const int q = qc0 + hf * 32 + e;
+              if (q >= p.S || krow >= p.S || (p.causal && krow > q)) pv = 0.f;
+            }
+            sv[e] = pv;
+            dp[e] = pv * (dp[e] - ds[u]);
+          }
+        }
+        pack32(sv, pkP);
+        pack32(dp, pkDS);
+      }
+      bb::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) bb::mbar_arrive(&s_empty[g]);
+      // P^T's buffer is free once the dV update that read it retired; the pair slot's dS^T buffers once
+      // the dK updates and the dQ product of the pair that used the slot before have
+      const bool ok2 = bb::mbar_wait(&p_empty[g], (n & 1) ^ 1, &ctl->abort_flag, p.status) &&
+                       bb::mbar_wait(&ds_empty[ps], ((n >> 1) & 1) ^ 1, &ctl->abort_flag, p.status);
+      if (!bb::named_bar_all(3 + g, GROUP_THREADS, ok2)) { alive = false; break; }
+      atom_store_half_row(myP, row, hf, pkP);
+      atom_store_half_row(sDS + (ps * 2 + g) * TILE_BYTES, row, hf, pkDS);
+      bb::fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) bb::mbar_arrive(&p_full[g]);
+      // a pair of this group's parity that is certainly complete by now: the one before last (group 0) /
+      // the last one (group 1; its second half was staged one iteration ago)
+      if (next_drain <= n - 2 + g) {
+        if (!drain(next_drain)) { alive = false; break; }
+        next_drain += 2;
+      }
+    }
+    while (alive && next_drain < npairs) {
+      if (!drain(next_drain)) { alive = false; break; }
+      next_drain += 2;
+    }
+    const bool fin = alive && nblk > 0 && bb::mbar_wait(acc_full, 0, &ctl->abort_flag, p.status);
+    if (bb::named_bar_all(3 + g, GROUP_THREADS, fin)) {
+      bb::tc_fence_after_sync();
+      float v[32];
+      // the two groups split the final stores: group 0 writes dV, group 1 writes dK
+      const uint32_t src = (g == 0) ? tDV : tDK;
+      ld32(src + lane_addr + hf * 32, v);
+      __nv_bfloat16* dst = (g == 0) ? p.dv : p.dk;
+      if (krow < p.S) store_row32(dst + (long long)(row_base + krow) * p.stride_dqkv + colq + hf * 32, v, g == 0 ? 1.f : p.scale);
+    }
+  }
+  bb::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) bb::tmem_dealloc(tmem, 512);
+}
+
+constexpr int BWD3_SMEM = 2 * TILE_BYTES + 2 * NST3 * SUB_BYTES + 2 * TILE_BYTES + 4 * TILE_BYTES + 4 * SUB * (int)sizeof(float) +
+                          (int)sizeof(Ctl) + 1024;
+
+// dq (bf16, packed projection layout) = scale * accumulator; eight values per thread
+__global__ void __launch_bounds__(256)
+attn_tc_dq_convert_kernel(const TcParams p) {
+  const int per_tok = p.H * 8;
+  const long long total = (long long)p.B * p.S * per_tok;
+  for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < total; c += (long long)gridDim.x * blockDim.x) {
+    const long long tok = c / per_tok;
+    const int within = (int)(c % per_tok), head = within >> 3, part = within & 7;
+    const float4* src = reinterpret_cast<const float4*>(p.dq_acc + (((tok / p.S) * p.H + head) * p.S + (tok % p.S)) * HD + part * 8);
+    const float4 a = __ldcg(src), b = __ldcg(src + 1);
+    uint4 o;
+    o.x = bb::pack_bf16x2(a.x * p.scale, a.y * p.scale); o.y = bb::pack_bf16x2(a.z * p.scale, a.w * p.scale);
+    o.z = bb::pack_bf16x2(b.x * p.scale, b.y * p.scale); o.w = bb::pack_bf16x2(b.z * p.scale, b.w * p.scale);
+    *reinterpret_cast<uint4*>(p.dq + tok * p.stride_dqkv + head * HD + part * 8) = o;
+  }
 }
 
 // ------------------------------------------------------------------ forward (two query tiles in ping-pong)
@@ -637,7 +940,7 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       bb::tma_load_2d(sQ + TILE_BYTES, &tm_q, q_full, colq, row_base + qb);
       for (int jj = 0; jj <= jmax; ++jj) {
         const int s = jj % NKV;
-        if (!bb::mbar_wait_spin(&kv_empty[s], ((jj / NKV) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+        if (!bb::mbar_wait(&kv_empty[s], ((jj / NKV) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
         bb::mbar_arrive_expect_tx(&kv_full[s], 2 * SUB_BYTES);
         bb::tma_load_2d(sK + s * SUB_BYTES, &tm_kv, &kv_full[s], colk, row_base + jj * SUB);
         bb::tma_load_2d(sV + s * SUB_BYTES, &tm_kv, &kv_full[s], colv, row_base + jj * SUB);
@@ -647,7 +950,7 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const uint64_t dQ0 = desc_k0(bb::smem_u32(sQ)), dP0 = desc_k0(bb::smem_u32(sP));
     const uint64_t dK0 = desc_k0(bb::smem_u32(sK)), dVm0 = desc_mn0(bb::smem_u32(sV));   // stage 0; stage s: + s * SUB_BYTES / 16
     const uint32_t i_s = idesc(64, 0, 0), i_pv = idesc(64, 0, 1);
-    bool alive = bb::mbar_wait_spin(q_full, 0, &ctl->abort_flag, p.status);
+    bool alive = bb::mbar_wait(q_full, 0, &ctl->abort_flag, p.status);
     // scores of sub-block jj for group g into score buffer jj & 1
     auto issue_scores = [&](int g, int jj) {
       const uint64_t dK = dK0 + (uint64_t)((jj % NKV) * (SUB_BYTES >> 4)), dQ = dQ0 + (uint64_t)(g * (TILE_BYTES >> 4));
@@ -658,7 +961,7 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     };
     // prologue: the first two score products of each group
     for (int jj = 0; jj < 2 && jj <= jmax && alive; ++jj) {
-      if (!bb::mbar_wait_spin(&kv_full[jj % NKV], 0, &ctl->abort_flag, p.status)) { alive = false; break; }
+      if (!bb::mbar_wait(&kv_full[jj % NKV], 0, &ctl->abort_flag, p.status)) { alive = false; break; }
       bb::tc_fence_after_sync();
       if (lane == 0) {
 #pragma unroll
@@ -673,9 +976,9 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       for (int g = 0; g < 2; ++g) {
         if (jj > BB_LAST(g)) continue;
         // P_g(jj) is in shared memory, and group g is done reading S_g(jj): its buffer is free
-        if (!bb::mbar_wait_spin(&p_full[g], jj & 1, &ctl->abort_flag, p.status)) { alive = false; break; }
+        if (!bb::mbar_wait(&p_full[g], jj & 1, &ctl->abort_flag, p.status)) { alive = false; break; }
         const bool more = (jj + 2 <= BB_LAST(g));
-        if (more && !bb::mbar_wait_spin(&kv_full[(jj + 2) % NKV], ((jj + 2) / NKV) & 1, &ctl->abort_flag, p.status)) { alive = false; break; }
+        if (more && !bb::mbar_wait(&kv_full[(jj + 2) % NKV], ((jj + 2) / NKV) & 1, &ctl->abort_flag, p.status)) { alive = false; break; }
         bb::tc_fence_after_sync();
         if (lane == 0) {
           if (more) issue_scores(g, jj + 2);               // first: the group's next-but-one scores
@@ -708,7 +1011,7 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     bool alive = true;
     for (int jj = 0; jj <= lastj; ++jj) {
       const int b = jj & 1;
-      const bool got = bb::mbar_wait_spin(&s_full[2 * g + b], (jj >> 1) & 1, &ctl->abort_flag, p.status);
+      const bool got = bb::mbar_wait(&s_full[2 * g + b], (jj >> 1) & 1, &ctl->abort_flag, p.status);
       if (!__all_sync(0xffffffffu, got)) { alive = false; break; }
       bb::tc_fence_after_sync();
       const int c0 = jj * SUB;
@@ -744,7 +1047,7 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       l_i = l_i * alpha + rs;
       // the product that read this P buffer two sub-blocks ago has retired (and so has the last one)
       if (jj > 0) {
-        const bool ok = bb::mbar_wait_spin(&pv_full[g], (jj - 1) & 1, &ctl->abort_flag, p.status);
+        const bool ok = bb::mbar_wait(&pv_full[g], (jj - 1) & 1, &ctl->abort_flag, p.status);
         if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
       }
       atom_store_row64(sP + (2 * g + b) * TILE_BYTES, row, sa, sb);
@@ -762,7 +1065,7 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
     }
     if (lastj >= 0) {
-      const bool fin = alive && bb::mbar_wait_spin(&pv_full[g], lastj & 1, &ctl->abort_flag, p.status);
+      const bool fin = alive && bb::mbar_wait(&pv_full[g], lastj & 1, &ctl->abort_flag, p.status);
       if (__all_sync(0xffffffffu, fin)) {
         bb::tc_fence_after_sync();
         float pa[32], pb[32];
@@ -813,8 +1116,8 @@ int bb_attention_tc_fwd(const void* qkv_q, void* out, float* lse, int B, int H, 
 }
 
 int bb_attention_tc_bwd(const void* qkv_q, const void* out, const void* d_out, const float* lse, void* dq, void* dk, void* dv,
-                        float* delta, int B, int H, int S, long long stride_qkv, long long stride_o, long long stride_dqkv,
-                        int causal, float scale, cudaStream_t stream) {
+                        float* delta, float* dq_acc, int B, int H, int S, long long stride_qkv, long long stride_o,
+                        long long stride_dqkv, int causal, float scale, cudaStream_t stream) {
   if (int rc = bbhost::bind_context()) return rc;
   CUtensorMap tm_qkv, tm_do;
   const long long T = (long long)B * S;
@@ -827,12 +1130,26 @@ int bb_attention_tc_bwd(const void* qkv_q, const void* out, const void* d_out, c
   CUtensorMap tm_qkv64, tm_do64;
   if (int rc = bbhost::encode_2d(&tm_qkv64, qkv_q, T, 3LL * H * HD, stride_qkv, HD, SUB)) return rc;
   if (int rc = bbhost::encode_2d(&tm_do64, d_out, T, (long long)H * HD, stride_o, HD, SUB)) return rc;
-  BB_ONCE_PER_DEVICE({ if (int rc = set_smem(attn_tc_bwd2_kernel, BWD2_SMEM)) return rc; });
+  // BB_ATTENTION_BWD=split in the environment selects the two-role kernel (dK/dV and dQ computed by
+  // different CTAs, every sum in a fixed order); the default is the fused kernel
+  static const bool split = [] { const char* e = getenv("BB_ATTENTION_BWD"); return e && e[0] == 's'; }();
   const long long chunks = T * H * 8;
   long long dgrid = (chunks + 511) / 512, cap = (long long)bb_num_sms() * 8;
+  if (split) {
+    BB_ONCE_PER_DEVICE({ if (int rc = set_smem(attn_tc_bwd2_kernel, BWD2_SMEM)) return rc; });
+    attn_tc_delta_kernel<<<(int)(dgrid < cap ? dgrid : cap), 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out, p);
+    dim3 grid(2 * ((S + TQ - 1) / TQ), H, B);
+    attn_tc_bwd2_kernel<<<grid, NT2, BWD2_SMEM, stream>>>(tm_qkv, tm_qkv64, tm_do, tm_do64, p);
+    BB_CUDA_CHECK(cudaGetLastError());
+    return BB_OK;
+  }
+  p.dq_acc = dq_acc;
+  BB_ONCE_PER_DEVICE({ if (int rc = set_smem(attn_tc_bwd3_kernel, BWD3_SMEM)) return rc; });
   attn_tc_delta_kernel<<<(int)(dgrid < cap ? dgrid : cap), 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out, p);
-  dim3 grid(2 * ((S + TQ - 1) / TQ), H, B);
-  attn_tc_bwd2_kernel<<<grid, NT2, BWD2_SMEM, stream>>>(tm_qkv, tm_qkv64, tm_do, tm_do64, p);
+  dim3 grid((S + TQ - 1) / TQ, H, B);
+  attn_tc_bwd3_kernel<<<grid, NT2, BWD3_SMEM, stream>>>(tm_qkv, tm_qkv64, tm_do64, p);
+  long long cgrid = (chunks + 255) / 256;
+  attn_tc_dq_convert_kernel<<<(int)(cgrid < cap ? cgrid : cap), 256, 0, stream>>>(p);
   BB_CUDA_CHECK(cudaGetLastError());
   return BB_OK;
 }

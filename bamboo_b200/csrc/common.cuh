@@ -142,31 +142,6 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
   }
 }
 
-// Bounded wait that polls with test_wait (never suspends the thread): for hand-offs on a
-// latency-critical path, where the wake-up delay of a suspended try_wait would dominate.
-__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* abort, int* status) {
-  uint32_t ok;
-  uint64_t t0 = 0;
-  for (uint32_t spin = 0;; ++spin) {
-    asm volatile(
-        "{\n\t.reg .pred P;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, P;\n\t}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    if (ok) return true;
-    if ((spin & 4095u) == 4095u) {
-      if (*abort) return false;
-      uint64_t now = globaltimer_ns();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > BB_WAIT_LIMIT_NS) {
-        *abort = 1;
-        if (status) atomicCAS(status, 0, BB_STATUS_KERNEL_WAIT_TIMEOUT);
-        return false;
-      }
-    }
-  }
-}
-
 // ---------------------------------------------------------------- TMA (no cluster multicast anywhere)
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, uint64_t* bar, int c0, int c1) {
   asm volatile(

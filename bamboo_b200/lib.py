@@ -63,7 +63,7 @@ class ConvDesc(ctypes.Structure):
 HALF_ATTENTION, HALF_MLP = 0, 1
 # kernels behind one call of bb_block_half_fwd / bb_block_half_bwd, per half (launch accounting)
 HALF_FWD_LAUNCHES = {HALF_ATTENTION: 4, HALF_MLP: 3}
-HALF_BWD_LAUNCHES = {HALF_ATTENTION: 9, HALF_MLP: 7}   # + 1 for attention with a head dimension other than 64
+HALF_BWD_LAUNCHES = {HALF_ATTENTION: 10, HALF_MLP: 7}   # attention backward: three launches for either head dimension
 
 _lib = None
 _lock = threading.Lock()
@@ -370,7 +370,7 @@ def block_half_fwd(desc, half, x, saved, out):
 def block_half_bwd(desc, half, x, saved, dout, dx, scratch, side_stream=None):
     """``side_stream``: raw handle of the stream for the weight gradients (None: the current stream)."""
     global LAUNCHES
-    LAUNCHES += HALF_BWD_LAUNCHES[half] + (1 if half == HALF_ATTENTION and desc.head_dim != 64 else 0)
+    LAUNCHES += HALF_BWD_LAUNCHES[half]
     main = _stream()
     side = main if side_stream is None else ctypes.c_void_p(side_stream)
     check(load().bb_block_half_bwd(ctypes.byref(desc), _I(half), _ptr(x), _ptr(saved), _ptr(dout), _ptr(dx), _ptr(scratch),

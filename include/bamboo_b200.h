@@ -148,6 +148,11 @@ int bb_embedding_bwd(const long long* tokens, const void* dout, float* dwte, flo
  * (EX/pipeline_parallelism/gpt2.py:66-75) and its autograd backward. */
 int bb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H, int S, int D,
                      long long stride_qkv, long long stride_o, int causal, float scale, void* stream);
+/* Backward: dq, dk, dv in the layout of q, k, v.  The workspace holds the per-row sums delta and, for
+ * head dimension 64, an fp32 accumulator [B, H, S, 64]: each CTA owns 128 keys, computes the scores
+ * once and adds its dQ contributions with vector reductions, so dq can differ in the last bits
+ * from run to run (the order of a row's additions is not fixed); dk and dv do not.
+ * BB_ATTENTION_BWD=split in the environment selects kernels that keep every sum in a fixed order. */
 long long bb_attention_bwd_workspace_bytes(int B, int H, int S);
 int bb_attention_bwd(const void* q, const void* k, const void* v, const void* out, const void* d_out, const float* lse,
                      void* dq, void* dk, void* dv, void* workspace, long long workspace_bytes, int B, int H, int S,

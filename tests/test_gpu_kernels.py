@@ -312,7 +312,11 @@ def _attn_ref(qkv, B, H, S, D, causal):
 
 @pytest.mark.parametrize("B,H,S,D,causal", [(2, 4, 128, 64, True), (2, 3, 256, 64, False), (1, 2, 1024, 64, True),
                                             (1, 2, 200, 64, True), (1, 2, 72, 64, False), (1, 2, 256, 128, True),
-                                            (2, 2, 320, 128, False)])
+                                            (2, 2, 320, 128, False),
+                                            # an odd number of 64-query sub-blocks (the fused backward pairs them up and
+                                            # pads with a masked one that reads the next batch's rows), several key tiles
+                                            (2, 2, 192, 64, True), (2, 2, 192, 64, False), (2, 1, 448, 64, True),
+                                            (1, 1, 2048, 64, True), (3, 2, 640, 64, False)])
 def test_attention(L, B, H, S, D, causal):
     torch.manual_seed(9)
     qkv = torch.randn(B * S, 3 * H * D, device="cuda").bfloat16()
