@@ -571,20 +571,20 @@ attn_tc_bwd2_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
 // but S^T and dP^T are computed once: the staged dS^T tiles of two consecutive sub-blocks
 // ([128 keys x 64 queries] each, adjacent in shared memory) also serve, read with the queries as
 // the M dimension, as the A operand of dQ[128 queries x 64] = dS . K for that pair of sub-blocks.
-// The pair's dQ leaves tensor memory as fp32 vector reductions into a [B, H, S, 64] accumulator
-// (each query row receives one contribution per key tile; their order is not fixed), which a small
-// kernel scales and converts once all CTAs are done.  Five contractions instead of seven, one
+// The pair's dQ [128 x 64] fp32 leaves tensor memory through a shared-memory staging tile and two
+// bulk tensor add-reductions (one per 32-column half) into a [B, H, S, 64] accumulator: each query
+// row receives one contribution per key tile, in no fixed order; a small kernel scales and converts
+// the sums once all CTAs are done.  Five contractions instead of seven, one
 // exponential pass instead of two, half the CTAs.
-// smem: K, V [128 x 64] | Q, dO sub-tiles x NST3 | P^T x 2 | dS^T x 2 pair slots x 2 groups | lse / delta
+// smem: K, V [128 x 64] | Q, dO sub-tiles x NST3 | P^T x 2 | dS^T x 2 pair slots x 2 groups | dQ staging 2 x 16 KiB | lse / delta
 // TMEM: S^T 2 x 64 | dP^T 2 x 64 | dV 64 | dK 64 | dQ 2 x 64
-constexpr int NST3 = 5;
-__device__ __forceinline__ void red_add_f32x4(float* dst, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" :: "l"(dst), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-
-__global__ void __launch_bounds__(NT2, 1)
+constexpr int NST3 = 4;
+// warps: 0 TMA, 1 score products (S^T, dP^T), 2 updates (dV, dK, dQ), 3 idle (compute warp w must sit at
+// w % 4 == its tensor-memory lane quarter), 4..19 the two compute groups
+constexpr int NT3 = 128 + 2 * GROUP_THREADS;
+__global__ void __launch_bounds__(NT3, 1)
 attn_tc_bwd3_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_constant__ CUtensorMap tm64,
-                    const __grid_constant__ CUtensorMap tm_do64, const TcParams p) {
+                    const __grid_constant__ CUtensorMap tm_do64, const __grid_constant__ CUtensorMap tm_acc, const TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
@@ -593,7 +593,8 @@ attn_tc_bwd3_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
   uint8_t* sDO = sQ + NST3 * SUB_BYTES;        // NST3 stages x 8 KiB
   uint8_t* sP = sDO + NST3 * SUB_BYTES;        // [group] x 16 KiB
   uint8_t* sDS = sP + 2 * TILE_BYTES;          // [pair slot][group] x 16 KiB
-  float* s_lse = reinterpret_cast<float*>(sDS + 4 * TILE_BYTES);   // [2][64]
+  uint8_t* sDQ = sDS + 4 * TILE_BYTES;         // [column half] x 16 KiB: [128 queries x 32] fp32, 128-byte rows
+  float* s_lse = reinterpret_cast<float*>(sDQ + 2 * TILE_BYTES);   // [2][64]
   float* s_delta = s_lse + 2 * SUB;                                // [2][64]
   Ctl* ctl = reinterpret_cast<Ctl*>(s_delta + 2 * SUB);
   uint64_t* kv_full = &ctl->bars[0];
@@ -632,7 +633,7 @@ attn_tc_bwd3_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
     }
     bb::mbar_init(acc_full, 1);
     bb::fence_barrier_init();
-    bb::tma_prefetch_desc(&tm128); bb::tma_prefetch_desc(&tm64); bb::tma_prefetch_desc(&tm_do64);
+    bb::tma_prefetch_desc(&tm128); bb::tma_prefetch_desc(&tm64); bb::tma_prefetch_desc(&tm_do64); bb::tma_prefetch_desc(&tm_acc);
   }
   if (warp == 1) { bb::tmem_alloc(&ctl->tmem_slot, 512); bb::tmem_relinquish(); }
   bb::tc_fence_before_sync();
@@ -656,86 +657,93 @@ attn_tc_bwd3_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
       }
     }
   } else if (warp == 1) {
+    // score products: one thread issues S^T = K . Q^T and dP^T = V . dO^T for every sub-block, as soon as its
+    // operands have landed and the group that owns the score buffer has read the previous contents
     const uint64_t dK0 = desc_k0(bb::smem_u32(sK)), dV0 = desc_k0(bb::smem_u32(sV));
     const uint64_t dQ0 = desc_k0(bb::smem_u32(sQ)), dDO0 = desc_k0(bb::smem_u32(sDO));   // stage 0; stage s: + s * SUB_BYTES / 16
+    const uint32_t i_s = idesc(64, 0, 0);
+    bool alive = bb::mbar_wait(kv_full, 0, &ctl->abort_flag, p.status);
+    for (int i = 0; i < nblk && alive; ++i) {
+      const int s = i % NST3, b = i & 1;
+      if (!bb::mbar_wait(&q_full[s], (i / NST3) & 1, &ctl->abort_flag, p.status)) break;
+      if (!bb::mbar_wait(&s_empty[b], ((i >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
+      bb::tc_fence_after_sync();
+      if (lane == 0) {
+        const uint64_t dQ = dQ0 + (uint64_t)(s * (SUB_BYTES >> 4)), dDO = dDO0 + (uint64_t)(s * (SUB_BYTES >> 4));
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          bb::umma_f16(tmem + 64 * b, desc_kmajor(dK0, k), desc_kmajor(dQ, k), i_s, k > 0);
+          bb::umma_f16(tmem + 128 + 64 * b, desc_kmajor(dV0, k), desc_kmajor(dDO, k), i_s, k > 0);
+        }
+        bb::umma_commit(&s_full[b]);
+      }
+      __syncwarp();
+    }
+  } else if (warp == 2) {
+    // updates: a second issuing thread, so that the score products of the next sub-blocks never queue
+    // behind a wait for staged operands (and the two instruction streams issue side by side)
     const uint64_t dQm0 = desc_mn0(bb::smem_u32(sQ)), dDOm0 = desc_mn0(bb::smem_u32(sDO));
     const uint64_t dP0 = desc_k0(bb::smem_u32(sP)), dDS0 = desc_k0(bb::smem_u32(sDS));
     // dS^T of a pair slot read with the queries as M: two 64-query blocks one tile apart, 8-key groups 1 KiB apart
     const uint64_t dDSm0 = bb::make_smem_desc_sw128(bb::smem_u32(sDS), TILE_BYTES, 1024);
     const uint64_t dKm0 = desc_mn0(bb::smem_u32(sK));
-    const uint32_t i_s = idesc(64, 0, 0), i_acc = idesc(64, 0, 1), i_dq = idesc(64, 1, 1);
+    const uint32_t i_acc = idesc(64, 0, 1), i_dq = idesc(64, 1, 1);
     bool alive = bb::mbar_wait(kv_full, 0, &ctl->abort_flag, p.status);
-    // the score products run two sub-blocks ahead of the dV / dK updates
-    for (int i = 0; i < nblk + 2 && alive; ++i) {
-      if (i < nblk) {
-        const int s = i % NST3, b = i & 1;
-        if (!bb::mbar_wait(&q_full[s], (i / NST3) & 1, &ctl->abort_flag, p.status)) break;
-        if (!bb::mbar_wait(&s_empty[b], ((i >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
-        bb::tc_fence_after_sync();
-        if (lane == 0) {
-          const uint64_t dQ = dQ0 + (uint64_t)(s * (SUB_BYTES >> 4)), dDO = dDO0 + (uint64_t)(s * (SUB_BYTES >> 4));
+    for (int ii = 0; ii < nblk && alive; ++ii) {
+      const int s2 = ii % NST3, g2 = ii & 1, pair = ii >> 1, ps = pair & 1;
+      // (the sub-tiles landed long ago - the score products read them; the wait makes them visible to this thread)
+      if (!bb::mbar_wait(&q_full[s2], (ii / NST3) & 1, &ctl->abort_flag, p.status)) break;
+      if (!bb::mbar_wait(&p_full[g2], pair & 1, &ctl->abort_flag, p.status)) break;
+      bb::tc_fence_after_sync();
+      if (lane == 0) {
+        const uint64_t dQ2 = dQm0 + (uint64_t)(s2 * (SUB_BYTES >> 4)), dDO2 = dDOm0 + (uint64_t)(s2 * (SUB_BYTES >> 4));
+        const uint64_t dP = dP0 + (uint64_t)(g2 * (TILE_BYTES >> 4));
+        const uint64_t dDS = dDS0 + (uint64_t)((ps * 2 + g2) * (TILE_BYTES >> 4));
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            bb::umma_f16(tmem + 64 * b, desc_kmajor(dK0, k), desc_kmajor(dQ, k), i_s, k > 0);
-            bb::umma_f16(tmem + 128 + 64 * b, desc_kmajor(dV0, k), desc_kmajor(dDO, k), i_s, k > 0);
-          }
-          bb::umma_commit(&s_full[b]);
+        for (int k = 0; k < 4; ++k) {
+          bb::umma_f16(tDV, desc_kmajor(dP, k), desc_mnmajor64(dDO2, k), i_acc, (ii > 0 || k > 0));
+          bb::umma_f16(tDK, desc_kmajor(dDS, k), desc_mnmajor64(dQ2, k), i_acc, (ii > 0 || k > 0));
         }
-        __syncwarp();
+        bb::umma_commit(&p_empty[g2]);
+        bb::umma_commit(&q_empty[s2]);
       }
-      if (i >= 2) {
-        const int ii = i - 2, s2 = ii % NST3, g2 = ii & 1, pair = ii >> 1, ps = pair & 1;
-        if (!bb::mbar_wait(&p_full[g2], pair & 1, &ctl->abort_flag, p.status)) break;
+      __syncwarp();
+      if (g2 == 1) {
+        // both halves of the pair are staged: dQ[pair] = dS . K over the tile's 128 keys
+        if (!bb::mbar_wait(&dq_empty[pair & 1], ((pair >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
         bb::tc_fence_after_sync();
         if (lane == 0) {
-          const uint64_t dQ2 = dQm0 + (uint64_t)(s2 * (SUB_BYTES >> 4)), dDO2 = dDOm0 + (uint64_t)(s2 * (SUB_BYTES >> 4));
-          const uint64_t dP = dP0 + (uint64_t)(g2 * (TILE_BYTES >> 4));
-          const uint64_t dDS = dDS0 + (uint64_t)((ps * 2 + g2) * (TILE_BYTES >> 4));
+          const uint64_t dA = dDSm0 + (uint64_t)(ps * 2 * (TILE_BYTES >> 4));
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            bb::umma_f16(tDV, desc_kmajor(dP, k), desc_mnmajor64(dDO2, k), i_acc, (ii > 0 || k > 0));
-            bb::umma_f16(tDK, desc_kmajor(dDS, k), desc_mnmajor64(dQ2, k), i_acc, (ii > 0 || k > 0));
-          }
-          bb::umma_commit(&p_empty[g2]);
-          bb::umma_commit(&q_empty[s2]);
+          for (int k = 0; k < 8; ++k)
+            bb::umma_f16(tDQ + 64 * (pair & 1), desc_mnmajor64(dA, k), desc_mnmajor64(dKm0, k), i_dq, k > 0);
+          bb::umma_commit(&ds_empty[ps]);
+          bb::umma_commit(&dq_full[pair & 1]);
+          if (ii == nblk - 1) bb::umma_commit(acc_full);
         }
         __syncwarp();
-        if (g2 == 1) {
-          // both halves of the pair are staged: dQ[pair] = dS . K over the tile's 128 keys
-          if (!bb::mbar_wait(&dq_empty[pair & 1], ((pair >> 1) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
-          bb::tc_fence_after_sync();
-          if (lane == 0) {
-            const uint64_t dA = dDSm0 + (uint64_t)(ps * 2 * (TILE_BYTES >> 4));
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-              bb::umma_f16(tDQ + 64 * (pair & 1), desc_mnmajor64(dA, k), desc_mnmajor64(dKm0, k), i_dq, k > 0);
-            bb::umma_commit(&ds_empty[ps]);
-            bb::umma_commit(&dq_full[pair & 1]);
-            if (ii == nblk - 1) bb::umma_commit(acc_full);
-          }
-          __syncwarp();
-        }
       }
     }
-  } else {
-    const int g = (warp - 2) >> 3;
-    const int hf = ((warp - 2) >> 2) & 1;                  // which 32 of the sub-block's 64 query columns
+  } else if (warp >= 4) {
+    const int g = (warp - 4) >> 3;
+    const int hf = ((warp - 4) >> 2) & 1;                  // which 32 of the sub-block's 64 query columns
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;                   // key row inside the tile / query row inside a pair
-    const int gt = threadIdx.x - 64 - GROUP_THREADS * g;   // thread index inside the group
+    const int gt = threadIdx.x - 128 - GROUP_THREADS * g;  // thread index inside the group
     const int krow = k0 + row;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const float* lse_g = p.lse + ((long long)batch * p.H + head) * p.S;
     const float* delta_g = p.delta + ((long long)batch * p.H + head) * p.S;
-    float* acc_g = p.dq_acc + ((long long)batch * p.H + head) * p.S * HD;
     const float sl = p.scale * LOG2E;
     uint8_t* myP = sP + g * TILE_BYTES;
     float* my_lse = s_lse + g * SUB;
     float* my_delta = s_delta + g * SUB;
     bool alive = true;
     int n = 0;
-    int next_drain = g;                                     // group g drains the pairs of its parity
-    // one pair's dQ: tensor memory -> fp32 reductions into the accumulator rows of its 128 queries
+    int next_drain = 0;                                     // group 1 drains every pair
+    const long long acc_row0 = ((long long)batch * p.H + head) * p.S;
+    // one pair's dQ: tensor memory -> staging tile -> add-reduction into the accumulator rows of its 128
+    // queries (rows past the sequence end carry exact zeros: their dS was masked)
     auto drain = [&](int pair) -> bool {
       const bool ok = bb::mbar_wait(&dq_full[pair & 1], (pair >> 1) & 1, &ctl->abort_flag, p.status);
       if (!bb::named_bar_all(3 + g, GROUP_THREADS, ok)) return false;
@@ -745,11 +753,20 @@ attn_tc_bwd3_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
       bb::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) bb::mbar_arrive(&dq_empty[pair & 1]);
-      const int q = (qstart + 2 * pair) * SUB + row;
-      if (q < p.S) {
-        float* dst = acc_g + (long long)q * HD + hf * 32;
+      // the staging tile is free once the previous pair's reductions have read it
+      if (gt == 0) bb::bulk_wait_group_read<0>();
+      bb::named_bar_sync(3 + g, GROUP_THREADS);
+      uint8_t* dst = sDQ + hf * TILE_BYTES + row * 128;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) red_add_f32x4(dst + 4 * c, v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<float4*>(dst + ((c ^ (row & 7)) << 4)) = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+      bb::fence_proxy_async();
+      bb::named_bar_sync(3 + g, GROUP_THREADS);
+      if (gt == 0) {
+        const int r0 = (int)(acc_row0 + (long long)(qstart + 2 * pair) * SUB);
+        bb::tma_reduce_add_2d(&tm_acc, sDQ, 0, r0);
+        bb::tma_reduce_add_2d(&tm_acc, sDQ + TILE_BYTES, 32, r0);
+        bb::bulk_commit_group();
       }
       return true;
     };
@@ -814,17 +831,17 @@ attn_tc_bwd3_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
       bb::fence_proxy_async();
       __syncwarp();
       if (lane == 0) bb::mbar_arrive(&p_full[g]);
-      // a pair of this group's parity that is certainly complete by now: the one before last (group 0) /
-      // the last one (group 1; its second half was staged one iteration ago)
-      if (next_drain <= n - 2 + g) {
+      // group 1 drains the previous pair, whose second half it staged one iteration ago: certainly complete
+      if (g == 1 && next_drain < n) {
         if (!drain(next_drain)) { alive = false; break; }
-        next_drain += 2;
+        ++next_drain;
       }
     }
-    while (alive && next_drain < npairs) {
+    while (g == 1 && alive && next_drain < npairs) {
       if (!drain(next_drain)) { alive = false; break; }
-      next_drain += 2;
+      ++next_drain;
     }
+    if (g == 1 && gt == 0) bb::bulk_wait_group<0>();       // the reductions read this CTA's shared memory
     const bool fin = alive && nblk > 0 && bb::mbar_wait(acc_full, 0, &ctl->abort_flag, p.status);
     if (bb::named_bar_all(3 + g, GROUP_THREADS, fin)) {
       bb::tc_fence_after_sync();
@@ -841,7 +858,7 @@ attn_tc_bwd3_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
   if (warp == 1) bb::tmem_dealloc(tmem, 512);
 }
 
-constexpr int BWD3_SMEM = 2 * TILE_BYTES + 2 * NST3 * SUB_BYTES + 2 * TILE_BYTES + 4 * TILE_BYTES + 4 * SUB * (int)sizeof(float) +
+constexpr int BWD3_SMEM = 2 * TILE_BYTES + 2 * NST3 * SUB_BYTES + 2 * TILE_BYTES + 4 * TILE_BYTES + 2 * TILE_BYTES + 4 * SUB * (int)sizeof(float) +
                           (int)sizeof(Ctl) + 1024;
 
 // dq (bf16, packed projection layout) = scale * accumulator; eight values per thread
@@ -1147,7 +1164,10 @@ int bb_attention_tc_bwd(const void* qkv_q, const void* out, const void* d_out, c
   BB_ONCE_PER_DEVICE({ if (int rc = set_smem(attn_tc_bwd3_kernel, BWD3_SMEM)) return rc; });
   attn_tc_delta_kernel<<<(int)(dgrid < cap ? dgrid : cap), 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out, p);
   dim3 grid((S + TQ - 1) / TQ, H, B);
-  attn_tc_bwd3_kernel<<<grid, NT2, BWD3_SMEM, stream>>>(tm_qkv, tm_qkv64, tm_do64, p);
+  // the accumulator as [B * H * S rows, 64] fp32; a reduction moves [128 rows x 32 columns]
+  CUtensorMap tm_acc;
+  if (int rc = bbhost::encode_2d(&tm_acc, dq_acc, (long long)B * H * S, HD, HD, 32, TQ, 1)) return rc;
+  attn_tc_bwd3_kernel<<<grid, NT3, BWD3_SMEM, stream>>>(tm_qkv, tm_qkv64, tm_do64, tm_acc, p);
   long long cgrid = (chunks + 255) / 256;
   attn_tc_dq_convert_kernel<<<(int)(cgrid < cap ? cgrid : cap), 256, 0, stream>>>(p);
   BB_CUDA_CHECK(cudaGetLastError());
