@@ -798,6 +798,10 @@ attn_tc_bwd3_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
       {
         float sv[32], dp[32];
         ld32x2(tS + lane_addr + hf * 32, tDP + lane_addr + hf * 32, sv, dp);
+        // the scores are in registers: the buffer can take the sub-block after next while this one is worked on
+        bb::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) bb::mbar_arrive(&s_empty[g]);
 #pragma unroll
         for (int e4 = 0; e4 < 32; e4 += 4) {
           const float4 l4 = *reinterpret_cast<const float4*>(my_lse + hf * 32 + e4);
@@ -818,9 +822,6 @@ attn_tc_bwd3_kernel(const __grid_constant__ CUtensorMap tm128, const __grid_cons
         pack32(sv, pkP);
         pack32(dp, pkDS);
       }
-      bb::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) bb::mbar_arrive(&s_empty[g]);
       // P^T's buffer is free once the dV update that read it retired; the pair slot's dS^T buffers once
       // the dK updates and the dQ product of the pair that used the slot before have
       const bool ok2 = bb::mbar_wait(&p_empty[g], (n & 1) ^ 1, &ctl->abort_flag, p.status) &&
