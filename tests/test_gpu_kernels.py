@@ -333,6 +333,45 @@ def test_attention(L, B, H, S, D, causal):
     close(dqkv, qf.grad)
 
 
+def test_attention_backward_with_fixed_summation_order(L):
+    """BB_ATTENTION_BWD=split selects the two-role backward kernels (dK/dV and dQ by different CTAs, no
+    reductions into an accumulator): same gradients, and bit-identical from run to run.  The switch is read
+    once per process, so the check runs in a child process."""
+    import os
+    import subprocess
+    import sys
+    code = """
+import sys, torch
+sys.path.insert(0, %r)
+import torch.nn.functional as F
+from bamboo_b200 import lib as L
+L.load()
+B, H, S, D = 2, 2, 448, 64
+torch.manual_seed(3)
+qkv = torch.randn(B * S, 3 * H * D, device="cuda").bfloat16()
+out = torch.empty(B * S, H * D, device="cuda", dtype=torch.bfloat16)
+lse = torch.empty(B, H, S, device="cuda")
+L.attention_fwd(qkv, out, lse, B, H, S, D, True)
+qf = qkv.float().requires_grad_(True)
+q, k, v = qf.view(B, S, 3, H, D).permute(2, 0, 3, 1, 4)
+ref = F.scaled_dot_product_attention(q, k, v, is_causal=True).permute(0, 2, 1, 3).reshape(B * S, H * D)
+do = torch.randn_like(out)
+ref.backward(do.float())
+a, b = torch.empty_like(qkv), torch.empty_like(qkv)
+L.attention_bwd(qkv, out, do, lse, a, B, H, S, D, True)
+L.attention_bwd(qkv, out, do, lse, b, B, H, S, D, True)
+torch.cuda.synchronize()
+err = (a.float() - qf.grad).abs().max().item()
+assert err <= 2e-2 * qf.grad.abs().max().item() + 1e-3, err
+assert torch.equal(a, b)
+assert L.read_status() == 0
+print("split backward ok")
+""" % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, BB_ATTENTION_BWD="split")
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "split backward ok" in r.stdout, r.stdout + r.stderr
+
+
 def test_attention_rows_sum_to_one_at_full_size(L):
     """GPT-2-medium attention shape: with V = 1 every output element must be 1."""
     B, H, S, D = 8, 16, 1024, 64
