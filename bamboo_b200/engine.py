@@ -33,6 +33,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
+from . import rendezvous as _rdzv
 from . import schedule
 from .arena import ParamArena
 from .config import PipeConfig
@@ -161,6 +162,21 @@ class PipelineEngine:
         self.next_stage = self._inc(self.stage_id)
         self.stage_ids = [self.stage_id]
 
+        # A job started by the launcher describes its rendezvous in the environment
+        # (PROJECT_PACTUM_ENABLED / ENDPOINT / RUN_ID / MIN_NODES / MAX_NODES / RDZV_CONFIGS /
+        # MAX_PIPE_PARALLEL_SIZE): the handler is built from it and its etcd-backed store carries the
+        # bookkeeping keys, as in deepspeed/runtime/engine.py:152-184.
+        launched = _rdzv.ENV_ENABLED in os.environ
+        if launched:
+            self.max_pipe_parallel_size = os.environ["PROJECT_PACTUM_MAX_PIPE_PARALLEL_SIZE"]
+            if rdzv_handler is None:
+                rdzv_handler = _rdzv.handler_from_env()
+            if store is None:
+                store = rdzv_handler.setup_kv_store()
+                _live_stores.append(store)
+                for rank in range(self.world_size):
+                    store.set(str(rank), "0")
+                store.set("failures", "{}")
         self.rdzv_handler = rdzv_handler or LocalRendezvous(self.grid.topology(), self.world_size)
         self.coordinates = [[self.grid.get_data_parallel_id(), self.stage_id]]
         for info in self.rdzv_handler.get_global_decision():
@@ -179,7 +195,7 @@ class PipelineEngine:
         self.fail_lock = self.rdzv_handler.create_lock("fail-lock")
         self.global_steps = self.rdzv_handler.get_current_step()
         self.global_samples = 0
-        self.join = False
+        self.join = "PROJECT_PACTUM_JOIN" in os.environ    # a worker that joins a job which is already running
 
         if redundancy_level > 1:
             raise NotImplementedError(f"R level {redundancy_level} > 1 is not supported now.")

@@ -674,3 +674,80 @@ def create_rdzv_handler(client, run_id, min_nodes, max_nodes, prefix="/torchelas
     ``RendezvousParameters``: endpoint, protocol, certificates, ``etcd.py:1472-1574``)."""
     return EtcdRendezvousHandler(EtcdRendezvous(client, prefix, run_id, min_nodes, max_nodes, timeout, last_call_timeout,
                                                 etcd_module=etcd_module))
+
+
+# ---------------------------------------------------------------------------------- environment contract
+# The launcher hands the job's rendezvous to every worker through the environment
+# (project_pactum/run/api.py:322-332); the reference engine builds its handler from it
+# (deepspeed/runtime/engine.py:152-184).  Same variables, same defaults here.
+ENV_ENABLED = "PROJECT_PACTUM_ENABLED"
+ENV_KEYS = ("PROJECT_PACTUM_ENDPOINT", "PROJECT_PACTUM_RUN_ID", "PROJECT_PACTUM_MIN_NODES", "PROJECT_PACTUM_MAX_NODES",
+            "PROJECT_PACTUM_RDZV_CONFIGS")
+
+
+def parse_endpoint(endpoint, default_port=2379):
+    """``host[:port]`` / ``[v6 host]:port`` -> (host, port)"""
+    endpoint = endpoint.strip()
+    if not endpoint:
+        return "localhost", default_port
+    if endpoint.startswith("["):
+        host, _, rest = endpoint[1:].partition("]")
+        port = rest[1:] if rest.startswith(":") else ""
+    elif endpoint.count(":") == 1:
+        host, _, port = endpoint.partition(":")
+    else:
+        host, port = endpoint, ""
+    if port and not port.isdigit():
+        raise ValueError(f"The port number of the rendezvous endpoint '{endpoint}' must be an integer between 0 and 65536.")
+    return host, (int(port) if port else default_port)
+
+
+def create_etcd_client(endpoint, config, etcd_module=None):
+    """python-etcd client for ``endpoint`` with the launcher's options (``protocol``, ``cert`` / ``key``,
+    ``cacert``: reference ``_create_etcd_client``, ``etcd.py:1472-1503``)."""
+    if etcd_module is None:
+        try:
+            import etcd as etcd_module
+        except ImportError as e:
+            raise RuntimeError("the etcd rendezvous needs the python-etcd package (module `etcd`)") from e
+    host, port = parse_endpoint(endpoint)
+    protocol = config.get("protocol") or "http"
+    if protocol not in ("http", "https"):
+        raise ValueError("The etcd protocol must be HTTP or HTTPS.")
+    cert = config.get("cert")
+    if cert is not None and config.get("key") is not None:
+        cert = (cert, config.get("key"))
+    return etcd_module.Client(host, port, protocol=protocol, cert=cert, ca_cert=config.get("cacert"), allow_reconnect=True)
+
+
+def handler_from_env(environ=None, etcd_module=None, client=None):
+    """The worker's rendezvous handler as the launcher described it in the environment, or None when
+    the job was not started by the launcher (``PROJECT_PACTUM_ENABLED`` absent).  ``last_call_timeout`` is
+    2 s inside a worker, whatever the launcher's own value, like the reference."""
+    import os
+    environ = os.environ if environ is None else environ
+    if ENV_ENABLED not in environ:
+        return None
+    missing = [k for k in ENV_KEYS if k not in environ]
+    if missing:
+        raise KeyError(f"{ENV_ENABLED} is set but {', '.join(missing)} missing from the environment")
+    config = json.loads(environ["PROJECT_PACTUM_RDZV_CONFIGS"])
+    config["last_call_timeout"] = 2
+    if client is None:
+        client = create_etcd_client(environ["PROJECT_PACTUM_ENDPOINT"], config, etcd_module)
+    return create_rdzv_handler(client, environ["PROJECT_PACTUM_RUN_ID"], int(environ["PROJECT_PACTUM_MIN_NODES"]),
+                               int(environ["PROJECT_PACTUM_MAX_NODES"]), prefix=config.get("etcd_prefix", "/torchelastic/p2p"),
+                               timeout=int(config.get("timeout", DEFAULT_TIMEOUT)),
+                               last_call_timeout=int(config["last_call_timeout"]), etcd_module=etcd_module)
+
+
+def grid_from_env(environ=None):
+    """(num_pipelines, num_stages, coordinates) that the node agent gave this worker
+    (``PROJECT_PACTUM_NUM_PIPELINES / NUM_STAGES / COORDINATES``, agent/api.py:342-362), or None."""
+    import os
+    environ = os.environ if environ is None else environ
+    if "PROJECT_PACTUM_NUM_PIPELINES" not in environ or "PROJECT_PACTUM_NUM_STAGES" not in environ:
+        return None
+    coords = json.loads(environ.get("PROJECT_PACTUM_COORDINATES", "[]"))
+    return int(environ["PROJECT_PACTUM_NUM_PIPELINES"]), int(environ["PROJECT_PACTUM_NUM_STAGES"]), coords
+
