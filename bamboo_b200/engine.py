@@ -685,6 +685,61 @@ class PipelineEngine:
         # shadow copies restart from their owners' state
         self._sync_shadow_state()
 
+    def _layer_shapes(self, layers):
+        """``{layer index: {parameter name: shape}}`` of arbitrary pipeline layers, from the layer specs."""
+        from .module import LayerSpec
+        shapes = {}
+        for idx in sorted(layers):
+            spec = self.module._layer_specs[idx]
+            mod = spec.build() if isinstance(spec, LayerSpec) else spec
+            if isinstance(mod, torch.nn.Module):
+                named = collections.OrderedDict((n, tuple(p.shape)) for n, p in mod.named_parameters() if p.requires_grad)
+                if named:
+                    shapes[idx] = named
+        return shapes
+
+    def _save_shadow_node_state(self, failures):
+        """A member that holds two stages (it absorbed a failed neighbour) and is itself announced to leave at
+        this step carries state nobody else has: the stage it took over is no longer shadowed.  Before it goes,
+        its layers and Adam moments move to the first member that stays, and that member's seats of the round
+        that is ending are extended, so that the re-partition plan of the next round finds the layers there
+        (reference ``save_shadow_node_state``, ``pipe/engine.py:660-727``).  Every member calls this with the
+        same ``failures`` and derives the same plan; returns what this member received."""
+        from . import reconfigure as R
+        recv_decisions, send_decisions = {}, {}
+        for fail_rank, at_step in failures.items():
+            if at_step != self.global_steps:
+                continue
+            prev = self.rdzv_handler.get_previous_state()
+            coords = self.rdzv_handler.get_rank_coordinates_for_version(prev, prev["version"])
+            leaving = coords.get(str(fail_rank), [])
+            if len(leaving) != 2:
+                continue
+            staying = [int(r) for r in coords
+                       if str(r) not in failures and _decode(self.global_store.get(str(r))) == "0"]
+            if not staying:
+                continue
+            send_node, recv_node = int(fail_rank), staying[0]
+            held = [s for _, s in coords.get(str(recv_node), [])]
+            stages = [s for _, s in leaving if s not in held]
+            if not stages:
+                continue
+            layers = set(range(self.module.parts[min(stages)], self.module.parts[max(stages) + 1]))
+            recv_decisions.setdefault(recv_node, {})[send_node] = layers
+            send_decisions.setdefault(send_node, {})[recv_node] = layers
+            if self.global_rank == recv_node:            # one writer: the update compares on the key's index
+                extended = [list(c) for c in coords[str(recv_node)]] + [[leaving[0][0], s] for s in stages]
+                self.rdzv_handler.update_coordinates_for_version(prev["version"], recv_node, extended)
+        if not recv_decisions:
+            return {}
+        incoming = set().union(*recv_decisions.get(self.global_rank, {}).values()) if self.global_rank in recv_decisions else set()
+        t0 = time.time()
+        received = R.transfer_layers(self.dist, self.global_rank, self.world_size, recv_decisions, send_decisions,
+                                     self.get_model_state(), self._layer_shapes(incoming), device=self.device)
+        if received:
+            self.log(f"took over layers {sorted(received)} of a leaving member in {time.time() - t0:.3f} s")
+        return received
+
     def _reconfigure(self, failures):
         """The rendezvous decided to re-form the cluster at this step (a member holding two stages
         is about to leave, or waiting members make another pipeline): re-join, rebuild the
@@ -693,6 +748,7 @@ class PipelineEngine:
         ``reconfigure_cluster`` ``:630-658``)."""
         import torch.distributed as tdist
         from .topology import PipeDataParallelTopology
+        received = self._save_shadow_node_state(failures)
         if failures.get(str(self.global_rank), -1) == self.global_steps:
             self.log("We are reconfiguring and I will die soon anyway. I'm leaving")
             self.global_store.set(str(self.global_rank), "1")
@@ -701,6 +757,7 @@ class PipelineEngine:
         state = self.get_model_state()
         state = {k: [collections.OrderedDict((n, t.clone()) for n, t in v[0].items()),
                      [{kk: tt.clone() for kk, tt in m.items()} for m in v[1]]] for k, v in state.items()}
+        state.update(received)
         self.log(f"Triggered a reconfiguration on global step {self.global_steps}")
         store, rank, world, num_pipelines, num_stages, decision = self.rdzv_handler.next_rendezvous(self.global_rank)
         for info in decision:

@@ -109,13 +109,14 @@ def transfer_layers(dist, my_rank, world_size, recv_decisions, send_decisions, s
     for turn in range(world_size):
         if turn == my_rank:
             for dst, layers in mine_out.items():
+                layers = [i for i in layers if i in state]          # layers without parameters carry no state
                 if not layers:
                     continue
                 p, m = pack_layers(state, layers)
                 dist.send(p.to(device).contiguous(), dst=dst)
                 dist.send(m.to(device).contiguous(), dst=dst)
-        elif turn in mine_in and mine_in[turn]:
-            layers = sorted(mine_in[turn])
+        elif turn in mine_in and any(i in shapes for i in mine_in[turn]):
+            layers = sorted(i for i in mine_in[turn] if i in shapes)
             n = sum(_numel(s) for idx in layers for s in shapes[idx].values())
             p = torch.empty(n, dtype=torch.float32, device=device)
             m = torch.empty(2 * n, dtype=torch.float32, device=device)
