@@ -7,7 +7,8 @@ import pytest
 
 def _line(par, ms, rc="eager", batch=128, failover=None, rc_off_ms=None, model="gpt2-medium"):
     d = {"metric": "tokens/sec", "ms_per_step": ms,
-         "config": {"workload": f"{model} (24 layers) pipeline step", "parallelism": par, "rc": rc, "global_batch": batch}}
+         "config": {"workload": f"{model} (24 layers) pipeline step, micro-batch 8 x 16", "parallelism": par, "rc": rc,
+                    "global_batch": batch}}
     if failover:
         d["failover"] = failover
     if rc_off_ms:
@@ -32,7 +33,37 @@ def test_constants_and_install():
     sim = SimpleNamespace(num_pipelines=2, num_stages=4, step_delta=None, fallback_slowdown=1.5, samples_per_step=32)
     simulation.install(sim, c, "gpt-6.7b")
     sim.simulate_step_delta()
-    assert sim.step_delta == 2121.7 and sim.fallback_slowdown == pytest.approx(1.54, rel=1e-2) and sim.samples_per_step == 128
+    assert sim.step_delta == 2122 and sim.fallback_slowdown == pytest.approx(1.54, rel=1e-2) and sim.samples_per_step == 128
     sim.num_pipelines = 3
     with pytest.raises(NotImplementedError):
         sim.simulate_step_delta()
+
+
+def test_prediction_for_grids_that_were_not_measured():
+    from bamboo_b200 import simulation
+    c = simulation.constants_from_bench([_line("pp4", 152.0), _line("pp8", 92.0), _line("pp2", 300.0), _line("pp2dp2", 306.0)])
+    assert c["micro_batches"]["gpt2-medium"][(1, 4)] == 16
+    assert simulation.predict_step_ms(c, "gpt2-medium", 1, 4) == 152.0                      # measured
+    slot = 152.0 / 19
+    assert simulation.predict_step_ms(c, "gpt2-medium", 2, 4) == pytest.approx(slot * (8 + 3) * 1.02)
+    assert simulation.predict_step_ms(c, "gpt2-medium", 3, 8) == pytest.approx(92.0 / 23 * (6 + 7) * 1.02)
+    assert simulation.predict_step_ms(c, "gpt2-medium", 2, 12) is None                      # no 12-stage run to scale from
+
+
+REFERENCE_SIMULATOR = "/root/reference/project_pactum/simulation/simulator.py"
+
+
+@pytest.mark.skipif(not __import__("os").path.exists(REFERENCE_SIMULATOR), reason="reference checkout not present")
+def test_reference_simulator_runs_on_measured_step_times():
+    """The reference's own spot-market simulator, imported in place, replays a day with this implementation's numbers."""
+    from bamboo_b200 import simulation
+    lines = [_line("pp4", 152.0, failover={"post_failover_step_s": 0.2316, "normal_step_s": 0.1499, "pause_s": 0.146}),
+             _line("pp8", 93.0), _line("pp2", 300.0), _line("pp2dp2", 306.0)]
+    result, sim = simulation.run_reference_simulator(REFERENCE_SIMULATOR, lines, "gpt2-medium", hours=6, seed=3, stages_target=4,
+                                                     capacity=16, removal_probability=0.05)
+    assert sim.num_stages_target == 4 and sim.samples_per_step == 128
+    assert sim.fallback_slowdown == pytest.approx(0.2316 / 0.1499)
+    assert result.num_steps_complete > 1000                                 # 6 h at ~0.1-0.15 s per step, minus rendezvous time
+    assert result.average_performance > 0 and result.average_cost > 0
+    # the step time in force at the end is one of ours (measured 4-stage value or a prediction from it)
+    assert 0 < sim.step_delta <= 152
