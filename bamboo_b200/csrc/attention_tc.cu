@@ -886,11 +886,14 @@ attn_tc_dq_convert_kernel(const TcParams p) {
 //   S_g(jj) = Q_g K_jj^T  ->  P_g = exp2(S_g * c - m_g)  ->  PV_g(jj) = P_g V_jj
 // Scores are double-buffered in tensor memory and issued two sub-blocks ahead, so a group never
 // waits for the tensor core between sub-blocks; P goes through shared memory (bf16, two buffers
-// per group); every P V product lands in its own TMEM buffer (two per group, alternating) and is
-// added to the output row held in registers, so the running-maximum rescale never touches
-// tensor memory.
+// per group).  The output row accumulates in tensor memory over all sub-blocks (O_g += P_g V_jj);
+// the exponent reference of a row only moves when the running maximum has grown by more than 2^8
+// since it was set, and only then is the row's accumulator rescaled (tensor memory -> registers ->
+// tensor memory, between two P V products): after the first few sub-blocks that is rare, and the
+// per-sub-block work of a thread is the softmax alone.  P <= 2^8 and the row sums stay far inside
+// fp32 / bf16 range; the final division by the row sum makes the choice of reference immaterial.
 // smem: Q_0, Q_1 [128 x 64] | K, V sub-tiles [64 x 64] x NKV stages | P_g,b [128 x 64] x 4
-// TMEM: S_g,b at 128 g + 64 b | PV_g,b at 256 + 128 g + 64 b
+// TMEM: S_g,b at 128 g + 64 b | O_g at 256 + 128 g
 constexpr int NKV = 6;
 constexpr int FWD2_THREADS = 320;
 constexpr int FWD2_SMEM = 2 * TILE_BYTES + 2 * NKV * SUB_BYTES + 4 * TILE_BYTES + (int)sizeof(Ctl) + 1024;
@@ -1000,10 +1003,10 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         bb::tc_fence_after_sync();
         if (lane == 0) {
           if (more) issue_scores(g, jj + 2);               // first: the group's next-but-one scores
-          const uint32_t tPV = tmem + 256 + 128 * g + 64 * (jj & 1);
+          const uint32_t tO = tmem + 256 + 128 * g;
           const uint64_t dPg = dP0 + (uint64_t)((2 * g + (jj & 1)) * (TILE_BYTES >> 4));
 #pragma unroll
-          for (int k = 0; k < 4; ++k) bb::umma_f16(tPV, desc_kmajor(dPg, k), desc_mnmajor64(dV, k), i_pv, k > 0);
+          for (int k = 0; k < 4; ++k) bb::umma_f16(tO, desc_kmajor(dPg, k), desc_mnmajor64(dV, k), i_pv, (jj > 0 || k > 0));
           bb::umma_commit(&pv_full[g]);
         }
         __syncwarp();
@@ -1019,13 +1022,11 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const int qrow = q0 + row;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const uint32_t tS = tmem + 128 * g + lane_addr;
-    const uint32_t tPV = tmem + 256 + 128 * g + lane_addr;
+    const uint32_t tO = tmem + 256 + 128 * g + lane_addr;
     const float sl = p.scale * LOG2E;
     const int lastj = BB_LAST(g);
-    float o[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) o[i] = 0.f;
-    float m_i = -INFINITY, l_i = 0.f;
+    constexpr float REF_SLACK = 8.f;                         // log2 units the maximum may grow past the reference
+    float m_ref = -INFINITY, l_i = 0.f;                     // exponent reference of this row, row sum relative to it
     bool alive = true;
     for (int jj = 0; jj <= lastj; ++jj) {
       const int b = jj & 1;
@@ -1051,50 +1052,56 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         }
       }
       mx *= sl;                                              // scale > 0: the maximum commutes with it
-      const float m_new = fmaxf(m_i, mx);
-      const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = ex2(m_i - m_safe);
-      m_i = m_new;
-      const float nm = -m_safe;
+      // move the reference only when the maximum outgrew it by more than the slack
+      float alpha = 1.f;
+      if (mx > m_ref + REF_SLACK || (m_ref == -INFINITY && mx > -INFINITY)) {
+        alpha = ex2(m_ref - mx);                             // 0 for the first finite maximum
+        m_ref = mx;
+        l_i *= alpha;
+      }
+      const float nm = (m_ref == -INFINITY) ? 0.f : -m_ref;
       float rs = 0.f;
 #pragma unroll
       for (int i = 0; i < 32; ++i) {                         // exp2(-inf) = 0 covers the masked entries
         sa[i] = ex2(fmaf(sa[i], sl, nm)); sb[i] = ex2(fmaf(sb[i], sl, nm));
         rs += sa[i] + sb[i];
       }
-      l_i = l_i * alpha + rs;
-      // the product that read this P buffer two sub-blocks ago has retired (and so has the last one)
+      l_i += rs;
       if (jj > 0) {
+        // the previous product has retired: its P buffer is free and the accumulator is at rest
         const bool ok = bb::mbar_wait(&pv_full[g], (jj - 1) & 1, &ctl->abort_flag, p.status);
         if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+          // some row of this warp moved its reference: rescale the warp's accumulator rows in place
+          bb::tc_fence_after_sync();
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r[32];
+            bb::tmem_ld_32x32b_x32(tO + 32 * h, r);
+            bb::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            bb::tmem_st_32x32b_x32(tO + 32 * h, r);
+          }
+          bb::tmem_st_wait();
+        }
       }
       atom_store_row64(sP + (2 * g + b) * TILE_BYTES, row, sa, sb);
       bb::tc_fence_before_sync();
       bb::fence_proxy_async();
       __syncwarp();
       if (lane == 0) bb::mbar_arrive(&p_full[g]);
-      // O = (O + P V of the previous sub-block) * alpha, while the tensor core works on this one
-      if (jj > 0) {
-        bb::tc_fence_after_sync();
-        const uint32_t t = tPV + 64 * ((jj - 1) & 1);
-        ld32x2(t, t + 32, sa, sb);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) { o[i] = (o[i] + sa[i]) * alpha; o[32 + i] = (o[32 + i] + sb[i]) * alpha; }
-      }
     }
     if (lastj >= 0) {
       const bool fin = alive && bb::mbar_wait(&pv_full[g], lastj & 1, &ctl->abort_flag, p.status);
       if (__all_sync(0xffffffffu, fin)) {
         bb::tc_fence_after_sync();
-        float pa[32], pb[32];
-        const uint32_t t = tPV + 64 * (lastj & 1);
-        ld32x2(t, t + 32, pa, pb);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) { o[i] += pa[i]; o[32 + i] += pb[i]; }
+        float o[64];
+        ld32x2(tO, tO + 32, o, o + 32);
         if (qrow < p.S) {
           const float inv = l_i > 0.f ? 1.f / l_i : 0.f;
           store_row64(p.out + (long long)(row_base + qrow) * p.stride_o + colq, o, inv);
-          p.lse[((long long)batch * p.H + head) * p.S + qrow] = (l_i > 0.f) ? (m_i + log2f(l_i)) / LOG2E : -INFINITY;
+          p.lse[((long long)batch * p.H + head) * p.S + qrow] = (l_i > 0.f) ? (m_ref + log2f(l_i)) / LOG2E : -INFINITY;
         }
       }
     }
