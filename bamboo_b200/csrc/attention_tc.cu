@@ -895,7 +895,9 @@ attn_tc_dq_convert_kernel(const TcParams p) {
 // smem: Q_0, Q_1 [128 x 64] | K, V sub-tiles [64 x 64] x NKV stages | P_g,b [128 x 64] x 4
 // TMEM: S_g,b at 128 g + 64 b | O_g at 256 + 128 g
 constexpr int NKV = 6;
-constexpr int FWD2_THREADS = 320;
+// warps: 0 TMA, 1 score products, 2 P V products (two issuing threads: the issue path of the small MMAs is the
+// bound, and two instruction streams get about a third more through it than one), 3..10 the two softmax groups
+constexpr int FWD2_THREADS = 96 + 256;
 constexpr int FWD2_SMEM = 2 * TILE_BYTES + 2 * NKV * SUB_BYTES + 4 * TILE_BYTES + (int)sizeof(Ctl) + 1024;
 
 // one row (64 values) of a [128 x 64] bf16 atom
@@ -968,9 +970,9 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
     }
   } else if (warp == 1) {
-    const uint64_t dQ0 = desc_k0(bb::smem_u32(sQ)), dP0 = desc_k0(bb::smem_u32(sP));
-    const uint64_t dK0 = desc_k0(bb::smem_u32(sK)), dVm0 = desc_mn0(bb::smem_u32(sV));   // stage 0; stage s: + s * SUB_BYTES / 16
-    const uint32_t i_s = idesc(64, 0, 0), i_pv = idesc(64, 0, 1);
+    const uint64_t dQ0 = desc_k0(bb::smem_u32(sQ));
+    const uint64_t dK0 = desc_k0(bb::smem_u32(sK));   // stage 0; stage s: + s * SUB_BYTES / 16
+    const uint32_t i_s = idesc(64, 0, 0);
     bool alive = bb::mbar_wait(q_full, 0, &ctl->abort_flag, p.status);
     // scores of sub-block jj for group g into score buffer jj & 1
     auto issue_scores = [&](int g, int jj) {
@@ -990,19 +992,34 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
       __syncwarp();
     }
+    // steady state: the scores two sub-blocks ahead, as soon as the group has read the buffer they go to
+    for (int jj = 0; jj + 2 <= jmax && alive; ++jj) {
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        if (jj + 2 > BB_LAST(g)) continue;
+        // P_g(jj) is in shared memory, and group g is done reading S_g(jj): its buffer is free
+        if (!bb::mbar_wait(&p_full[g], jj & 1, &ctl->abort_flag, p.status)) { alive = false; break; }
+        if (!bb::mbar_wait(&kv_full[(jj + 2) % NKV], ((jj + 2) / NKV) & 1, &ctl->abort_flag, p.status)) { alive = false; break; }
+        bb::tc_fence_after_sync();
+        if (lane == 0) issue_scores(g, jj + 2);
+        __syncwarp();
+      }
+    }
+  } else if (warp == 2) {
+    const uint64_t dP0 = desc_k0(bb::smem_u32(sP)), dVm0 = desc_mn0(bb::smem_u32(sV));   // stage 0; stage s: + s * SUB_BYTES / 16
+    const uint32_t i_pv = idesc(64, 0, 1);
+    bool alive = true;
     for (int jj = 0; jj <= jmax && alive; ++jj) {
       const int s = jj % NKV;
       const uint64_t dV = dVm0 + (uint64_t)(s * (SUB_BYTES >> 4));
+      // (V_jj landed before the scores of this sub-block were issued; the wait makes it visible to this thread)
+      if (!bb::mbar_wait(&kv_full[s], (jj / NKV) & 1, &ctl->abort_flag, p.status)) break;
 #pragma unroll
       for (int g = 0; g < 2; ++g) {
         if (jj > BB_LAST(g)) continue;
-        // P_g(jj) is in shared memory, and group g is done reading S_g(jj): its buffer is free
         if (!bb::mbar_wait(&p_full[g], jj & 1, &ctl->abort_flag, p.status)) { alive = false; break; }
-        const bool more = (jj + 2 <= BB_LAST(g));
-        if (more && !bb::mbar_wait(&kv_full[(jj + 2) % NKV], ((jj + 2) / NKV) & 1, &ctl->abort_flag, p.status)) { alive = false; break; }
         bb::tc_fence_after_sync();
         if (lane == 0) {
-          if (more) issue_scores(g, jj + 2);               // first: the group's next-but-one scores
           const uint32_t tO = tmem + 256 + 128 * g;
           const uint64_t dPg = dP0 + (uint64_t)((2 * g + (jj & 1)) * (TILE_BYTES >> 4));
 #pragma unroll
@@ -1011,11 +1028,12 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         }
         __syncwarp();
       }
-      if (alive && lane == 0) bb::umma_commit(&kv_empty[s]);      // K_jj, V_jj: every product that reads them is issued
+      // K_jj, V_jj: the score products that read K_jj retired before P(jj) existed, the P V products are issued
+      if (alive && lane == 0) bb::umma_commit(&kv_empty[s]);
       __syncwarp();
     }
-  } else {
-    const int g = (warp - 2) >> 2;
+  } else if (warp >= 3) {
+    const int g = (warp - 3) >> 2;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const int q0 = g ? qb : qa;
