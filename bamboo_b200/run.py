@@ -292,6 +292,8 @@ class NodeAgent:
             os.makedirs(self.config.log_dir, exist_ok=True)
             out = open(os.path.join(self.config.log_dir, f"{self.config.run_id}_rank{rank}_attempt{restart_count}_{self.rounds}.log"), "w")
         self._proc = subprocess.Popen([self.cmd] + self.cmd_args, env=env, stdout=out, stderr=subprocess.STDOUT if out else None)
+        if out is not None:
+            out.close()                                  # the child holds its own descriptor
         if self._draining:
             self._drain()
 
