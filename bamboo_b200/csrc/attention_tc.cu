@@ -7,12 +7,15 @@
 // nothing is transposed.  Probabilities are recomputed from the saved log-sum-exp in the
 // backward pass; scores never reach HBM.
 //
-// In every kernel warp 0 issues TMA, warp 1 issues MMAs and the remaining warps (one TMEM lane
-// quarter each) do the softmax / element-wise work and the final stores.  Three kernels:
-//   forward : CTA owns 256 query rows as two tiles in ping-pong (one compute group per tile);
-//   dQ      : CTA owns 128 query rows, streams 64-row key/value sub-tiles;
-//   dK, dV  : CTA owns 128 key rows, streams 64-row query / dO sub-tiles;
-// the backward split keeps every sum in a fixed order (no atomics).
+// In every kernel warp 0 issues TMA, one or two warps issue MMAs and the remaining warps (one TMEM
+// lane quarter each) do the softmax / element-wise work and the final stores.  Kernels:
+//   forward          : CTA owns 256 query rows as two tiles in ping-pong (one softmax group per tile),
+//                      the output row accumulates in tensor memory;
+//   fused backward   : CTA owns 128 key rows, streams 64-row query / dO sub-tiles, computes the scores
+//                      once and produces dK, dV (fixed summation order) and dQ (fp32 add-reductions
+//                      into an accumulator that a small kernel scales and converts);
+//   two-role backward: dK/dV CTAs and dQ CTAs in one launch, scores computed by both roles, every
+//                      sum in a fixed order (no reductions) - selected by BB_ATTENTION_BWD=split.
 #include "tma_host.cuh"
 #include <math.h>
 #include <stdlib.h>
