@@ -1,8 +1,10 @@
 // HBM-bound row-wise kernels of a transformer stage: LayerNorm forward/backward (with the
-// residual gradient folded in), bias-gradient column sums, token+position embedding
-// gather and its gradient scatter.  All loads/stores are 16-byte vectors; one warp owns a
-// row so no block-level synchronisation is needed on the hot loops; grids are sized as a
-// multiple of the SM count and stride over rows.
+// residual gradient folded in, and optionally its column sums), bias-gradient column sums, token+position
+// embedding gather and its gradient scatter.  All loads/stores are 8- or 16-byte vectors.  Forward and
+// embedding kernels: one warp owns a row, no block-level synchronisation.  LayerNorm backward for hidden
+// sizes that are multiples of 256: a thread owns a few columns of a row slot and keeps their column sums in
+// registers (one block barrier per iteration combines the row sums); other sizes: one warp per row.  Grids are
+// sized as a multiple of the SM count and stride over rows.
 #include "common.cuh"
 #include <stdio.h>
 #include <stdlib.h>
