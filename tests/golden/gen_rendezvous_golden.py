@@ -35,4 +35,7 @@ def main(reference_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("BAMBOO_REFERENCE")
+    if not root:
+        sys.exit(f"usage: {os.path.basename(__file__)} <path of the reference checkout>  (or set BAMBOO_REFERENCE)")
+    main(root)

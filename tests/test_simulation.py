@@ -50,10 +50,15 @@ def test_prediction_for_grids_that_were_not_measured():
     assert simulation.predict_step_ms(c, "gpt2-medium", 2, 12) is None                      # no 12-stage run to scale from
 
 
-REFERENCE_SIMULATOR = "/root/reference/project_pactum/simulation/simulator.py"
+# the reference checkout, when it lies beside this repository (or where BAMBOO_REFERENCE points)
+import os as _os  # noqa: E402
+
+_REFERENCE = _os.environ.get("BAMBOO_REFERENCE") or _os.path.join(
+    _os.path.dirname(_os.path.dirname(_os.path.dirname(_os.path.abspath(__file__)))), "reference")
+REFERENCE_SIMULATOR = _os.path.join(_REFERENCE, "project_pactum", "simulation", "simulator.py")
 
 
-@pytest.mark.skipif(not __import__("os").path.exists(REFERENCE_SIMULATOR), reason="reference checkout not present")
+@pytest.mark.skipif(not _os.path.exists(REFERENCE_SIMULATOR), reason="reference checkout not present")
 def test_reference_simulator_runs_on_measured_step_times():
     """The reference's own spot-market simulator, imported in place, replays a day with this implementation's numbers."""
     from bamboo_b200 import simulation
