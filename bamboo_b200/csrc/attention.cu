@@ -468,25 +468,26 @@ bool bad_layout(long long stride, int D, const void* a, const void* b, const voi
 
 }  // namespace
 
-// tcgen05 kernels for head dimension 64 (attention_tc.cu)
-int bb_attention_tc_fwd(const void* qkv_q, void* out, float* lse, int B, int H, int S, long long stride_qkv, long long stride_o,
-                        int causal, float scale, cudaStream_t stream);
+// tcgen05 kernels (attention_tc.cu): forward for head dimensions 64 and 128, backward for 64
+int bb_attention_tc_fwd(const void* qkv_q, void* out, float* lse, int B, int H, int S, int D, long long stride_qkv,
+                        long long stride_o, int causal, float scale, cudaStream_t stream);
 int bb_attention_tc_bwd(const void* qkv_q, const void* out, const void* d_out, const float* lse, void* dq, void* dk, void* dv,
                         float* delta, float* dq_acc, int B, int H, int S, long long stride_qkv, long long stride_o,
                         long long stride_dqkv, int causal, float scale, cudaStream_t stream);
 
 namespace {
 // The tcgen05 kernels (attention_tc.cu) read q, k, v through one tensor map over the packed
-// projection [tokens, 3*H*64] and are the default for head dimension 64.  Measured on B200 (B8 H16
-// S1024 causal): forward 70 us, backward 180 us, against 120 us and 593 us for the warp-level
-// kernels above.  BB_ATTENTION_IMPL=mma in the environment forces the warp-level kernels.
-bool use_tc_path(const void* q, const void* k, const void* v, int H, int D, long long stride_qkv) {
+// projection [tokens, 3*H*D] and are the default for head dimension 64 (forward and backward) and
+// for the forward pass at head dimension 128.  Measured on B200 (B8 H16 S1024 D64 causal): forward
+// 70 us, backward 180 us, against 120 us and 593 us for the warp-level kernels above; B2 H32 S2048
+// D128 causal: forward 121 us.  BB_ATTENTION_IMPL=mma in the environment forces the warp-level kernels.
+bool use_tc_path(const void* q, const void* k, const void* v, int H, int D, long long stride_qkv, bool forward) {
   static int mode = -1;   // 0 = tcgen05 kernels where they apply (default), 2 = warp-level kernels only
   if (mode < 0) {
     const char* e = getenv("BB_ATTENTION_IMPL");
     mode = (e && e[0] == 'm') ? 2 : 0;
   }
-  if (D != 64 || mode == 2) return false;
+  if (mode == 2 || !(D == 64 || (D == 128 && forward))) return false;
   // the tcgen05 kernels address q, k and v through one tensor map over the packed projection
   const long long hb = (long long)H * D * 2;
   return (const char*)k - (const char*)q == hb && (const char*)v - (const char*)q == 2 * hb && stride_qkv >= 3LL * H * D &&
@@ -504,8 +505,8 @@ extern "C" int bb_attention_fwd(const void* q, const void* k, const void* v, voi
   AttnParams p = {};
   p.q = (const __nv_bfloat16*)q; p.k = (const __nv_bfloat16*)k; p.v = (const __nv_bfloat16*)v; p.out = (__nv_bfloat16*)out;
   p.lse = lse; p.stride_qkv = stride_qkv; p.stride_o = stride_o; p.B = B; p.H = H; p.S = S; p.causal = causal; p.scale = scale;
-  if (use_tc_path(q, k, v, H, D, stride_qkv))
-    return bb_attention_tc_fwd(q, out, lse, B, H, S, stride_qkv, stride_o, causal, scale, (cudaStream_t)stream);
+  if (use_tc_path(q, k, v, H, D, stride_qkv, true))
+    return bb_attention_tc_fwd(q, out, lse, B, H, S, D, stride_qkv, stride_o, causal, scale, (cudaStream_t)stream);
   if (D == 64) return launch_fwd<64>(p, (cudaStream_t)stream);
   if (D == 128) return launch_fwd<128>(p, (cudaStream_t)stream);
   bb_set_last_error_msg("bb_attention_fwd: head dimension must be 64 or 128");
@@ -544,7 +545,7 @@ extern "C" int bb_attention_bwd(const void* q, const void* k, const void* v, con
   p.lse = const_cast<float*>(lse); p.delta = (float*)workspace;
   p.stride_qkv = stride_qkv; p.stride_o = stride_o; p.stride_dqkv = stride_dqkv;
   p.B = B; p.H = H; p.S = S; p.causal = causal; p.scale = scale;
-  if (use_tc_path(q, k, v, H, D, stride_qkv))
+  if (use_tc_path(q, k, v, H, D, stride_qkv, false))
     return bb_attention_tc_bwd(q, out, d_out, lse, dq, dk, dv, (float*)workspace,
                                (float*)((char*)workspace + attn_ws_delta_bytes(B, H, S)), B, H, S, stride_qkv, stride_o,
                                stride_dqkv, causal, scale, (cudaStream_t)stream);

@@ -1,4 +1,4 @@
-// Fused attention for head dimension 64 on the 5th-generation tensor cores.
+// Fused attention on the 5th-generation tensor cores: head dimension 64 (forward and backward) and 128 (forward).
 //
 // Every contraction (Q.K^T, P.V, dO.V^T, dS.K, P^T.dO, dS^T.Q) is a tcgen05.mma with fp32
 // accumulators in tensor memory; tiles arrive by TMA into 128-byte-swizzled shared memory;
@@ -10,7 +10,7 @@
 // In every kernel warp 0 issues TMA, one or two warps issue MMAs and the remaining warps (one TMEM
 // lane quarter each) do the softmax / element-wise work and the final stores.  Kernels:
 //   forward          : CTA owns 256 query rows as two tiles in ping-pong (one softmax group per tile),
-//                      the output row accumulates in tensor memory;
+//                      the output row accumulates in tensor memory; templated on the head dimension;
 //   fused backward   : CTA owns 128 key rows, streams 64-row query / dO sub-tiles, computes the scores
 //                      once and produces dK, dV (fixed summation order) and dQ (fp32 add-reductions
 //                      into an accumulator that a small kernel scales and converts);
@@ -895,13 +895,23 @@ attn_tc_dq_convert_kernel(const TcParams p) {
 // tensor memory, between two P V products): after the first few sub-blocks that is rare, and the
 // per-sub-block work of a thread is the softmax alone.  P <= 2^8 and the row sums stay far inside
 // fp32 / bf16 range; the final division by the row sum makes the choice of reference immaterial.
-// smem: Q_0, Q_1 [128 x 64] | K, V sub-tiles [64 x 64] x NKV stages | P_g,b [128 x 64] x 4
-// TMEM: S_g,b at 128 g + 64 b | O_g at 256 + 128 g
-constexpr int NKV = 6;
+// smem: Q_0, Q_1 [128 x D] | K, V sub-tiles [64 x D] x NKV stages | P_g,b [128 x 64] x 4
+// TMEM: S_g,b at 128 g + 64 b | O_g at 256 + 128 g (D columns)
+// Head dimension D = 64 or 128.  A [rows x 128] operand lies in shared memory as two [rows x 64] atoms of
+// 128-byte rows, one after the other (two TMA boxes): the score product walks its eight 16-column k-steps
+// through both atoms; V as the B operand of P V (N = D, its columns) names the distance between the atoms in
+// the descriptor's leading-dimension field.  The whole tensor memory is in use at D = 128 (2 x 2 score
+// buffers of 64 columns, 2 outputs of 128), and the sub-tile ring is 3 deep instead of 6.
+template <int D> struct Fwd2 {
+  static constexpr int NA = D / 64;                            // 64-column atoms per row
+  static constexpr int NKV = (D == 64) ? 6 : 3;                // sub-tile ring depth
+  static constexpr int Q_BYTES = NA * TILE_BYTES;              // one query tile
+  static constexpr int KV_BYTES = NA * SUB_BYTES;              // one key (or value) sub-tile
+  static constexpr int SMEM = 2 * Q_BYTES + 2 * NKV * KV_BYTES + 4 * TILE_BYTES + (int)sizeof(Ctl) + 1024;
+};
 // warps: 0 TMA, 1 score products, 2 P V products (two issuing threads: the issue path of the small MMAs is the
 // bound, and two instruction streams get about a third more through it than one), 3..10 the two softmax groups
 constexpr int FWD2_THREADS = 96 + 256;
-constexpr int FWD2_SMEM = 2 * TILE_BYTES + 2 * NKV * SUB_BYTES + 4 * TILE_BYTES + (int)sizeof(Ctl) + 1024;
 
 // one row (64 values) of a [128 x 64] bf16 atom
 __device__ __forceinline__ void atom_store_row64(uint8_t* atom, int row, const float* a /*32*/, const float* b /*32*/) {
@@ -916,14 +926,17 @@ __device__ __forceinline__ void atom_store_row64(uint8_t* atom, int row, const f
   }
 }
 
+template <int D>
 __global__ void __launch_bounds__(FWD2_THREADS, 1)
 attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv, const TcParams p) {
+  using C = Fwd2<D>;
+  constexpr int NA = C::NA, NKV = C::NKV, Q_BYTES = C::Q_BYTES, KV_BYTES = C::KV_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;                          // 2 tiles
-  uint8_t* sK = sQ + 2 * TILE_BYTES;           // NKV sub-tiles
-  uint8_t* sV = sK + NKV * SUB_BYTES;          // NKV sub-tiles
-  uint8_t* sP = sV + NKV * SUB_BYTES;          // [group][buffer] x 16 KiB
+  uint8_t* sK = sQ + 2 * Q_BYTES;              // NKV sub-tiles
+  uint8_t* sV = sK + NKV * KV_BYTES;           // NKV sub-tiles
+  uint8_t* sP = sV + NKV * KV_BYTES;           // [group][buffer] x 16 KiB
   Ctl* ctl = reinterpret_cast<Ctl*>(sP + 4 * TILE_BYTES);
   uint64_t* q_full = &ctl->bars[0];
   uint64_t* kv_full = &ctl->bars[1];           // [NKV]
@@ -931,11 +944,15 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   uint64_t* s_full = &ctl->bars[1 + 2 * NKV];  // [group][buffer] scores ready
   uint64_t* p_full = s_full + 4;               // [group] probabilities in shared memory, scores read
   uint64_t* pv_full = p_full + 2;              // [group] P V product ready
+  // [group][buffer] the group is done with the scores in this buffer.  Completes at the same moment as p_full, but
+  // per buffer: its next phase needs the next score product into the buffer, which only the waiter issues, so
+  // the waiter can never find it two phases on (p_full can be: the other issuing warp moves that one along)
+  uint64_t* s_free = pv_full + 2;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cb = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, batch = blockIdx.z;   // long CTAs first
   const int row_base = batch * p.S;
-  const int colq = head * HD, colk = p.hidden + head * HD, colv = 2 * p.hidden + head * HD;
+  const int colq = head * D, colk = p.hidden + head * D, colv = 2 * p.hidden + head * D;
   const int nsub = (p.S + SUB - 1) / SUB;
   // last key sub-block of each query tile (-1: the tile lies past the end of the sequence)
   const int qa = cb * 2 * TQ, qb = qa + TQ;
@@ -948,7 +965,7 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     ctl->abort_flag = 0;
     bb::mbar_init(q_full, 1);
     for (int i = 0; i < NKV; ++i) { bb::mbar_init(&kv_full[i], 1); bb::mbar_init(&kv_empty[i], 1); }
-    for (int i = 0; i < 4; ++i) bb::mbar_init(&s_full[i], 1);
+    for (int i = 0; i < 4; ++i) { bb::mbar_init(&s_full[i], 1); bb::mbar_init(&s_free[i], 4); }
     for (int g = 0; g < 2; ++g) { bb::mbar_init(&p_full[g], 4); bb::mbar_init(&pv_full[g], 1); }
     bb::fence_barrier_init();
     bb::tma_prefetch_desc(&tm_q); bb::tma_prefetch_desc(&tm_kv);
@@ -961,28 +978,36 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
   if (warp == 0) {
     if (lane == 0) {
-      bb::mbar_arrive_expect_tx(q_full, 2 * TILE_BYTES);
-      bb::tma_load_2d(sQ, &tm_q, q_full, colq, row_base + qa);
-      bb::tma_load_2d(sQ + TILE_BYTES, &tm_q, q_full, colq, row_base + qb);
+      bb::mbar_arrive_expect_tx(q_full, 2 * Q_BYTES);
+#pragma unroll
+      for (int a = 0; a < NA; ++a) {
+        bb::tma_load_2d(sQ + a * TILE_BYTES, &tm_q, q_full, colq + 64 * a, row_base + qa);
+        bb::tma_load_2d(sQ + Q_BYTES + a * TILE_BYTES, &tm_q, q_full, colq + 64 * a, row_base + qb);
+      }
       for (int jj = 0; jj <= jmax; ++jj) {
         const int s = jj % NKV;
         if (!bb::mbar_wait(&kv_empty[s], ((jj / NKV) & 1) ^ 1, &ctl->abort_flag, p.status)) break;
-        bb::mbar_arrive_expect_tx(&kv_full[s], 2 * SUB_BYTES);
-        bb::tma_load_2d(sK + s * SUB_BYTES, &tm_kv, &kv_full[s], colk, row_base + jj * SUB);
-        bb::tma_load_2d(sV + s * SUB_BYTES, &tm_kv, &kv_full[s], colv, row_base + jj * SUB);
+        bb::mbar_arrive_expect_tx(&kv_full[s], 2 * KV_BYTES);
+#pragma unroll
+        for (int a = 0; a < NA; ++a) {
+          bb::tma_load_2d(sK + s * KV_BYTES + a * SUB_BYTES, &tm_kv, &kv_full[s], colk + 64 * a, row_base + jj * SUB);
+          bb::tma_load_2d(sV + s * KV_BYTES + a * SUB_BYTES, &tm_kv, &kv_full[s], colv + 64 * a, row_base + jj * SUB);
+        }
       }
     }
   } else if (warp == 1) {
     const uint64_t dQ0 = desc_k0(bb::smem_u32(sQ));
-    const uint64_t dK0 = desc_k0(bb::smem_u32(sK));   // stage 0; stage s: + s * SUB_BYTES / 16
+    const uint64_t dK0 = desc_k0(bb::smem_u32(sK));   // stage 0; stage s: + s * KV_BYTES / 16
     const uint32_t i_s = idesc(64, 0, 0);
     bool alive = bb::mbar_wait(q_full, 0, &ctl->abort_flag, p.status);
     // scores of sub-block jj for group g into score buffer jj & 1
     auto issue_scores = [&](int g, int jj) {
-      const uint64_t dK = dK0 + (uint64_t)((jj % NKV) * (SUB_BYTES >> 4)), dQ = dQ0 + (uint64_t)(g * (TILE_BYTES >> 4));
+      const uint64_t dK = dK0 + (uint64_t)((jj % NKV) * (KV_BYTES >> 4)), dQ = dQ0 + (uint64_t)(g * (Q_BYTES >> 4));
       const uint32_t tS = tmem + 128 * g + 64 * (jj & 1);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) bb::umma_f16(tS, desc_kmajor(dQ, k), desc_kmajor(dK, k), i_s, k > 0);
+      for (int k = 0; k < D / 16; ++k)           // four k-steps per 64-column atom
+        bb::umma_f16(tS, desc_kmajor(dQ + (uint64_t)((k >> 2) * (TILE_BYTES >> 4)), k & 3),
+                     desc_kmajor(dK + (uint64_t)((k >> 2) * (SUB_BYTES >> 4)), k & 3), i_s, k > 0);
       bb::umma_commit(&s_full[2 * g + (jj & 1)]);
     };
     // prologue: the first two score products of each group
@@ -1000,8 +1025,8 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
       for (int g = 0; g < 2; ++g) {
         if (jj + 2 > BB_LAST(g)) continue;
-        // P_g(jj) is in shared memory, and group g is done reading S_g(jj): its buffer is free
-        if (!bb::mbar_wait(&p_full[g], jj & 1, &ctl->abort_flag, p.status)) { alive = false; break; }
+        // group g is done reading S_g(jj): its buffer is free
+        if (!bb::mbar_wait(&s_free[2 * g + (jj & 1)], (jj >> 1) & 1, &ctl->abort_flag, p.status)) { alive = false; break; }
         if (!bb::mbar_wait(&kv_full[(jj + 2) % NKV], ((jj + 2) / NKV) & 1, &ctl->abort_flag, p.status)) { alive = false; break; }
         bb::tc_fence_after_sync();
         if (lane == 0) issue_scores(g, jj + 2);
@@ -1009,12 +1034,14 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
     }
   } else if (warp == 2) {
-    const uint64_t dP0 = desc_k0(bb::smem_u32(sP)), dVm0 = desc_mn0(bb::smem_u32(sV));   // stage 0; stage s: + s * SUB_BYTES / 16
-    const uint32_t i_pv = idesc(64, 0, 1);
+    // V: [64 keys x D]; its atoms (64 columns each) lie SUB_BYTES apart, which is desc_mn0's leading-dimension field
+    static_assert(SUB_BYTES == 8192, "desc_mn0 names the distance between the 64-column atoms of V");
+    const uint64_t dP0 = desc_k0(bb::smem_u32(sP)), dVm0 = desc_mn0(bb::smem_u32(sV));   // stage 0; stage s: + s * KV_BYTES / 16
+    const uint32_t i_pv = idesc(D, 0, 1);
     bool alive = true;
     for (int jj = 0; jj <= jmax && alive; ++jj) {
       const int s = jj % NKV;
-      const uint64_t dV = dVm0 + (uint64_t)(s * (SUB_BYTES >> 4));
+      const uint64_t dV = dVm0 + (uint64_t)(s * (KV_BYTES >> 4));
       // (V_jj landed before the scores of this sub-block were issued; the wait makes it visible to this thread)
       if (!bb::mbar_wait(&kv_full[s], (jj / NKV) & 1, &ctl->abort_flag, p.status)) break;
 #pragma unroll
@@ -1096,7 +1123,7 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           // some row of this warp moved its reference: rescale the warp's accumulator rows in place
           bb::tc_fence_after_sync();
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
+          for (int h = 0; h < D / 32; ++h) {
             uint32_t r[32];
             bb::tmem_ld_32x32b_x32(tO + 32 * h, r);
             bb::tmem_ld_wait();
@@ -1111,17 +1138,20 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       bb::tc_fence_before_sync();
       bb::fence_proxy_async();
       __syncwarp();
-      if (lane == 0) bb::mbar_arrive(&p_full[g]);
+      if (lane == 0) { bb::mbar_arrive(&p_full[g]); bb::mbar_arrive(&s_free[2 * g + b]); }
     }
     if (lastj >= 0) {
       const bool fin = alive && bb::mbar_wait(&pv_full[g], lastj & 1, &ctl->abort_flag, p.status);
       if (__all_sync(0xffffffffu, fin)) {
         bb::tc_fence_after_sync();
-        float o[64];
-        ld32x2(tO, tO + 32, o, o + 32);
+        const float inv = l_i > 0.f ? 1.f / l_i : 0.f;
+#pragma unroll
+        for (int a = 0; a < NA; ++a) {
+          float o[64];
+          ld32x2(tO + 64 * a, tO + 64 * a + 32, o, o + 32);
+          if (qrow < p.S) store_row64(p.out + (long long)(row_base + qrow) * p.stride_o + colq + 64 * a, o, inv);
+        }
         if (qrow < p.S) {
-          const float inv = l_i > 0.f ? 1.f / l_i : 0.f;
-          store_row64(p.out + (long long)(row_base + qrow) * p.stride_o + colq, o, inv);
           p.lse[((long long)batch * p.H + head) * p.S + qrow] = (l_i > 0.f) ? (m_ref + log2f(l_i)) / LOG2E : -INFINITY;
         }
       }
@@ -1141,24 +1171,34 @@ template <typename K> int set_smem(K kernel, int bytes) {
 
 }  // namespace
 
-// Entry points used by attention.cu's dispatch when the head dimension is 64.
-int bb_attention_tc_fwd(const void* qkv_q, void* out, float* lse, int B, int H, int S, long long stride_qkv, long long stride_o,
-                        int causal, float scale, cudaStream_t stream) {
-  if (int rc = bbhost::bind_context()) return rc;
+// Entry points used by attention.cu's dispatch: forward for head dimensions 64 and 128, backward for 64.
+namespace {
+template <int D>
+int launch_fwd2(const void* qkv_q, void* out, float* lse, int B, int H, int S, long long stride_qkv, long long stride_o,
+                int causal, float scale, cudaStream_t stream) {
   CUtensorMap tm_q, tm_kv;
   const long long T = (long long)B * S;
-  // the packed projection [T, 3*H*64]: q, k, v blocks of H*64 columns each; 128-row boxes for
-  // the query tiles, 64-row boxes for the streamed key/value sub-tiles
-  if (int rc = bbhost::encode_2d(&tm_q, qkv_q, T, 3LL * H * HD, stride_qkv, HD, TQ)) return rc;
-  if (int rc = bbhost::encode_2d(&tm_kv, qkv_q, T, 3LL * H * HD, stride_qkv, HD, SUB)) return rc;
+  // the packed projection [T, 3*H*D]: q, k, v blocks of H*D columns each; boxes of 64 columns (one
+  // 128-byte swizzle atom), 128 rows for the query tiles, 64 rows for the streamed key/value sub-tiles
+  if (int rc = bbhost::encode_2d(&tm_q, qkv_q, T, 3LL * H * D, stride_qkv, 64, TQ)) return rc;
+  if (int rc = bbhost::encode_2d(&tm_kv, qkv_q, T, 3LL * H * D, stride_qkv, 64, SUB)) return rc;
   TcParams p = {};
-  p.out = (__nv_bfloat16*)out; p.lse = lse; p.stride_o = stride_o; p.B = B; p.H = H; p.S = S; p.hidden = H * HD;
+  p.out = (__nv_bfloat16*)out; p.lse = lse; p.stride_o = stride_o; p.B = B; p.H = H; p.S = S; p.hidden = H * D;
   p.causal = causal; p.scale = scale; p.status = bb_device_status_word();
-  BB_ONCE_PER_DEVICE({ if (int rc = set_smem(attn_tc_fwd2_kernel, FWD2_SMEM)) return rc; });
+  BB_ONCE_PER_DEVICE({ if (int rc = set_smem(attn_tc_fwd2_kernel<D>, Fwd2<D>::SMEM)) return rc; });
   dim3 grid((S + 2 * TQ - 1) / (2 * TQ), H, B);
-  attn_tc_fwd2_kernel<<<grid, FWD2_THREADS, FWD2_SMEM, stream>>>(tm_q, tm_kv, p);
+  attn_tc_fwd2_kernel<D><<<grid, FWD2_THREADS, Fwd2<D>::SMEM, stream>>>(tm_q, tm_kv, p);
   BB_CUDA_CHECK(cudaGetLastError());
   return BB_OK;
+}
+}  // namespace
+
+int bb_attention_tc_fwd(const void* qkv_q, void* out, float* lse, int B, int H, int S, int D, long long stride_qkv,
+                        long long stride_o, int causal, float scale, cudaStream_t stream) {
+  if (int rc = bbhost::bind_context()) return rc;
+  if (D == 64) return launch_fwd2<64>(qkv_q, out, lse, B, H, S, stride_qkv, stride_o, causal, scale, stream);
+  if (D == 128) return launch_fwd2<128>(qkv_q, out, lse, B, H, S, stride_qkv, stride_o, causal, scale, stream);
+  return BB_ERR_UNSUPPORTED;
 }
 
 int bb_attention_tc_bwd(const void* qkv_q, const void* out, const void* d_out, const float* lse, void* dq, void* dk, void* dv,

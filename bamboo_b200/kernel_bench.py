@@ -42,7 +42,8 @@ def _graph_us(fn, sets, passes=3, replays=10):
 
 
 def attention():
-    for (B, H, S, D, causal) in [(8, 16, 1024, 64, True), (8, 16, 1024, 64, False), (4, 16, 512, 64, False)]:
+    for (B, H, S, D, causal) in [(8, 16, 1024, 64, True), (8, 16, 1024, 64, False), (4, 16, 512, 64, False),
+                                 (2, 32, 2048, 128, True)]:
         sets = 4
         qkv = [(torch.randn(B * S, 3 * H * D, device="cuda") * 0.5).bfloat16() for _ in range(sets)]
         out = [torch.empty(B * S, H * D, device="cuda", dtype=torch.bfloat16) for _ in range(sets)]
@@ -58,6 +59,10 @@ def attention():
         for i in range(sets):
             fwd(i)
             bwd(i)
+        torch.cuda.synchronize()
+        if L.read_status() != 0:
+            print(f"attention B{B} H{H} S{S} D{D} causal={causal}: device status {L.read_status()} after the warm-up calls, not timed", flush=True)
+            return
         tf, tb = _events(fwd, 40), _events(bwd, 40)
         half = 0.5 if causal else 1.0
         print(f"attention B{B} H{H} S{S} D{D} causal={causal}: forward {tf:.1f} us ({2 * 2 * B * H * S * S * D * half / tf / 1e6:.0f} TFLOP/s), "

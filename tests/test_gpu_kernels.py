@@ -316,7 +316,11 @@ def _attn_ref(qkv, B, H, S, D, causal):
                                             # an odd number of 64-query sub-blocks (the fused backward pairs them up and
                                             # pads with a masked one that reads the next batch's rows), several key tiles
                                             (2, 2, 192, 64, True), (2, 2, 192, 64, False), (2, 1, 448, 64, True),
-                                            (1, 1, 2048, 64, True), (3, 2, 640, 64, False)])
+                                            (1, 1, 2048, 64, True), (3, 2, 640, 64, False),
+                                            # head dimension 128: tcgen05 forward (two 64-column atoms per row), warp-level backward
+                                            (1, 2, 1024, 128, True), (1, 2, 200, 128, True), (2, 1, 448, 128, False),
+                                            (1, 1, 72, 128, False),
+                                            (1, 16, 2048, 128, True)])     # enough CTAs to keep every SM and the TMA unit busy
 def test_attention(L, B, H, S, D, causal):
     torch.manual_seed(9)
     qkv = torch.randn(B * S, 3 * H * D, device="cuda").bfloat16()
