@@ -20,6 +20,8 @@ One agent runs per node:
    standby / re-form the job") starts over at 1 without using up a restart; any other failure starts over
    while restarts remain; new nodes that wait do NOT restart a healthy worker (the engine re-forms the job
    itself at the next step boundary);
+   On a node with several GPUs one agent runs per GPU, each with ``BAMBOO_AGENT_LOCAL_RANK=<gpu index>`` in
+   its environment (the worker's ``LOCAL_RANK``; default 0, the reference's one-GPU nodes);
 5. SIGTERM to the agent - sent by the operator or by the spot-notice poller - is passed on to the worker,
    whose engine then announces its preemption and leaves between steps.
 """
@@ -203,6 +205,9 @@ class NodeAgent:
         self.config, self.handler, self.cmd, self.cmd_args = config, handler, cmd, list(cmd_args)
         self.extra_env = dict(extra_env or {})
         self.master_addr, self.master_port = master_addr, master_port
+        # one agent per node in the reference (one GPU per node); on a multi-GPU node one agent runs per GPU
+        # and BAMBOO_AGENT_LOCAL_RANK names the GPU of this agent's worker
+        self.local_rank = str(int(os.environ.get("BAMBOO_AGENT_LOCAL_RANK", "0")))
         self._remaining_restarts = config.max_restarts
         self._proc: Optional[subprocess.Popen] = None
         self._draining = False
@@ -264,7 +269,7 @@ class NodeAgent:
 
     def worker_env(self, rank, world, pipelines, stages, coords, master_addr, master_port, restart_count) -> Dict[str, str]:
         env = {
-            "LOCAL_RANK": "0", "RANK": str(rank), "GROUP_RANK": str(rank), "ROLE_RANK": str(rank), "ROLE_NAME": self.config.role,
+            "LOCAL_RANK": self.local_rank, "RANK": str(rank), "GROUP_RANK": str(rank), "ROLE_RANK": str(rank), "ROLE_NAME": self.config.role,
             "LOCAL_WORLD_SIZE": "1", "WORLD_SIZE": str(world), "GROUP_WORLD_SIZE": str(world), "ROLE_WORLD_SIZE": str(world),
             "MASTER_ADDR": master_addr, "MASTER_PORT": str(master_port),
             "TORCHELASTIC_RESTART_COUNT": str(restart_count), "TORCHELASTIC_MAX_RESTARTS": str(self.config.max_restarts),

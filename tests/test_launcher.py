@@ -74,6 +74,13 @@ def test_agent_environment_and_preemption_forwarding(tmp_path):
     assert (env["PROJECT_PACTUM_NUM_PIPELINES"], env["PROJECT_PACTUM_NUM_STAGES"]) == ("1", "1")
     assert json.loads(env["PROJECT_PACTUM_COORDINATES"]) == [[0, 0]]
     assert env["NCCL_ASYNC_ERROR_HANDLING"] == "1" and env["TORCHELASTIC_RUN_ID"] == "solo" and env["PROJECT_PACTUM_ENABLED"] == "1"
+    # several GPUs on a node: one agent per GPU, told which one through its environment
+    os.environ["BAMBOO_AGENT_LOCAL_RANK"] = "5"
+    try:
+        other = run.NodeAgent(config, handler, sys.executable, [], master_addr="127.0.0.1")
+        assert other.worker_env(3, 8, 2, 4, [[1, 1]], "127.0.0.1", 29500, 0)["LOCAL_RANK"] == "5"
+    finally:
+        del os.environ["BAMBOO_AGENT_LOCAL_RANK"]
 
 
 @pytest.mark.parametrize("standby_once", [False, True])
