@@ -706,7 +706,7 @@ class PipelineEngine:
         (reference ``save_shadow_node_state``, ``pipe/engine.py:660-727``).  Every member calls this with the
         same ``failures`` and derives the same plan; returns what this member received."""
         from . import reconfigure as R
-        recv_decisions, send_decisions = {}, {}
+        recv_decisions, send_decisions, seat_updates = {}, {}, []
         for fail_rank, at_step in failures.items():
             if at_step != self.global_steps:
                 continue
@@ -729,13 +729,19 @@ class PipelineEngine:
             send_decisions.setdefault(send_node, {})[recv_node] = layers
             if self.global_rank == recv_node:            # one writer: the update compares on the key's index
                 extended = [list(c) for c in coords[str(recv_node)]] + [[leaving[0][0], s] for s in stages]
-                self.rdzv_handler.update_coordinates_for_version(prev["version"], recv_node, extended)
+                seat_updates.append((prev["version"], recv_node, extended))
         if not recv_decisions:
             return {}
         incoming = set().union(*recv_decisions.get(self.global_rank, {}).values()) if self.global_rank in recv_decisions else set()
         t0 = time.time()
         received = R.transfer_layers(self.dist, self.global_rank, self.world_size, recv_decisions, send_decisions,
                                      self.get_model_state(), self._layer_shapes(incoming), device=self.device)
+        # The seats are extended only now: the plan above is derived from the seats as they were, by every member
+        # on its own, and a sender that read them after the receiver's update would find nothing left to hand over
+        # and leave without sending.  The layers having arrived, the sender has made its plan; and this member joins
+        # the next rendezvous after the update, so the re-partition plan of the next round sees it.
+        for version, node, extended in seat_updates:
+            self.rdzv_handler.update_coordinates_for_version(version, node, extended)
         if received:
             self.log(f"took over layers {sorted(received)} of a leaving member in {time.time() - t0:.3f} s")
         return received
