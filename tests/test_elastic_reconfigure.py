@@ -23,11 +23,14 @@ MB, GAS, LR, STEPS, GROW_AT = 2, 2, 1e-3, 4, 2
 PREFIX, RUN = "/torchelastic/p2p", "elastic"
 
 
-def _waiting(client):
+def _newcomers_wait(client, n):
+    """True once ``n`` newcomers wait on the final round - or the round is already gone or being re-formed: another
+    member saw them first, went on into the step and took the decision."""
     try:
-        return json.loads(client.get(f"{PREFIX}/run_{RUN}/rdzv/active_version").value).get("num_workers_waiting", 0)
+        state = json.loads(client.get(f"{PREFIX}/run_{RUN}/rdzv/active_version").value)
     except Exception:
-        return 0
+        return True
+    return state.get("status") != "final" or state.get("num_workers_waiting", 0) >= n
 
 
 def _member(idx, address, late, queue):
@@ -67,7 +70,7 @@ def _member(idx, address, late, queue):
         while engine.global_steps < STEPS:
             step = engine.global_steps
             if step == GROW_AT and not late and engine.dp_world_size == 1:
-                while _waiting(client) < 2:            # the step at which the job grows is fixed by the test
+                while not _newcomers_wait(client, 2):            # the step at which the job grows is fixed by the test
                     time.sleep(0.05)
             batches = data[step]
             # micro-batches of a step are dealt to the replicas in blocks; a replica learns its id only

@@ -27,6 +27,16 @@ MIDDLE_LEAVES_AT, LOADED_LEAVES_AT = 1, 3
 PREFIX, RUN = "/torchelastic/p2p", "handover"
 
 
+def _newcomers_wait(client, n):
+    """True once ``n`` newcomers wait on the final round - or the round is already gone or being re-formed: another
+    member saw them first, went on into the step and took the decision."""
+    try:
+        state = json.loads(client.get(f"{PREFIX}/run_{RUN}/rdzv/active_version").value)
+    except Exception:
+        return True
+    return state.get("status") != "final" or state.get("num_workers_waiting", 0) >= n
+
+
 def _member(idx, address, late, queue):
     try:
         import fake_etcd
@@ -67,7 +77,7 @@ def _member(idx, address, late, queue):
                 engine.announce_preemption()
             if not late and step == LOADED_LEAVES_AT:
                 # the step at which the job re-forms is fixed by the test: both newcomers are waiting by then
-                while json.loads(client.get(f"{PREFIX}/run_{RUN}/rdzv/active_version").value).get("num_workers_waiting", 0) < 2:
+                while not _newcomers_wait(client, 2):
                     time.sleep(0.05)
             loss = float(engine.train_batch(data_iter=iter(data[step])))
             record.append({"step": step, "stages": list(engine.stage_ids), "loss": loss, "rank": engine.global_rank,
