@@ -23,10 +23,12 @@ What is different underneath:
   there would continue from zeros; here failover continues the same optimisation trajectory.
 """
 import collections
+import contextlib
 import json
 import os
 import signal
 import sys
+import threading
 import time
 from types import MethodType
 from typing import Dict, List, Optional, Tuple
@@ -74,6 +76,7 @@ class LocalStore:
 
     def __init__(self):
         self._d = {}
+        self._add_lock = threading.Lock()
 
     def set(self, key, value):
         self._d[key] = value if isinstance(value, bytes) else str(value).encode()
@@ -83,6 +86,34 @@ class LocalStore:
 
     def check(self, keys):
         return all(k in self._d for k in keys)
+
+    def add(self, key, num):
+        with self._add_lock:
+            value = int(self._d.get(key, b"0")) + int(num)
+            self._d[key] = str(value).encode()
+            return value
+
+
+@contextlib.contextmanager
+def store_mutex(store, name, timeout_s=5.0):
+    """Mutual exclusion between the members of a job through their key/value store: a ticket lock on the
+    store's atomic ``add`` (c10d TCP / file stores, the etcd-backed store and the in-process one all have it).
+    A member that waited ``timeout_s`` for a holder that never released (it died in between) goes ahead anyway
+    and moves the counter past its own ticket, so that the members behind it are served again."""
+    add = getattr(store, "add", None)
+    if add is None:
+        yield
+        return
+    ticket = int(add(f"{name}-ticket", 1))
+    deadline = time.time() + timeout_s
+    while int(add(f"{name}-serving", 0)) < ticket - 1 and time.time() < deadline:
+        time.sleep(0.002)
+    try:
+        yield
+    finally:
+        behind = ticket - int(add(f"{name}-serving", 0))
+        if behind > 0:
+            add(f"{name}-serving", behind)
 
 
 class LocalRendezvous:
@@ -451,11 +482,18 @@ class PipelineEngine:
         return self.grid.get_data_parallel_id() == dp_id and self.stage_id == stage_id
 
     def announce_preemption(self):
-        """What the SIGTERM handler's flag leads to: publish 'this rank dies before step+1'."""
-        failures = json.loads(_decode(self.global_store.get("failures")))
-        failures = {r: s for r, s in failures.items() if s >= self.global_steps}
-        failures[str(self.global_rank)] = self.global_steps + 1
-        self.global_store.set("failures", json.dumps(failures))
+        """What the SIGTERM handler's flag leads to: publish 'this rank dies before step+1'.
+
+        The record is one shared key that every announcer reads, extends and writes back (reference
+        ``pipe/engine.py:1099-1109``).  Spot instances are often reclaimed several at a time, and two members
+        doing this at the same moment would lose one of the two entries - that member's departure would then
+        only be found by its neighbours' timeouts.  So the update runs under a mutex kept in the store itself."""
+        me, when = str(self.global_rank), self.global_steps + 1
+        with store_mutex(self.global_store, "failures"):
+            failures = json.loads(_decode(self.global_store.get("failures")))
+            failures = {r: s for r, s in failures.items() if s >= self.global_steps}
+            failures[me] = when
+            self.global_store.set("failures", json.dumps(failures))
 
     def _promote_next_stage(self):
         """Take over the successor stage from the shadow copy: its arena becomes a live stage

@@ -307,6 +307,49 @@ def test_concurrent_detectors_agree_on_the_earlier_step():
         assert out == {0: 5, 2: 5}
 
 
+def test_simultaneous_preemption_announcements_are_both_recorded():
+    """Several members announce their preemption at the same moment: the shared record ends up with every
+    entry (the read-extend-write of the record runs under a mutex kept in the store), and an entry of a step
+    long past is dropped on the way."""
+    import json
+    import threading
+    import time
+    from types import SimpleNamespace
+    from bamboo_b200.engine import LocalStore, PipelineEngine, store_mutex
+
+    class SlowStore(LocalStore):
+        """Widens the window between reading and writing the record, so that unprotected updates would collide."""
+        def set(self, key, value):
+            if key == "failures":
+                time.sleep(0.005)
+            super().set(key, value)
+
+    for trial in range(3):
+        store = SlowStore()
+        store.set("failures", json.dumps({"7": 2}))
+        start = threading.Barrier(4)
+
+        def announce(rank):
+            eng = SimpleNamespace(global_store=store, global_rank=rank, global_steps=5)
+            start.wait()
+            PipelineEngine.announce_preemption(eng)
+        ts = [threading.Thread(target=announce, args=(r,)) for r in (1, 3, 4, 6)]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        assert json.loads(store.get("failures")) == {"1": 6, "3": 6, "4": 6, "6": 6}
+    # a holder that died without releasing delays the next member by the timeout, no longer
+    store = LocalStore()
+    store.add("m-ticket", 1)                                 # somebody took a ticket and never released
+    t0 = time.time()
+    with store_mutex(store, "m", timeout_s=0.3):
+        pass
+    assert 0.25 < time.time() - t0 < 2.0
+    t0 = time.time()
+    with store_mutex(store, "m", timeout_s=0.3):             # the counter was moved past the dead holder's ticket
+        pass
+    assert time.time() - t0 < 0.2
+
+
 def test_lone_detector_keeps_its_own_step():
     from types import SimpleNamespace
     from bamboo_b200.engine import LocalStore, PipelineEngine
